@@ -1,0 +1,181 @@
+/*
+ * nslq_b200.h -- C ABI of the B200 (sm_100a) quantized-linear library.
+ *
+ * Drop-in boundary for NSL's quantized-linear path: BitLinear (ternary W1.58 x
+ * int8 activations, exact int32 accumulation) and W4A16 (uint4 group-quantised
+ * weights x 16-bit activations, fp32 accumulation).  Plain pointers and sizes
+ * only; every data pointer is a CUDA device pointer unless a comment says host.
+ * `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *
+ * Conventions follow NSL's extern "C" runtime (docs/abi/README.md:80-113 in the
+ * NSL tree): handles are raw pointers, outputs are caller-allocated, nothing
+ * unwinds across the boundary.  Core functions return a status (0 = ok, < 0 =
+ * error, text from nslq_last_error()); the shims with NSL's own names keep
+ * NSL's behaviour (print + abort on a bad dtype/shape, print + return 0 on null).
+ *
+ * There is no CPU fallback anywhere in this library: every entry point that
+ * computes launches CUDA kernels and fails with NSLQ_ERR_CUDA if it cannot.
+ */
+#ifndef NSLQ_B200_H
+#define NSLQ_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define NSLQ_OK                0
+#define NSLQ_ERR_ARG          -1 /* null pointer, bad enum, misaligned pointer      */
+#define NSLQ_ERR_SHAPE        -2 /* shape the path cannot represent (e.g. K % 4)    */
+#define NSLQ_ERR_CUDA         -3 /* a CUDA runtime call or launch failed            */
+#define NSLQ_ERR_UNSUPPORTED  -4 /* valid request with no kernel for it             */
+#define NSLQ_ERR_WORKSPACE    -5 /* workspace missing or too small                  */
+
+/* ---- dtype tags: NSL's NslTensor.dtype wire tags -------------------------
+ * crates/nsl-runtime/src/tensor/mod.rs:246-256 */
+#define NSLQ_DTYPE_F64   0
+#define NSLQ_DTYPE_F32   1
+#define NSLQ_DTYPE_FP16  2
+#define NSLQ_DTYPE_BF16  3
+#define NSLQ_DTYPE_INT8  4
+#define NSLQ_DTYPE_I32   9
+
+/* Library/ABI version (major*100 + minor) and the last error text of the
+ * calling thread (never NULL; valid until that thread's next failing call). */
+int         nslq_version(void);
+const char *nslq_last_error(void);
+
+/* ========================================================================== */
+/* Stage 1: per-token absmax int8 activation quantisation                      */
+/* ========================================================================== */
+/*
+ * Replaces absmax_scale_row + quantize_row_int8
+ * (crates/nsl-codegen/tests/bitnet_reference_impl.rs:46-70) and the fused
+ * absmax phase of the reference GPU kernel
+ * (crates/nsl-codegen/src/bitnet/phases/absmean_quant.rs:62-177).
+ *
+ *   scale[r] = max_k |x[r,k]|            (NaN ignored; 0 for an all-zero row)
+ *   q[r,k]   = round_half_away(clamp(x[r,k] * (127/scale[r]), -127, 127)) as i8
+ *
+ * x: [M,K] row-major, x_dtype in {F32, FP16, BF16}.  Outputs (each may be NULL
+ * except scale):
+ *   q_plain [M,K] int8   natural k order (what the reference returns)
+ *   q_perm  [M,K] int8   the order the matmul kernels consume: inside every
+ *                        aligned group of 16 k, position 4*i+j holds k = 4*j+i
+ *                        (requires K % 16 == 0)
+ *   scale   [M]   f32
+ *   rowsum  [M]   int32  sum_k q[r,k]
+ */
+int nslq_act_quant_i8(const void *x, int x_dtype, int64_t M, int64_t K,
+                      int8_t *q_plain, int8_t *q_perm, float *scale, int32_t *rowsum,
+                      void *stream);
+
+/* ========================================================================== */
+/* BitLinear (ternary W1.58 A8)                                                */
+/* ========================================================================== */
+typedef struct nslq_bitlinear nslq_bitlinear_t;
+
+/*
+ * Wraps a packed ternary weight in NSL's own layout, zero-copy: row-major
+ * [N = out_dim][K/4] bytes, four consecutive-k trits per byte, HIGH-BITS-FIRST,
+ * code = trit + 1 (crates/nsl-codegen/src/bitnet/pack.rs:38-43; weight layout
+ * crates/nsl-codegen/src/bitnet/mod.rs:97-103).  `weight_scale` is the
+ * per-tensor absmean scale the loader produces
+ * (crates/nsl-codegen/src/bitnet/loader.rs:47-56).  The buffer is borrowed and
+ * must outlive the handle.  K % 4 == 0 (NSL's own constraint,
+ * crates/nsl-codegen/src/bitnet/mod.rs:134-139).
+ */
+int  nslq_bitlinear_create(const uint8_t *packed, int64_t N, int64_t K, float weight_scale,
+                           nslq_bitlinear_t **out);
+void nslq_bitlinear_destroy(nslq_bitlinear_t *w);
+
+/* Bytes of device scratch nslq_bitlinear_forward needs for M tokens of width K
+ * (quantised activations, scales, row sums). */
+int64_t nslq_bitlinear_workspace_bytes(int64_t M, int64_t K);
+
+/*
+ * y[M,N] = BitLinear(x[M,K]).  Replaces the fused reference kernel
+ * nsl_bitnet_b158_gemm_* (crates/nsl-codegen/src/bitnet/mod.rs:133-307) and its
+ * CPU statement forward_reference
+ * (crates/nsl-codegen/tests/bitnet_reference_impl.rs:101-141):
+ *
+ *   acc[r,c] = sum_k q[r,k] * W[c,k]                      exact int32
+ *   y[r,c]   = ((scale[r] / 127) * (float)acc) * weight_scale
+ *              [+ bias[c]] [+ residual[r,c]]               each step rounded to f32
+ *
+ * (finalize order: crates/nsl-codegen/src/bitnet/phases/finalize.rs:39-80).
+ * x_dtype, y_dtype in {F32, FP16, BF16}.  acc_out (int32 [M,N]), bias (f32 [N])
+ * and residual (f32 [M,N]) may be NULL.  workspace: device memory of at least
+ * nslq_bitlinear_workspace_bytes(M,K), 256-byte aligned, private to this call
+ * until the stream reaches the end of it.
+ */
+int nslq_bitlinear_forward(const nslq_bitlinear_t *w, const void *x, int x_dtype, int64_t M,
+                           void *y, int y_dtype, int32_t *acc_out,
+                           const float *bias, const float *residual,
+                           void *workspace, int64_t workspace_bytes, void *stream);
+
+/*
+ * Same product on activations already quantised by nslq_act_quant_i8 (q_perm,
+ * scale, rowsum), so several projections of one input share one quantisation.
+ */
+int nslq_bitlinear_forward_quantized(const nslq_bitlinear_t *w, const int8_t *q_perm,
+                                     const float *scale, const int32_t *rowsum, int64_t M,
+                                     void *y, int y_dtype, int32_t *acc_out,
+                                     const float *bias, const float *residual, void *stream);
+
+/* ========================================================================== */
+/* W4A16 (uint4 group-quantised weights, 16-bit activations)                   */
+/* ========================================================================== */
+typedef struct nslq_w4a16 nslq_w4a16_t;
+
+/*
+ * Weight stored as an NSL QuantizedTensor of shape [N,K], INT4, per-group along
+ * axis 1 stores it (crates/nsl-runtime/src/quantize.rs:27-51, :366-417): codes
+ * two per byte over the flat index n*K+k, low nibble = even k; one scale and one
+ * zero point per (n, k/group); dequantisation (q - zp) * scale
+ * (quantize.rs:263-266).  codes are borrowed; scales/zero points are converted
+ * once into the library's own small f32 tables.
+ *   scale_dtype: F32, BF16, FP16 or F64;  zp_packed: 0 = one u8 per group,
+ *   1 = two uint4 per byte (low nibble = even group index over the flat n*G+g).
+ */
+int nslq_w4a16_create_nk(const uint8_t *codes, const void *scales, int scale_dtype,
+                         const uint8_t *zero_points, int zp_packed,
+                         int64_t N, int64_t K, int64_t group_size, nslq_w4a16_t **out);
+
+/*
+ * Weight in NSL's AwqPackedWeight form (crates/nsl-runtime/src/awq.rs:29-45):
+ * logical [K,N], nibble index row*N+col, f64 scales and f64 float zeros indexed
+ * [g*N+col], dequantisation q*scale+zero (awq.rs:74-76).  Re-laid out once on the
+ * GPU into the [N,K] streaming order; nothing is borrowed.
+ */
+int nslq_w4a16_create_awq_kn(const uint8_t *data, const double *scales, const double *zeros,
+                             int64_t K, int64_t N, int64_t group_size, nslq_w4a16_t **out);
+void nslq_w4a16_destroy(nslq_w4a16_t *w);
+
+/*
+ * y[M,N] = x[M,K] @ dequant(W)^T with fp32 accumulation.  Replaces
+ * awq_matmul_cpu (crates/nsl-runtime/src/awq.rs:202-226) and the
+ * dequantise-then-matmul of nsl_qtensor_matmul_mixed
+ * (crates/nsl-runtime/src/quantize.rs:547-585).  x_dtype in {BF16, FP16, F32},
+ * y_dtype in {BF16, FP16, F32}.
+ */
+int nslq_w4a16_forward(const nslq_w4a16_t *w, const void *x, int x_dtype, int64_t M,
+                       void *y, int y_dtype, void *stream);
+
+/* ========================================================================== */
+/* Column-parallel sharding                                                    */
+/* ========================================================================== */
+/*
+ * Rank `rank` of `world` owns output rows [row0, row0+rows) of W[out,in] -- the
+ * contiguous dim-0 split of NSL's shard math
+ * (crates/nsl-runtime/src/tensor_parallel/sharding.rs:18-58).  N % world != 0 is
+ * NSLQ_ERR_SHAPE, as in the reference.
+ */
+int nslq_shard_rows(int64_t N, int world, int rank, int64_t *row0, int64_t *rows);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NSLQ_B200_H */

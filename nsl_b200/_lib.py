@@ -1,0 +1,58 @@
+"""Loads libnslq_b200.so (the C ABI declared in include/nslq_b200.h) with ctypes.
+
+There is no fallback: if the shared library is missing, loading raises.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libnslq_b200.so")
+
+vp, i64, i32, f32 = C.c_void_p, C.c_int64, C.c_int, C.c_float
+
+# name -> (restype, argtypes); every symbol include/nslq_b200.h declares.
+SIGNATURES = {
+    "nslq_version": (i32, []),
+    "nslq_last_error": (C.c_char_p, []),
+    "nslq_act_quant_i8": (i32, [vp, i32, i64, i64, vp, vp, vp, vp, vp]),
+    "nslq_bitlinear_create": (i32, [vp, i64, i64, f32, C.POINTER(vp)]),
+    "nslq_bitlinear_destroy": (None, [vp]),
+    "nslq_bitlinear_workspace_bytes": (i64, [i64, i64]),
+    "nslq_bitlinear_forward": (i32, [vp, vp, i32, i64, vp, i32, vp, vp, vp, vp, i64, vp]),
+    "nslq_bitlinear_forward_quantized": (i32, [vp, vp, vp, vp, i64, vp, i32, vp, vp, vp, vp]),
+    "nslq_w4a16_create_nk": (i32, [vp, vp, i32, vp, i32, i64, i64, i64, C.POINTER(vp)]),
+    "nslq_w4a16_create_awq_kn": (i32, [vp, vp, vp, i64, i64, i64, C.POINTER(vp)]),
+    "nslq_w4a16_destroy": (None, [vp]),
+    "nslq_w4a16_forward": (i32, [vp, vp, i32, i64, vp, i32, vp]),
+    "nslq_shard_rows": (i32, [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]),
+}
+
+_lib = None
+
+
+class NslqError(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__("nslq error %d: %s" % (code, text))
+        self.code = code
+
+
+def lib():
+    """The loaded library.  Raises if it has not been built (python -m nsl_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                "libnslq_b200.so is missing (%s): build it with `python -m nsl_b200.build`; "
+                "this package has no CPU or PyTorch fallback" % LIB_PATH)
+        l = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        raise NslqError(rc, lib().nslq_last_error().decode("utf-8", "replace"))

@@ -1,0 +1,314 @@
+// extern "C" entry points of libnslq_b200: argument checks, handle objects,
+// kernel selection.  No arithmetic happens on the host and there is no CPU path:
+// every computing call ends in a kernel launch or an error status.
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace nslq {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int check_launch(const char *what)
+{
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    return NSLQ_OK;
+}
+
+// kernels (other translation units)
+int act_quant_dispatch(const void *, int, int64_t, int64_t, int8_t *, int8_t *, float *, int32_t *, cudaStream_t);
+bool ternary_gemv_supported(const void *, const void *, int64_t);
+int ternary_gemv_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int, int64_t, int64_t,
+                          float, void *, int, int32_t *, const float *, const float *, cudaStream_t);
+int ternary_scalar_dispatch(const uint8_t *, const int8_t *, const float *, int64_t, int64_t, int64_t, float,
+                            void *, int, int32_t *, const float *, const float *, cudaStream_t);
+bool ternary_gemm_supported(const void *, const void *, int64_t, int64_t, int64_t);
+int ternary_gemm_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int64_t, int64_t,
+                          int64_t, float, void *, int, int32_t *, const float *, const float *, cudaStream_t);
+bool w4a16_gemv_supported(const void *, const void *, int, int64_t, int64_t);
+int w4a16_gemv_dispatch(const uint8_t *, const float *, const float *, int64_t, int64_t, int, int, const void *,
+                        int, int, void *, int, cudaStream_t);
+int w4a16_scalar_dispatch(const uint8_t *, const float *, const float *, int64_t, int64_t, int, int, const void *,
+                          int, int64_t, void *, int, cudaStream_t);
+
+static inline int out_elem_size(int dt)
+{
+    return dt == NSLQ_DTYPE_F32 ? 4 : (dt == NSLQ_DTYPE_FP16 || dt == NSLQ_DTYPE_BF16) ? 2 : 0;
+}
+
+static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace nslq
+
+using namespace nslq;
+
+struct nslq_bitlinear {
+    const uint8_t *packed;
+    int64_t N, K;
+    float weight_scale;
+};
+
+struct nslq_w4a16 {
+    const uint8_t *codes;   // [N][K/2]
+    uint8_t *codes_owned;   // non-null when the library made its own copy
+    float *scale;           // [N][G] owned
+    float *zc;              // [N][G] owned, zero point in code units
+    int64_t N, K;
+    int G, gs;
+};
+
+// ------------------------------------------------------------------ small table kernels
+namespace nslq {
+
+template <typename S>
+__global__ void w4_tables_nk_kernel(const S *__restrict__ scales, const uint8_t *__restrict__ zp, int zp_packed,
+                                    int64_t n, float *__restrict__ scale_out, float *__restrict__ zc_out)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    scale_out[i] = (float)scales[i];
+    int z = zp_packed ? ((i & 1) ? (zp[i >> 1] >> 4) : (zp[i >> 1] & 15)) : zp[i];
+    zc_out[i] = (float)z;
+}
+
+// AWQ [K,N] -> [N,K]: one thread per output byte (n, k/2).
+__global__ void awq_repack_codes_kernel(const uint8_t *__restrict__ data, int64_t K, int64_t N,
+                                        uint8_t *__restrict__ out)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t kb = K >> 1;
+    if (i >= N * kb) return;
+    const int64_t n = i / kb, k0 = (i % kb) * 2;
+    const int64_t f0 = k0 * N + n, f1 = (k0 + 1) * N + n;
+    const uint8_t q0 = (f0 & 1) ? (data[f0 >> 1] >> 4) : (data[f0 >> 1] & 15);
+    const uint8_t q1 = (f1 & 1) ? (data[f1 >> 1] >> 4) : (data[f1 >> 1] & 15);
+    out[i] = (uint8_t)(q0 | (q1 << 4));
+}
+
+// AWQ tables [G,N] f64 -> [N,G] f32; zero (group minimum) becomes a zero point in
+// code units: q*s + z = (q - (-z/s)) * s.
+__global__ void awq_tables_kernel(const double *__restrict__ scales, const double *__restrict__ zeros, int G,
+                                  int64_t N, float *__restrict__ scale_out, float *__restrict__ zc_out)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N * G) return;
+    const int64_t n = i / G;
+    const int g = (int)(i % G);
+    const double s = scales[(int64_t)g * N + n], z = zeros[(int64_t)g * N + n];
+    scale_out[i] = (float)s;
+    zc_out[i] = (float)(-z / s);
+}
+
+}  // namespace nslq
+
+// ------------------------------------------------------------------ extern "C"
+extern "C" {
+
+int nslq_version(void) { return 100; }
+
+const char *nslq_last_error(void) { return g_err; }
+
+int nslq_act_quant_i8(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q_plain, int8_t *q_perm,
+                      float *scale, int32_t *rowsum, void *stream)
+{
+    return act_quant_dispatch(x, x_dtype, M, K, q_plain, q_perm, scale, rowsum, (cudaStream_t)stream);
+}
+
+int nslq_bitlinear_create(const uint8_t *packed, int64_t N, int64_t K, float weight_scale,
+                          nslq_bitlinear_t **out)
+{
+    if (!packed || !out) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_create: null argument");
+    if (N <= 0 || K <= 0) return fail(NSLQ_ERR_SHAPE, "nslq_bitlinear_create: N=%lld K=%lld", (long long)N, (long long)K);
+    if (K % 4 != 0) return fail(NSLQ_ERR_SHAPE, "nslq_bitlinear_create: hidden_dim %lld is not a multiple of 4", (long long)K);
+    nslq_bitlinear *h = (nslq_bitlinear *)malloc(sizeof(nslq_bitlinear));
+    if (!h) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_create: out of host memory");
+    h->packed = packed; h->N = N; h->K = K; h->weight_scale = weight_scale;
+    *out = h;
+    return NSLQ_OK;
+}
+
+void nslq_bitlinear_destroy(nslq_bitlinear_t *w) { free(w); }
+
+// workspace layout: [q_perm or q_plain: M*K, 256-aligned][scale: M f32, 256-aligned][rowsum: M i32]
+int64_t nslq_bitlinear_workspace_bytes(int64_t M, int64_t K)
+{
+    if (M < 0 || K <= 0) return 0;
+    return align_up(M * K, 256) + align_up(M * 4, 256) + align_up(M * 4, 256);
+}
+
+int nslq_bitlinear_forward_quantized(const nslq_bitlinear_t *w, const int8_t *q_perm, const float *scale,
+                                     const int32_t *rowsum, int64_t M, void *y, int y_dtype, int32_t *acc_out,
+                                     const float *bias, const float *residual, void *stream)
+{
+    if (!w || !q_perm || !scale || !rowsum || !y) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_forward_quantized: null argument");
+    if (!out_elem_size(y_dtype)) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_forward_quantized: y_dtype %d not in {F32,FP16,BF16}", y_dtype);
+    if (M < 0) return fail(NSLQ_ERR_SHAPE, "nslq_bitlinear_forward_quantized: M=%lld", (long long)M);
+    if (M == 0) return NSLQ_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M > 16 && ternary_gemm_supported(w->packed, q_perm, M, w->N, w->K))
+        return ternary_gemm_dispatch(w->packed, q_perm, scale, rowsum, M, w->N, w->K, w->weight_scale, y, y_dtype,
+                                     acc_out, bias, residual, st);
+    if (!ternary_gemv_supported(w->packed, q_perm, w->K))
+        return fail(NSLQ_ERR_UNSUPPORTED, "nslq_bitlinear_forward_quantized: needs K %% 64 == 0 and 16-byte aligned buffers (K=%lld)",
+                    (long long)w->K);
+    const int es = out_elem_size(y_dtype);
+    for (int64_t m0 = 0; m0 < M; m0 += 16) {
+        const int mc = (int)((M - m0) < 16 ? (M - m0) : 16);
+        int rc = ternary_gemv_dispatch(w->packed, q_perm + m0 * w->K, scale + m0, rowsum + m0, mc, w->N, w->K,
+                                       w->weight_scale, (char *)y + m0 * w->N * es, y_dtype,
+                                       acc_out ? acc_out + m0 * w->N : nullptr, bias,
+                                       residual ? residual + m0 * w->N : nullptr, st);
+        if (rc) return rc;
+    }
+    return NSLQ_OK;
+}
+
+int nslq_bitlinear_forward(const nslq_bitlinear_t *w, const void *x, int x_dtype, int64_t M, void *y, int y_dtype,
+                           int32_t *acc_out, const float *bias, const float *residual, void *workspace,
+                           int64_t workspace_bytes, void *stream)
+{
+    if (!w || !x || !y) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_forward: null argument");
+    if (!out_elem_size(y_dtype)) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_forward: y_dtype %d not in {F32,FP16,BF16}", y_dtype);
+    if (M < 0) return fail(NSLQ_ERR_SHAPE, "nslq_bitlinear_forward: M=%lld", (long long)M);
+    if (M == 0) return NSLQ_OK;
+    const int64_t need = nslq_bitlinear_workspace_bytes(M, w->K);
+    if (!workspace || workspace_bytes < need)
+        return fail(NSLQ_ERR_WORKSPACE, "nslq_bitlinear_forward: workspace %lld bytes, need %lld", (long long)workspace_bytes, (long long)need);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_forward: workspace not 256-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    int8_t *q = (int8_t *)workspace;
+    float *scale = (float *)((char *)workspace + align_up(M * w->K, 256));
+    int32_t *rowsum = (int32_t *)((char *)scale + align_up(M * 4, 256));
+    const bool fast = (w->K % 64 == 0) && aligned16(w->packed);
+    if (fast) {
+        int rc = act_quant_dispatch(x, x_dtype, M, w->K, nullptr, q, scale, rowsum, st);
+        if (rc) return rc;
+        return nslq_bitlinear_forward_quantized(w, q, scale, rowsum, M, y, y_dtype, acc_out, bias, residual, stream);
+    }
+    int rc = act_quant_dispatch(x, x_dtype, M, w->K, q, nullptr, scale, rowsum, st);
+    if (rc) return rc;
+    return ternary_scalar_dispatch(w->packed, q, scale, M, w->N, w->K, w->weight_scale, y, y_dtype, acc_out, bias,
+                                   residual, st);
+}
+
+// ---------------------------------------------------------------- W4A16
+static int w4_alloc_tables(nslq_w4a16 *h)
+{
+    const size_t n = (size_t)h->N * (size_t)h->G;
+    if (cudaMalloc(&h->scale, n * 4) != cudaSuccess || cudaMalloc(&h->zc, n * 4) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "W4A16 tables: cudaMalloc failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return NSLQ_OK;
+}
+
+static int w4_check_shape(const char *who, int64_t N, int64_t K, int64_t gs)
+{
+    if (N <= 0 || K <= 0 || gs <= 0) return fail(NSLQ_ERR_SHAPE, "%s: N=%lld K=%lld group=%lld", who, (long long)N, (long long)K, (long long)gs);
+    if (K % 2 != 0) return fail(NSLQ_ERR_SHAPE, "%s: K=%lld must be even (two codes per byte)", who, (long long)K);
+    return NSLQ_OK;
+}
+
+int nslq_w4a16_create_nk(const uint8_t *codes, const void *scales, int scale_dtype, const uint8_t *zero_points,
+                         int zp_packed, int64_t N, int64_t K, int64_t group_size, nslq_w4a16_t **out)
+{
+    if (!codes || !scales || !zero_points || !out) return fail(NSLQ_ERR_ARG, "nslq_w4a16_create_nk: null argument");
+    int rc = w4_check_shape("nslq_w4a16_create_nk", N, K, group_size);
+    if (rc) return rc;
+    nslq_w4a16 *h = (nslq_w4a16 *)calloc(1, sizeof(nslq_w4a16));
+    if (!h) return fail(NSLQ_ERR_ARG, "nslq_w4a16_create_nk: out of host memory");
+    h->codes = codes; h->N = N; h->K = K; h->gs = (int)group_size; h->G = (int)((K + group_size - 1) / group_size);
+    if ((rc = w4_alloc_tables(h))) { nslq_w4a16_destroy(h); return rc; }
+    const int64_t n = N * h->G;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    switch (scale_dtype) {
+    case NSLQ_DTYPE_F32: w4_tables_nk_kernel<float><<<blocks, 256>>>((const float *)scales, zero_points, zp_packed, n, h->scale, h->zc); break;
+    case NSLQ_DTYPE_F64: w4_tables_nk_kernel<double><<<blocks, 256>>>((const double *)scales, zero_points, zp_packed, n, h->scale, h->zc); break;
+    case NSLQ_DTYPE_BF16: w4_tables_nk_kernel<__nv_bfloat16><<<blocks, 256>>>((const __nv_bfloat16 *)scales, zero_points, zp_packed, n, h->scale, h->zc); break;
+    case NSLQ_DTYPE_FP16: w4_tables_nk_kernel<__half><<<blocks, 256>>>((const __half *)scales, zero_points, zp_packed, n, h->scale, h->zc); break;
+    default: nslq_w4a16_destroy(h); return fail(NSLQ_ERR_ARG, "nslq_w4a16_create_nk: scale_dtype %d", scale_dtype);
+    }
+    if ((rc = check_launch("w4_tables_nk_kernel"))) { nslq_w4a16_destroy(h); return rc; }
+    if (cudaDeviceSynchronize() != cudaSuccess) { nslq_w4a16_destroy(h); return fail(NSLQ_ERR_CUDA, "nslq_w4a16_create_nk: %s", cudaGetErrorString(cudaGetLastError())); }
+    *out = h;
+    return NSLQ_OK;
+}
+
+int nslq_w4a16_create_awq_kn(const uint8_t *data, const double *scales, const double *zeros, int64_t K, int64_t N,
+                             int64_t group_size, nslq_w4a16_t **out)
+{
+    if (!data || !scales || !zeros || !out) return fail(NSLQ_ERR_ARG, "nslq_w4a16_create_awq_kn: null argument");
+    int rc = w4_check_shape("nslq_w4a16_create_awq_kn", N, K, group_size);
+    if (rc) return rc;
+    nslq_w4a16 *h = (nslq_w4a16 *)calloc(1, sizeof(nslq_w4a16));
+    if (!h) return fail(NSLQ_ERR_ARG, "nslq_w4a16_create_awq_kn: out of host memory");
+    h->N = N; h->K = K; h->gs = (int)group_size; h->G = (int)((K + group_size - 1) / group_size);
+    if ((rc = w4_alloc_tables(h))) { nslq_w4a16_destroy(h); return rc; }
+    if (cudaMalloc(&h->codes_owned, (size_t)(N * (K / 2))) != cudaSuccess) {
+        nslq_w4a16_destroy(h);
+        return fail(NSLQ_ERR_CUDA, "nslq_w4a16_create_awq_kn: cudaMalloc failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+    h->codes = h->codes_owned;
+    const int64_t nb = N * (K / 2);
+    awq_repack_codes_kernel<<<(unsigned)((nb + 255) / 256), 256>>>(data, K, N, h->codes_owned);
+    if ((rc = check_launch("awq_repack_codes_kernel"))) { nslq_w4a16_destroy(h); return rc; }
+    awq_tables_kernel<<<(unsigned)((N * h->G + 255) / 256), 256>>>(scales, zeros, h->G, N, h->scale, h->zc);
+    if ((rc = check_launch("awq_tables_kernel"))) { nslq_w4a16_destroy(h); return rc; }
+    if (cudaDeviceSynchronize() != cudaSuccess) { nslq_w4a16_destroy(h); return fail(NSLQ_ERR_CUDA, "nslq_w4a16_create_awq_kn: %s", cudaGetErrorString(cudaGetLastError())); }
+    *out = h;
+    return NSLQ_OK;
+}
+
+void nslq_w4a16_destroy(nslq_w4a16_t *w)
+{
+    if (!w) return;
+    if (w->scale) cudaFree(w->scale);
+    if (w->zc) cudaFree(w->zc);
+    if (w->codes_owned) cudaFree(w->codes_owned);
+    free(w);
+}
+
+int nslq_w4a16_forward(const nslq_w4a16_t *w, const void *x, int x_dtype, int64_t M, void *y, int y_dtype,
+                       void *stream)
+{
+    if (!w || !x || !y) return fail(NSLQ_ERR_ARG, "nslq_w4a16_forward: null argument");
+    const int es = out_elem_size(y_dtype);
+    if (!es) return fail(NSLQ_ERR_ARG, "nslq_w4a16_forward: y_dtype %d not in {F32,FP16,BF16}", y_dtype);
+    if (M < 0) return fail(NSLQ_ERR_SHAPE, "nslq_w4a16_forward: M=%lld", (long long)M);
+    if (M == 0) return NSLQ_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (w4a16_gemv_supported(w->codes, x, x_dtype, w->K, w->gs)) {
+        for (int64_t m0 = 0; m0 < M; m0 += 16) {
+            const int mc = (int)((M - m0) < 16 ? (M - m0) : 16);
+            int rc = w4a16_gemv_dispatch(w->codes, w->scale, w->zc, w->N, w->K, w->G, w->gs,
+                                         (const char *)x + m0 * w->K * 2, x_dtype, mc,
+                                         (char *)y + m0 * w->N * es, y_dtype, st);
+            if (rc) return rc;
+        }
+        return NSLQ_OK;
+    }
+    return w4a16_scalar_dispatch(w->codes, w->scale, w->zc, w->N, w->K, w->G, w->gs, x, x_dtype, M, y, y_dtype, st);
+}
+
+int nslq_shard_rows(int64_t N, int world, int rank, int64_t *row0, int64_t *rows)
+{
+    if (!row0 || !rows) return fail(NSLQ_ERR_ARG, "nslq_shard_rows: null output");
+    if (world <= 0 || rank < 0 || rank >= world) return fail(NSLQ_ERR_ARG, "nslq_shard_rows: rank %d of %d", rank, world);
+    if (N % world != 0) return fail(NSLQ_ERR_SHAPE, "nslq_shard_rows: out_dim %lld is not divisible by world size %d", (long long)N, world);
+    *rows = N / world;
+    *row0 = *rows * rank;
+    return NSLQ_OK;
+}
+
+}  // extern "C"

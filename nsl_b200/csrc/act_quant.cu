@@ -1,0 +1,176 @@
+// Stage 1: per-token absmax int8 activation quantisation.
+//
+// One CTA per token row.  Pass 1 reduces max|x| with warp shuffles (then across
+// warps through shared memory); pass 2 re-reads the row (it is still in L1/L2),
+// quantises with the reference's exact arithmetic and writes the int8 row in the
+// natural order and/or the order the matmul kernels consume, plus scale and sum.
+//
+// Arithmetic follows crates/nsl-codegen/tests/bitnet_reference_impl.rs:46-70 of
+// NSL: inv = 127/scale (IEEE divide), v = x*inv, clamp to [-127,127], round half
+// away from zero, NaN -> 0.
+#include "common.cuh"
+
+namespace nslq {
+
+constexpr int AQ_THREADS = 256;
+
+static __device__ __forceinline__ int quant_one(float x, float inv)
+{
+    float s = __fmul_rn(x, inv);
+    s = (s < -127.0f) ? -127.0f : ((s > 127.0f) ? 127.0f : s);  // NaN passes through
+    float t = truncf(s);
+    if (fabsf(s - t) >= 0.5f) t += copysignf(1.0f, s);           // half away from zero
+    return __float2int_rz(t);                                   // NaN -> 0
+}
+
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float *row, int64_t v) {
+        return reinterpret_cast<const float4 *>(row)[v];
+    }
+};
+template <> struct Vec4<__half> {
+    static __device__ __forceinline__ float4 load(const __half *row, int64_t v) {
+        uint2 r = reinterpret_cast<const uint2 *>(row)[v];
+        float2 a = __half22float2(*reinterpret_cast<__half2 *>(&r.x));
+        float2 b = __half22float2(*reinterpret_cast<__half2 *>(&r.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16 *row, int64_t v) {
+        uint2 r = reinterpret_cast<const uint2 *>(row)[v];
+        float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&r.x));
+        float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&r.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
+
+static __device__ __forceinline__ float block_max(float v, float *smem)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) smem[w] = v;
+    __syncthreads();
+    float r = (l < AQ_THREADS / 32) ? smem[l] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, o));
+    return r;  // every thread holds the block maximum
+}
+
+static __device__ __forceinline__ int block_sum(int v, int *smem)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __syncthreads();
+    if (l == 0) smem[w] = v;
+    __syncthreads();
+    int r = (l < AQ_THREADS / 32) ? smem[l] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    return r;
+}
+
+// VEC = true: K % 16 == 0 and 16-byte aligned rows; four elements per thread per
+// iteration, quads of lanes cover one group of 16 k (needed for q_perm).
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(AQ_THREADS)
+act_quant_kernel(const T *__restrict__ x, int64_t K, int8_t *__restrict__ q_plain,
+                 int8_t *__restrict__ q_perm, float *__restrict__ scale_out,
+                 int32_t *__restrict__ rowsum_out)
+{
+    __shared__ float smax[AQ_THREADS / 32];
+    __shared__ int ssum[AQ_THREADS / 32];
+    const int64_t r = blockIdx.x;
+    const T *row = x + r * K;
+    pdl_wait();
+
+    float m = 0.0f;
+    if (VEC) {
+        for (int64_t v = threadIdx.x; v < K / 4; v += AQ_THREADS) {
+            float4 f = Vec4<T>::load(row, v);
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+        }
+    } else {
+        for (int64_t k = threadIdx.x; k < K; k += AQ_THREADS) m = fmaxf(m, fabsf(Elem<T>::to_f32(row[k])));
+    }
+    const float scale = block_max(m, smax);
+    pdl_launch_dependents();
+    const float inv = __fdiv_rn(127.0f, scale);
+    const bool zero_row = (scale == 0.0f);
+
+    int sum = 0;
+    if (VEC) {
+        // K/4 is a multiple of 4 and AQ_THREADS is a multiple of 4, so the four
+        // lanes of a quad are always inside the row together.
+        for (int64_t base = 0; base < K / 4; base += AQ_THREADS) {
+            const int64_t v = base + threadIdx.x;
+            const bool in = v < K / 4;
+            // lanes that are inside the row (whole quads); the shuffles below name exactly these
+            const unsigned mask = __ballot_sync(0xffffffffu, in);
+            if (!in) continue;
+            float4 f = Vec4<T>::load(row, v);
+            int q0 = zero_row ? 0 : quant_one(f.x, inv), q1 = zero_row ? 0 : quant_one(f.y, inv);
+            int q2 = zero_row ? 0 : quant_one(f.z, inv), q3 = zero_row ? 0 : quant_one(f.w, inv);
+            sum += q0 + q1 + q2 + q3;
+            uint32_t w = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) |
+                         ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+            if (q_plain) reinterpret_cast<uint32_t *>(q_plain + r * K)[v] = w;
+            if (q_perm) {
+                // lane j of the quad holds k = 4j..4j+3 of a 16-group; output word i
+                // (written by lane i) is byte i of lanes 0..3: a 4x4 byte transpose.
+                const int lane = threadIdx.x & 31, qb = lane & ~3, i = lane & 3;
+                uint32_t w0 = __shfl_sync(mask, w, qb + 0), w1 = __shfl_sync(mask, w, qb + 1);
+                uint32_t w2 = __shfl_sync(mask, w, qb + 2), w3 = __shfl_sync(mask, w, qb + 3);
+                uint32_t lo = __byte_perm(w0, w1, 0x0040 + i * 0x0011);   // (w0.b[i], w1.b[i], -, -)
+                uint32_t hi = __byte_perm(w2, w3, 0x0040 + i * 0x0011);
+                uint32_t o = __byte_perm(lo, hi, 0x5410);
+                reinterpret_cast<uint32_t *>(q_perm + r * K)[v] = o;
+            }
+        }
+    } else {
+        for (int64_t k = threadIdx.x; k < K; k += AQ_THREADS) {
+            int q = zero_row ? 0 : quant_one(Elem<T>::to_f32(row[k]), inv);
+            sum += q;
+            if (q_plain) q_plain[r * K + k] = (int8_t)q;
+        }
+    }
+    if (rowsum_out) {
+        int tot = block_sum(sum, ssum);
+        if (threadIdx.x == 0) rowsum_out[r] = tot;
+    }
+    if (threadIdx.x == 0) scale_out[r] = scale;
+}
+
+template <typename T>
+static int launch_act_quant(const void *x, int64_t M, int64_t K, int8_t *q_plain, int8_t *q_perm,
+                            float *scale, int32_t *rowsum, cudaStream_t st)
+{
+    const bool vec = (K % 16 == 0) && aligned16(x) && (!q_plain || aligned16(q_plain)) &&
+                     (!q_perm || aligned16(q_perm));
+    if (q_perm && !vec)
+        return fail(NSLQ_ERR_SHAPE, "nslq_act_quant_i8: q_perm needs K %% 16 == 0 and 16-byte aligned buffers (K=%lld)",
+                    (long long)K);
+    dim3 grid((unsigned)M), block(AQ_THREADS);
+    if (vec) act_quant_kernel<T, true><<<grid, block, 0, st>>>((const T *)x, K, q_plain, q_perm, scale, rowsum);
+    else act_quant_kernel<T, false><<<grid, block, 0, st>>>((const T *)x, K, q_plain, q_perm, scale, rowsum);
+    return check_launch("act_quant_kernel");
+}
+
+int act_quant_dispatch(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q_plain, int8_t *q_perm,
+                       float *scale, int32_t *rowsum, cudaStream_t st)
+{
+    if (!x || !scale) return fail(NSLQ_ERR_ARG, "nslq_act_quant_i8: null x or scale");
+    if (M < 0 || K <= 0 || M > 0x7fffffffLL) return fail(NSLQ_ERR_SHAPE, "nslq_act_quant_i8: bad M=%lld K=%lld", (long long)M, (long long)K);
+    if (M == 0) return NSLQ_OK;
+    switch (x_dtype) {
+    case NSLQ_DTYPE_F32: return launch_act_quant<float>(x, M, K, q_plain, q_perm, scale, rowsum, st);
+    case NSLQ_DTYPE_FP16: return launch_act_quant<__half>(x, M, K, q_plain, q_perm, scale, rowsum, st);
+    case NSLQ_DTYPE_BF16: return launch_act_quant<__nv_bfloat16>(x, M, K, q_plain, q_perm, scale, rowsum, st);
+    default: return fail(NSLQ_ERR_ARG, "nslq_act_quant_i8: x_dtype %d not in {F32,FP16,BF16}", x_dtype);
+    }
+}
+
+}  // namespace nslq

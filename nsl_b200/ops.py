@@ -1,0 +1,146 @@
+"""Host-side operators over torch CUDA tensors, one per entry point of the C ABI.
+
+torch is used for device memory and streams only; all arithmetic runs in the
+CUDA kernels of libnslq_b200.so.  Names follow NSL: BitLinear forward
+(crates/nsl-codegen/src/bitnet/mod.rs:133), nsl_qtensor_matmul_mixed
+(crates/nsl-runtime/src/quantize.rs:547), nsl_awq_matmul
+(crates/nsl-runtime/src/awq.rs:261).
+"""
+import ctypes as C
+
+import torch
+
+from ._lib import check, lib
+
+F64, F32, FP16, BF16, INT8, I32 = 0, 1, 2, 3, 4, 9
+_TAG = {torch.float64: F64, torch.float32: F32, torch.float16: FP16, torch.bfloat16: BF16}
+
+
+def _tag(dtype):
+    if dtype not in _TAG:
+        raise TypeError("dtype %s has no NSL tensor tag on this path" % dtype)
+    return _TAG[dtype]
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _cuda2d(x, what):
+    if not x.is_cuda:
+        raise ValueError("%s must be a CUDA tensor (there is no CPU path)" % what)
+    if x.dim() != 2 or not x.is_contiguous():
+        raise ValueError("%s must be a contiguous 2-D tensor" % what)
+    return x
+
+
+def act_quant_i8(x, plain=True, perm=True):
+    """Per-token absmax int8 quantisation.  Returns dict(scale, rowsum, q_plain, q_perm)."""
+    _cuda2d(x, "x")
+    M, K = x.shape
+    dev = x.device
+    out = {
+        "scale": torch.empty(M, dtype=torch.float32, device=dev),
+        "rowsum": torch.empty(M, dtype=torch.int32, device=dev),
+        "q_plain": torch.empty(M, K, dtype=torch.int8, device=dev) if plain else None,
+        "q_perm": torch.empty(M, K, dtype=torch.int8, device=dev) if perm else None,
+    }
+    check(lib().nslq_act_quant_i8(_ptr(x), _tag(x.dtype), M, K, _ptr(out["q_plain"]), _ptr(out["q_perm"]),
+                                  _ptr(out["scale"]), _ptr(out["rowsum"]), _stream()))
+    return out
+
+
+class BitLinear:
+    """A ternary weight in NSL's packed layout ([out_dim, hidden_dim/4] uint8) on the GPU."""
+
+    def __init__(self, packed, weight_scale=1.0):
+        if not packed.is_cuda or packed.dtype != torch.uint8 or packed.dim() != 2 or not packed.is_contiguous():
+            raise ValueError("packed must be a contiguous CUDA uint8 tensor [out_dim, hidden_dim/4]")
+        self.packed = packed                    # keeps the borrowed buffer alive
+        self.N, self.K = packed.shape[0], packed.shape[1] * 4
+        self.weight_scale = float(weight_scale)
+        h = C.c_void_p()
+        check(lib().nslq_bitlinear_create(_ptr(packed), self.N, self.K, self.weight_scale, C.byref(h)))
+        self._h = h
+        self._ws = None
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            lib().nslq_bitlinear_destroy(h)
+
+    def workspace(self, M):
+        need = int(lib().nslq_bitlinear_workspace_bytes(M, self.K))
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=self.packed.device)
+        return self._ws
+
+    def forward(self, x, out_dtype=torch.float32, return_acc=False, bias=None, residual=None, out=None,
+                workspace=None):
+        _cuda2d(x, "x")
+        M = x.shape[0]
+        if x.shape[1] != self.K:
+            raise ValueError("x has hidden dim %d, weight expects %d" % (x.shape[1], self.K))
+        y = out if out is not None else torch.empty(M, self.N, dtype=out_dtype, device=x.device)
+        acc = torch.empty(M, self.N, dtype=torch.int32, device=x.device) if return_acc else None
+        ws = workspace if workspace is not None else self.workspace(M)
+        check(lib().nslq_bitlinear_forward(self._h, _ptr(x), _tag(x.dtype), M, _ptr(y), _tag(y.dtype), _ptr(acc),
+                                           _ptr(bias), _ptr(residual), _ptr(ws), ws.numel(), _stream()))
+        return (y, acc) if return_acc else y
+
+    def forward_quantized(self, qa, out_dtype=torch.float32, return_acc=False, bias=None, residual=None, out=None):
+        """qa: the dict act_quant_i8 returns (uses q_perm, scale, rowsum)."""
+        M = qa["scale"].shape[0]
+        dev = qa["scale"].device
+        y = out if out is not None else torch.empty(M, self.N, dtype=out_dtype, device=dev)
+        acc = torch.empty(M, self.N, dtype=torch.int32, device=dev) if return_acc else None
+        check(lib().nslq_bitlinear_forward_quantized(self._h, _ptr(qa["q_perm"]), _ptr(qa["scale"]),
+                                                     _ptr(qa["rowsum"]), M, _ptr(y), _tag(y.dtype), _ptr(acc),
+                                                     _ptr(bias), _ptr(residual), _stream()))
+        return (y, acc) if return_acc else y
+
+
+class W4A16:
+    """A uint4 group-quantised weight; see nslq_w4a16_create_nk / _awq_kn in the header."""
+
+    def __init__(self, handle, keep, N, K, group_size):
+        self._h, self._keep, self.N, self.K, self.group_size = handle, keep, N, K, group_size
+
+    @classmethod
+    def from_nk(cls, codes, scales, zero_points, group_size, zp_packed=False):
+        N, K = codes.shape[0], codes.shape[1] * 2
+        h = C.c_void_p()
+        check(lib().nslq_w4a16_create_nk(_ptr(codes), _ptr(scales), _tag(scales.dtype), _ptr(zero_points),
+                                         1 if zp_packed else 0, N, K, group_size, C.byref(h)))
+        return cls(h, (codes,), N, K, group_size)
+
+    @classmethod
+    def from_awq_kn(cls, data, scales, zeros, K, N, group_size):
+        h = C.c_void_p()
+        check(lib().nslq_w4a16_create_awq_kn(_ptr(data), _ptr(scales), _ptr(zeros), K, N, group_size, C.byref(h)))
+        return cls(h, (), N, K, group_size)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            lib().nslq_w4a16_destroy(h)
+
+    def forward(self, x, out_dtype=None, out=None):
+        _cuda2d(x, "x")
+        M = x.shape[0]
+        if x.shape[1] != self.K:
+            raise ValueError("x has K=%d, weight expects %d" % (x.shape[1], self.K))
+        y = out if out is not None else torch.empty(M, self.N, dtype=out_dtype or x.dtype, device=x.device)
+        check(lib().nslq_w4a16_forward(self._h, _ptr(x), _tag(x.dtype), M, _ptr(y), _tag(y.dtype), _stream()))
+        return y
+
+
+def shard_rows(N, world, rank):
+    """(row0, rows) of the output rows rank `rank` owns under column-parallel sharding."""
+    r0, n = C.c_int64(), C.c_int64()
+    check(lib().nslq_shard_rows(N, world, rank, C.byref(r0), C.byref(n)))
+    return r0.value, n.value

@@ -1,0 +1,65 @@
+"""CPU checks of the boundary: the shared library loads, exports every symbol the
+header declares, and the argument checks that need no GPU behave."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def built():
+    from nsl_b200 import build
+    return build.build()
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "nslq_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(nslq?_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(built):
+    names = declared_symbols()
+    assert "nslq_bitlinear_forward" in names and "nslq_w4a16_forward" in names
+    l = C.CDLL(built)
+    missing = [n for n in names if not hasattr(l, n)]
+    assert not missing, missing
+
+
+def test_ctypes_table_matches_header(built):
+    from nsl_b200 import _lib
+    assert sorted(_lib.SIGNATURES) == declared_symbols()
+
+
+def test_argument_checks_without_gpu(built):
+    from nsl_b200 import _lib
+    l = _lib.lib()
+    assert l.nslq_version() >= 100
+    r0, n = C.c_int64(), C.c_int64()
+    assert l.nslq_shard_rows(8640, 8, 7, C.byref(r0), C.byref(n)) == 0 and (r0.value, n.value) == (7560, 1080)
+    assert l.nslq_shard_rows(10, 4, 0, C.byref(r0), C.byref(n)) == -2
+    assert b"divisible" in l.nslq_last_error()
+    assert l.nslq_shard_rows(16, 4, 4, C.byref(r0), C.byref(n)) == -1
+    h = C.c_void_p()
+    assert l.nslq_bitlinear_create(None, 16, 64, 1.0, C.byref(h)) == -1
+    assert l.nslq_bitlinear_create(C.c_void_p(256), 16, 62, 1.0, C.byref(h)) == -2     # K % 4
+    assert l.nslq_bitlinear_create(C.c_void_p(256), 16, 64, 1.0, C.byref(h)) == 0
+    assert l.nslq_bitlinear_workspace_bytes(16, 3200) >= 16 * 3200 + 128
+    # missing workspace is refused before anything is launched
+    assert l.nslq_bitlinear_forward(h, C.c_void_p(256), 1, 1, C.c_void_p(512), 1, None, None, None, None, 0, None) == -5
+    l.nslq_bitlinear_destroy(h)
+    assert l.nslq_act_quant_i8(None, 1, 1, 16, None, None, None, None, None) == -1
+    assert l.nslq_w4a16_forward(None, None, 3, 1, None, 3, None) == -1
+
+
+def test_no_oracle_in_product():
+    """The package must not import or reference the CPU checker."""
+    pkg = os.path.join(ROOT, "nsl_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.lower(), os.path.join(dirpath, f)
