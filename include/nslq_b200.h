@@ -47,6 +47,12 @@ extern "C" {
 int         nslq_version(void);
 const char *nslq_last_error(void);
 
+/* Every wait inside the kernels (mbarrier phases of the tensor-core GEMM) is
+ * bounded in time; a kernel whose wait expires records a nonzero code and ends
+ * normally instead of spinning.  This reads that word of the current device into
+ * *status (0 = no wait ever expired) and clears it.  Synchronises the device. */
+int nslq_device_status(int *status);
+
 /* ========================================================================== */
 /* Stage 1: per-token absmax int8 activation quantisation                      */
 /* ========================================================================== */

@@ -38,6 +38,7 @@ int ternary_scalar_dispatch(const uint8_t *, const int8_t *, const float *, int6
 bool ternary_gemm_supported(const void *, const void *, int64_t, int64_t, int64_t);
 int ternary_gemm_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int64_t, int64_t,
                           int64_t, float, void *, int, int32_t *, const float *, const float *, cudaStream_t);
+int device_status_read(int *);
 bool w4a16_gemv_supported(const void *, const void *, int, int64_t, int64_t);
 int w4a16_gemv_dispatch(const uint8_t *, const float *, const float *, int64_t, int64_t, int, int, const void *,
                         int, int, void *, int, cudaStream_t);
@@ -120,6 +121,14 @@ extern "C" {
 int nslq_version(void) { return 100; }
 
 const char *nslq_last_error(void) { return g_err; }
+
+int nslq_device_status(int *status)
+{
+    if (!status) return fail(NSLQ_ERR_ARG, "nslq_device_status: null output");
+    if (cudaDeviceSynchronize() != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "nslq_device_status: %s", cudaGetErrorString(cudaGetLastError()));
+    return device_status_read(status);
+}
 
 int nslq_act_quant_i8(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q_plain, int8_t *q_perm,
                       float *scale, int32_t *rowsum, void *stream)

@@ -1,8 +1,479 @@
-// placeholder until the tcgen05 kernel lands
+// Stage 3: BitLinear prefill GEMM on the 5th-generation tensor cores (sm_100a).
+//
+//   acc[m,n] = sum_k q[m,k] * W[n,k]        int8 x ternary, exact int32
+//
+// Persistent, warp-specialised kernel, one CTA per SM, 128 x BN output tiles:
+//
+//   warp 0      TMA producer: the int8 activation tile (128 rows x 128 k) is copied
+//               by cp.async.bulk.tensor (2-D, SWIZZLE_128B, no multicast) into a
+//               ring of shared-memory stages.
+//   warps 8-11  unpack: the 2-bit packed weight tile (BN rows x 32 bytes) is read
+//               from global memory one k-block ahead, expanded in registers with
+//               (w >> s) & 0x03030303 -- one 32-bit word of packed bytes becomes
+//               one 16-byte group of u8 codes {0,1,2} -- and written into the same
+//               stage in the K-major 128-byte-swizzled layout the tensor core
+//               reads, then published with fence.proxy.async + mbarrier arrive.
+//               The activations are stored in the matching order (position 4i+j of
+//               every 16 holds k = 4j+i), so nothing is permuted here.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma.kind::i8 (M=128, N=BN,
+//               K=32; A = s8 activations, B = u8 codes, D = s32 in TMEM) four times
+//               per stage and releases the stage with tcgen05.commit.
+//   warps 4-7   epilogue: tcgen05.ld the accumulator (double-buffered in TMEM, so
+//               the next tile's MMAs run meanwhile), subtract the token's row sum
+//               (code = trit + 1), apply ((scale/127)*acc)*weight_scale with
+//               separately rounded steps, transpose through a padded shared-memory
+//               patch and store 128-byte row segments.
+//
+// Every mbarrier wait is bounded in time; on expiry the kernel records a status
+// word (read with nslq_device_status) and falls through to the common teardown,
+// which frees its TMEM.  No spin is unbounded.
+#include <cuda.h>
+
 #include "common.cuh"
+
 namespace nslq {
-bool ternary_gemm_supported(const void *, const void *, int64_t, int64_t, int64_t) { return false; }
-int ternary_gemm_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int64_t, int64_t,
-                          int64_t, float, void *, int, int32_t *, const float *, const float *, cudaStream_t)
-{ return fail(NSLQ_ERR_UNSUPPORTED, "tcgen05 GEMM not built"); }
+
+__device__ int g_device_status = 0;   // 0 = ok; else (role << 8 | site) of the first wait that expired
+
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BK = 128;                  // bytes of int8 along K per stage = one 128B swizzle row
+constexpr int THREADS = 384;
+constexpr int A_BYTES = BM * BK;         // 16 KiB
+constexpr int STAGE_PAD = 36;            // floats per staged row (32 + 4: conflict-free 16-byte accesses)
+constexpr int STAGING_BYTES = 4 * 32 * STAGE_PAD * 4;
+constexpr unsigned long long WAIT_NS = 2000000000ull;   // 2 s per wait, then give up
+
+template <int BN> struct Cfg {
+    static constexpr int B_BYTES = BN * BK;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : 5;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + STAGING_BYTES + 256 + 1024;  // + barriers + alignment slack
+    static constexpr uint32_t IDESC = (2u << 4)        // D format: s32
+                                      | (1u << 7)      // A format: signed 8-bit
+                                      | (0u << 10)     // B format: unsigned 8-bit
+                                      | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+};
+
+struct Params {
+    const uint8_t *w;        // [N][K/4]
+    const float *scale;      // [M]
+    const int32_t *rowsum;   // [M]
+    void *y;                 // [M][N]
+    int32_t *acc_out;        // [M][N] or null
+    const float *bias;       // [N] or null
+    const float *residual;   // [M][N] or null
+    int64_t M, N, K;
+    int y_dtype;
+    float weight_scale;
+    int tiles_m, tiles_n;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+static __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+static __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+static __device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+static __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+static __device__ __forceinline__ unsigned long long globaltimer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: true when the phase completed, false after WAIT_NS (status word set).
+static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int site)
+{
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((spin & 63u) == 63u) {
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_NS) { atomicCAS(&g_device_status, 0, site); return false; }
+        }
+    }
+}
+static __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tmap, int x, int y, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+static __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+static __device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+static __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+static __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+static __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major, 128-byte swizzle: 8-row groups 1024 B apart (SBO), LBO unused (=1), version 1.
+static __device__ __forceinline__ uint64_t smem_desc(uint32_t addr)
+{
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// ---------------------------------------------------------------- kernel
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const Params p)
+{
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                  // 1024-byte aligned (swizzle atom)
+    uint8_t *base_ptr = smem_raw + (base - raw);
+    const uint32_t staging = base + C::STAGES * C::STAGE_BYTES;
+    float *staging_ptr = reinterpret_cast<float *>(base_ptr + C::STAGES * C::STAGE_BYTES);
+    const uint32_t bars = staging + STAGING_BYTES;
+    // barrier map (8 bytes each): full[s], empty[s], acc_full[2], acc_empty[2]; then the TMEM slot
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+    auto accf_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + b); };
+    auto acce_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + 2 + b); };
+    const uint32_t slot = bars + 8u * (2 * C::STAGES + 4);
+    volatile uint32_t *slot_ptr = reinterpret_cast<volatile uint32_t *>(base_ptr + C::STAGES * C::STAGE_BYTES + STAGING_BYTES + 8 * (2 * C::STAGES + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nkb = (int)((p.K + BK - 1) / BK);
+    const int ntiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1 + 128); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 128); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(slot) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *slot_ptr;
+
+    pdl_wait();   // activations, scales and row sums come from the preceding kernel
+
+    if (warp == 0) {
+        // ---------------- TMA producer (A tiles)
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % p.tiles_m) * BM;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % C::STAGES;
+                    const uint32_t ph = (it / C::STAGES) & 1u;
+                    if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, 0x101))) break;
+                    mbar_arrive_expect_tx(full_bar(s), A_BYTES);
+                    tma_load_2d(base + s * C::STAGE_BYTES, &tmap_a, kb * BK, m0, full_bar(s));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0, t = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
+                const uint32_t buf = t & 1u, aph = (t >> 1) & 1u;
+                if (!(ok = mbar_wait(acce_bar(buf), aph ^ 1u, 0x201))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * 256u;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % C::STAGES;
+                    const uint32_t ph = (it / C::STAGES) & 1u;
+                    if (!(ok = mbar_wait(full_bar(s), ph, 0x202))) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = base + s * C::STAGE_BYTES;
+                    const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(a_addr + A_BYTES);
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4)   // 32 bytes of K per MMA: descriptor start + 2 (16-byte units)
+                        umma_i8(d_tmem, adesc + 2u * k4, bdesc + 2u * k4, C::IDESC, (kb | k4) != 0);
+                    umma_commit(empty_bar(s));
+                }
+                if (ok) umma_commit(accf_bar(buf));
+            }
+        }
+    } else if (warp >= 8) {
+        // ---------------- unpack warps (B tiles)
+        constexpr int PER = BN * 2 / 128;            // uint4 loads per thread per stage
+        const int u = threadIdx.x - 256;
+        const int64_t row_bytes = p.K >> 2;
+        const int kbytes = (int)row_bytes;
+        auto load_block = [&](int tile, int kb, uint4 (&dst)[PER]) {
+            const int64_t n0 = (int64_t)(tile / p.tiles_m) * BN;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int idx = i * 128 + u, row = idx >> 1, half = idx & 1;
+                const int kb_off = kb * 32 + half * 16;
+                const bool valid = (n0 + row < p.N) && (kb_off < kbytes);
+                dst[i] = valid ? __ldg(reinterpret_cast<const uint4 *>(p.w + (n0 + row) * row_bytes + kb_off))
+                               : make_uint4(0, 0, 0, 0);
+            }
+        };
+        uint4 cur[PER], nxt[PER];
+        int tile = blockIdx.x, kb = 0;
+        if (tile < ntiles) load_block(tile, 0, cur);
+        uint32_t it = 0;
+        bool ok = true;
+        while (tile < ntiles && ok) {
+            int ntile = tile, nkbi = kb + 1;
+            if (nkbi == nkb) { nkbi = 0; ntile = tile + gridDim.x; }
+            if (ntile < ntiles) load_block(ntile, nkbi, nxt);
+            const int s = it % C::STAGES;
+            const uint32_t ph = (it / C::STAGES) & 1u;
+            if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, 0x301))) break;
+            uint8_t *bst = base_ptr + s * C::STAGE_BYTES + A_BYTES;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int idx = i * 128 + u, row = idx >> 1, half = idx & 1;
+                const uint32_t ww[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
+                uint8_t *rowp = bst + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t w = ww[j];
+                    uint4 v;
+                    v.x = (w >> 6) & 0x03030303u; v.y = (w >> 4) & 0x03030303u;
+                    v.z = (w >> 2) & 0x03030303u; v.w = w & 0x03030303u;
+                    const int c = half * 4 + j;
+                    *reinterpret_cast<uint4 *>(rowp + ((c ^ (row & 7)) << 4)) = v;
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(full_bar(s));
+#pragma unroll
+            for (int i = 0; i < PER; ++i) cur[i] = nxt[i];
+            ++it;
+            tile = ntile; kb = nkbi;
+        }
+    } else if (warp >= 4) {
+        // ---------------- epilogue warps (TMEM -> registers -> shared patch -> global)
+        const int q = warp & 3;                       // TMEM lane quadrant of this warp
+        float *patch = staging_ptr + q * 32 * STAGE_PAD;
+        uint32_t t = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
+            const uint32_t buf = t & 1u, aph = (t >> 1) & 1u;
+            const int64_t m0 = (int64_t)(tile % p.tiles_m) * BM, n0 = (int64_t)(tile / p.tiles_m) * BN;
+            const int64_t my_m = m0 + q * 32 + lane;
+            const bool m_ok = my_m < p.M;
+            const float s127 = m_ok ? __fdiv_rn(p.scale[my_m], 127.0f) : 0.0f;
+            const int rsum = m_ok ? p.rowsum[my_m] : 0;
+            if (!(ok = mbar_wait(accf_bar(buf), aph, 0x401))) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c * 32, r);
+                if (c == BN / 32 - 1) {              // last read of this accumulator: hand it back
+                    tc_fence_before();
+                    mbar_arrive(acce_bar(buf));
+                }
+                if (n0 + c * 32 >= p.N) continue;    // warp-uniform
+                const int64_t ncol = n0 + c * 32 + (lane & 7) * 4;
+                if (p.acc_out) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        int4 v = make_int4((int)r[4 * j] - rsum, (int)r[4 * j + 1] - rsum, (int)r[4 * j + 2] - rsum, (int)r[4 * j + 3] - rsum);
+                        *reinterpret_cast<int4 *>(patch + lane * STAGE_PAD + 4 * j) = v;
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rl = 4 * i + (lane >> 3);
+                        const int64_t m = m0 + q * 32 + rl;
+                        const int4 v = *reinterpret_cast<const int4 *>(patch + rl * STAGE_PAD + (lane & 7) * 4);
+                        if (m < p.M && ncol < p.N) *reinterpret_cast<int4 *>(p.acc_out + m * p.N + ncol) = v;
+                    }
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float4 v;
+                    v.x = __fmul_rn(__fmul_rn(s127, __int2float_rn((int)r[4 * j + 0] - rsum)), p.weight_scale);
+                    v.y = __fmul_rn(__fmul_rn(s127, __int2float_rn((int)r[4 * j + 1] - rsum)), p.weight_scale);
+                    v.z = __fmul_rn(__fmul_rn(s127, __int2float_rn((int)r[4 * j + 2] - rsum)), p.weight_scale);
+                    v.w = __fmul_rn(__fmul_rn(s127, __int2float_rn((int)r[4 * j + 3] - rsum)), p.weight_scale);
+                    *reinterpret_cast<float4 *>(patch + lane * STAGE_PAD + 4 * j) = v;
+                }
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int rl = 4 * i + (lane >> 3);
+                    const int64_t m = m0 + q * 32 + rl;
+                    float4 v = *reinterpret_cast<const float4 *>(patch + rl * STAGE_PAD + (lane & 7) * 4);
+                    if (m < p.M && ncol < p.N) {
+                        const int64_t o = m * p.N + ncol;
+                        if (p.bias) {
+                            const float4 b = *reinterpret_cast<const float4 *>(p.bias + ncol);
+                            v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y); v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
+                        }
+                        if (p.residual) {
+                            const float4 b = *reinterpret_cast<const float4 *>(p.residual + o);
+                            v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y); v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
+                        }
+                        if (p.y_dtype == NSLQ_DTYPE_F32) {
+                            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.y) + o) = v;
+                        } else if (p.y_dtype == NSLQ_DTYPE_BF16) {
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                            uint2 pk = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+                            *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(p.y) + o) = pk;
+                        } else {
+                            __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+                            uint2 pk = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+                            *reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(p.y) + o) = pk;
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    }
+    // ---------------- teardown: every thread arrives here, on success and after an expired wait
+    pdl_launch_dependents();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    }
+}
+
+}  // namespace gemm
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+static int sm_count()
+{
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    }
+    return n;
+}
+
+// The tensor-core path needs whole 16-byte vectors everywhere: K % 64 == 0 (packed
+// rows and TMA strides), N % 4 == 0 (vector stores) and aligned base pointers.
+bool ternary_gemm_supported(const void *w, const void *q_perm, int64_t M, int64_t N, int64_t K)
+{
+    return (K % 64 == 0) && (N % 4 == 0) && aligned16(w) && aligned16(q_perm) && M > 0 && M < (1ll << 31) &&
+           N < (1ll << 31) && K < (1ll << 31);
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap &tmap, gemm::Params &p, cudaStream_t st)
+{
+    using C = gemm::Cfg<BN>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(gemm::ternary_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
+            return fail(NSLQ_ERR_CUDA, "ternary_gemm_kernel: cannot reserve %d bytes of shared memory: %s", C::SMEM,
+                        cudaGetErrorString(cudaGetLastError()));
+        attr_set = true;
+    }
+    p.tiles_m = (int)((p.M + gemm::BM - 1) / gemm::BM);
+    p.tiles_n = (int)((p.N + BN - 1) / BN);
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    gemm::ternary_gemm_kernel<BN><<<grid, gemm::THREADS, C::SMEM, st>>>(tmap, p);
+    return check_launch("ternary_gemm_kernel");
+}
+
+int ternary_gemm_dispatch(const uint8_t *w, const int8_t *q_perm, const float *scale, const int32_t *rowsum, int64_t M,
+                          int64_t N, int64_t K, float weight_scale, void *y, int y_dtype, int32_t *acc_out,
+                          const float *bias, const float *residual, cudaStream_t st)
+{
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return fail(NSLQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    if ((acc_out && !aligned16(acc_out)) || !aligned16(y) || (bias && !aligned16(bias)) || (residual && !aligned16(residual)))
+        return fail(NSLQ_ERR_ARG, "BitLinear GEMM: y, acc_out, bias and residual must be 16-byte aligned");
+    CUtensorMap tmap;
+    const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t gstride[1] = {(cuuint64_t)K};
+    const cuuint32_t box[2] = {(cuuint32_t)gemm::BK, (cuuint32_t)gemm::BM};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)q_perm, gdim, gstride, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(NSLQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for M=%lld K=%lld", (int)r, (long long)M, (long long)K);
+    gemm::Params p{w, scale, rowsum, y, acc_out, bias, residual, M, N, K, y_dtype, weight_scale, 0, 0};
+    // Tile width: the one that wastes fewer SM-rounds on this shape.
+    const int sms = sm_count();
+    auto rounds_cost = [&](int bn) {
+        const int64_t tiles = ((M + gemm::BM - 1) / gemm::BM) * ((N + bn - 1) / bn);
+        const int64_t rounds = (tiles + sms - 1) / sms;
+        return (double)rounds * bn;
+    };
+    if (rounds_cost(192) < rounds_cost(256)) return launch_gemm<192>(tmap, p, st);
+    return launch_gemm<256>(tmap, p, st);
+}
+
+// Reads and clears the status word the kernels set when a bounded wait expires.
+int device_status_read(int *out)
+{
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "nslq_device_status: %s", cudaGetErrorString(cudaGetLastError()));
+    if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+    *out = v;
+    return NSLQ_OK;
+}
+
+}  // namespace nslq

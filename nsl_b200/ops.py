@@ -139,6 +139,13 @@ class W4A16:
         return y
 
 
+def device_status():
+    """Nonzero if a bounded wait inside a kernel expired since the last call (then cleared)."""
+    v = C.c_int()
+    check(lib().nslq_device_status(C.byref(v)))
+    return v.value
+
+
 def shard_rows(N, world, rank):
     """(row0, rows) of the output rows rank `rank` owns under column-parallel sharding."""
     r0, n = C.c_int64(), C.c_int64()
