@@ -4,15 +4,17 @@
 //
 // Persistent, warp-specialised kernel, one CTA per SM, 128 x BN output tiles:
 //
-//   warp 0      TMA producer: the int8 activation tile (128 rows x 128 k) is copied
-//               by cp.async.bulk.tensor (2-D, SWIZZLE_128B, no multicast) into a
-//               ring of shared-memory stages.
-//   warps 8-11  unpack: the 2-bit packed weight tile (BN rows x 32 bytes) is read
-//               from global memory one k-block ahead, expanded in registers with
-//               (w >> s) & 0x03030303 -- one 32-bit word of packed bytes becomes
-//               one 16-byte group of u8 codes {0,1,2} -- and written into the same
-//               stage in the K-major 128-byte-swizzled layout the tensor core
-//               reads, then published with fence.proxy.async + mbarrier arrive.
+//   warp 0      TMA producer: per stage, two cp.async.bulk.tensor copies (2-D, no
+//               multicast): the int8 activation tile (128 rows x 128 k,
+//               SWIZZLE_128B) and the still-packed 2-bit weight tile (BN rows x 32
+//               bytes) land in a ring of shared-memory stages; out-of-range rows
+//               and the K tail are zero-filled by the copy engine.
+//   warps 8-11  unpack: read the packed tile from shared memory, expand it in
+//               registers with (w >> s) & 0x03030303 -- one 32-bit word of packed
+//               bytes becomes one 16-byte group of u8 codes {0,1,2} -- and write it
+//               into the same stage in the K-major 128-byte-swizzled layout the
+//               tensor core reads, then publish it with fence.proxy.async +
+//               mbarrier arrive.
 //               The activations are stored in the matching order (position 4i+j of
 //               every 16 holds k = 4j+i), so nothing is permuted here.
 //   warp 1      MMA issuer: one thread issues tcgen05.mma.kind::i8 (M=128, N=BN,
@@ -46,9 +48,10 @@ constexpr int STAGING_BYTES = 4 * 32 * STAGE_PAD * 4;
 constexpr unsigned long long WAIT_NS = 2000000000ull;   // 2 s per wait, then give up
 
 template <int BN> struct Cfg {
-    static constexpr int B_BYTES = BN * BK;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN == 256) ? 4 : 5;
+    static constexpr int B_BYTES = BN * BK;          // unpacked u8 codes
+    static constexpr int P_BYTES = BN * (BK / 4);    // packed 2-bit tile as it sits in global memory
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + P_BYTES;   // multiple of 1024
+    static constexpr int STAGES = (BN == 256) ? 3 : 4;
     static constexpr int SMEM = STAGES * STAGE_BYTES + STAGING_BYTES + 256 + 1024;  // + barriers + alignment slack
     static constexpr uint32_t IDESC = (2u << 4)        // D format: s32
                                       | (1u << 7)      // A format: signed 8-bit
@@ -153,7 +156,7 @@ static __device__ __forceinline__ uint64_t smem_desc(uint32_t addr)
 // ---------------------------------------------------------------- kernel
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
-ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const Params p)
+ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, const Params p)
 {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -163,20 +166,22 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const Params p)
     const uint32_t staging = base + C::STAGES * C::STAGE_BYTES;
     float *staging_ptr = reinterpret_cast<float *>(base_ptr + C::STAGES * C::STAGE_BYTES);
     const uint32_t bars = staging + STAGING_BYTES;
-    // barrier map (8 bytes each): full[s], empty[s], acc_full[2], acc_empty[2]; then the TMEM slot
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
-    auto accf_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + b); };
-    auto acce_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + 2 + b); };
-    const uint32_t slot = bars + 8u * (2 * C::STAGES + 4);
-    volatile uint32_t *slot_ptr = reinterpret_cast<volatile uint32_t *>(base_ptr + C::STAGES * C::STAGE_BYTES + STAGING_BYTES + 8 * (2 * C::STAGES + 4));
+    // barrier map (8 bytes each): raw[s] (TMA bytes landed), full[s] (codes unpacked), empty[s]
+    // (MMAs of the stage retired), acc_full[2], acc_empty[2]; then the TMEM slot
+    auto raw_bar = [&](int s) { return bars + 8u * s; };
+    auto full_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+    auto empty_bar = [&](int s) { return bars + 8u * (2 * C::STAGES + s); };
+    auto accf_bar = [&](int b) { return bars + 8u * (3 * C::STAGES + b); };
+    auto acce_bar = [&](int b) { return bars + 8u * (3 * C::STAGES + 2 + b); };
+    const uint32_t slot = bars + 8u * (3 * C::STAGES + 4);
+    volatile uint32_t *slot_ptr = reinterpret_cast<volatile uint32_t *>(base_ptr + C::STAGES * C::STAGE_BYTES + STAGING_BYTES + 8 * (3 * C::STAGES + 4));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nkb = (int)((p.K + BK - 1) / BK);
     const int ntiles = p.tiles_m * p.tiles_n;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1 + 128); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(raw_bar(s), 1); mbar_init(full_bar(s), 128); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 128); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -192,18 +197,20 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const Params p)
     pdl_wait();   // activations, scales and row sums come from the preceding kernel
 
     if (warp == 0) {
-        // ---------------- TMA producer (A tiles)
+        // ---------------- TMA producer (activation tile + packed weight tile)
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % p.tiles_m) * BM;
+                const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1u;
                     if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, 0x101))) break;
-                    mbar_arrive_expect_tx(full_bar(s), A_BYTES);
-                    tma_load_2d(base + s * C::STAGE_BYTES, &tmap_a, kb * BK, m0, full_bar(s));
+                    const uint32_t st = base + s * C::STAGE_BYTES;
+                    mbar_arrive_expect_tx(raw_bar(s), A_BYTES + C::P_BYTES);
+                    tma_load_2d(st, &tmap_a, kb * BK, m0, raw_bar(s));
+                    tma_load_2d(st + A_BYTES + C::B_BYTES, &tmap_w, kb * (BK / 4), n0, raw_bar(s));
                 }
             }
         }
@@ -220,7 +227,8 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const Params p)
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1u;
-                    if (!(ok = mbar_wait(full_bar(s), ph, 0x202))) break;
+                    if (!(ok = mbar_wait(raw_bar(s), ph, 0x202))) break;    // activation tile landed
+                    if (!(ok = mbar_wait(full_bar(s), ph, 0x203))) break;   // weight codes unpacked
                     tc_fence_after();
                     const uint32_t a_addr = base + s * C::STAGE_BYTES;
                     const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(a_addr + A_BYTES);
@@ -233,56 +241,41 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const Params p)
             }
         }
     } else if (warp >= 8) {
-        // ---------------- unpack warps (B tiles)
-        constexpr int PER = BN * 2 / 128;            // uint4 loads per thread per stage
+        // ---------------- unpack warps (packed tile -> u8 codes, swizzled K-major)
+        constexpr int PER = BN * 2 / 128;            // 16-byte pieces of the packed tile per thread per stage
         const int u = threadIdx.x - 256;
-        const int64_t row_bytes = p.K >> 2;
-        const int kbytes = (int)row_bytes;
-        auto load_block = [&](int tile, int kb, uint4 (&dst)[PER]) {
-            const int64_t n0 = (int64_t)(tile / p.tiles_m) * BN;
-#pragma unroll
-            for (int i = 0; i < PER; ++i) {
-                const int idx = i * 128 + u, row = idx >> 1, half = idx & 1;
-                const int kb_off = kb * 32 + half * 16;
-                const bool valid = (n0 + row < p.N) && (kb_off < kbytes);
-                dst[i] = valid ? __ldg(reinterpret_cast<const uint4 *>(p.w + (n0 + row) * row_bytes + kb_off))
-                               : make_uint4(0, 0, 0, 0);
-            }
-        };
-        uint4 cur[PER], nxt[PER];
-        int tile = blockIdx.x, kb = 0;
-        if (tile < ntiles) load_block(tile, 0, cur);
         uint32_t it = 0;
         bool ok = true;
-        while (tile < ntiles && ok) {
-            int ntile = tile, nkbi = kb + 1;
-            if (nkbi == nkb) { nkbi = 0; ntile = tile + gridDim.x; }
-            if (ntile < ntiles) load_block(ntile, nkbi, nxt);
-            const int s = it % C::STAGES;
-            const uint32_t ph = (it / C::STAGES) & 1u;
-            if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, 0x301))) break;
-            uint8_t *bst = base_ptr + s * C::STAGE_BYTES + A_BYTES;
+        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % C::STAGES;
+                const uint32_t ph = (it / C::STAGES) & 1u;
+                // raw[s] completes only after the producer saw empty[s], so the codes
+                // buffer of this stage is free to overwrite once the packed tile is here.
+                if (!(ok = mbar_wait(raw_bar(s), ph, 0x301))) break;
+                uint8_t *bst = base_ptr + s * C::STAGE_BYTES + A_BYTES;
+                const uint4 *pk = reinterpret_cast<const uint4 *>(bst + C::B_BYTES);
+                uint4 cur[PER];
 #pragma unroll
-            for (int i = 0; i < PER; ++i) {
-                const int idx = i * 128 + u, row = idx >> 1, half = idx & 1;
-                const uint32_t ww[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
-                uint8_t *rowp = bst + (row >> 3) * 1024 + (row & 7) * 128;
+                for (int i = 0; i < PER; ++i) cur[i] = pk[i * 128 + u];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t w = ww[j];
-                    uint4 v;
-                    v.x = (w >> 6) & 0x03030303u; v.y = (w >> 4) & 0x03030303u;
-                    v.z = (w >> 2) & 0x03030303u; v.w = w & 0x03030303u;
-                    const int c = half * 4 + j;
-                    *reinterpret_cast<uint4 *>(rowp + ((c ^ (row & 7)) << 4)) = v;
+                for (int i = 0; i < PER; ++i) {
+                    const int idx = i * 128 + u, row = idx >> 1, half = idx & 1;
+                    const uint32_t ww[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
+                    uint8_t *rowp = bst + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t w = ww[j];
+                        uint4 v;
+                        v.x = (w >> 6) & 0x03030303u; v.y = (w >> 4) & 0x03030303u;
+                        v.z = (w >> 2) & 0x03030303u; v.w = w & 0x03030303u;
+                        const int c = half * 4 + j;
+                        *reinterpret_cast<uint4 *>(rowp + ((c ^ (row & 7)) << 4)) = v;
+                    }
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(full_bar(s));
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(full_bar(s));
-#pragma unroll
-            for (int i = 0; i < PER; ++i) cur[i] = nxt[i];
-            ++it;
-            tile = ntile; kb = nkbi;
         }
     } else if (warp >= 4) {
         // ---------------- epilogue warps (TMEM -> registers -> shared patch -> global)
@@ -417,8 +410,26 @@ bool ternary_gemm_supported(const void *w, const void *q_perm, int64_t M, int64_
            N < (1ll << 31) && K < (1ll << 31);
 }
 
+static int make_map_2d(CUtensorMap *m, const void *ptr, uint64_t inner_bytes, uint64_t rows, uint32_t box_inner,
+                       uint32_t box_rows, CUtensorMapSwizzle swz)
+{
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return fail(NSLQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t gdim[2] = {inner_bytes, rows};
+    const cuuint64_t gstride[1] = {inner_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), gdim, gstride, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(NSLQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for %llu x %llu bytes", (int)r,
+                    (unsigned long long)rows, (unsigned long long)inner_bytes);
+    return NSLQ_OK;
+}
+
 template <int BN>
-static int launch_gemm(const CUtensorMap &tmap, gemm::Params &p, cudaStream_t st)
+static int launch_gemm(const void *q_perm, gemm::Params &p, cudaStream_t st)
 {
     using C = gemm::Cfg<BN>;
     static bool attr_set = false;
@@ -428,11 +439,16 @@ static int launch_gemm(const CUtensorMap &tmap, gemm::Params &p, cudaStream_t st
                         cudaGetErrorString(cudaGetLastError()));
         attr_set = true;
     }
+    CUtensorMap tmap_a, tmap_w;
+    int rc = make_map_2d(&tmap_a, q_perm, (uint64_t)p.K, (uint64_t)p.M, gemm::BK, gemm::BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_map_2d(&tmap_w, p.w, (uint64_t)(p.K / 4), (uint64_t)p.N, gemm::BK / 4, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
     p.tiles_m = (int)((p.M + gemm::BM - 1) / gemm::BM);
     p.tiles_n = (int)((p.N + BN - 1) / BN);
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    gemm::ternary_gemm_kernel<BN><<<grid, gemm::THREADS, C::SMEM, st>>>(tmap, p);
+    gemm::ternary_gemm_kernel<BN><<<grid, gemm::THREADS, C::SMEM, st>>>(tmap_a, tmap_w, p);
     return check_launch("ternary_gemm_kernel");
 }
 
@@ -440,19 +456,8 @@ int ternary_gemm_dispatch(const uint8_t *w, const int8_t *q_perm, const float *s
                           int64_t N, int64_t K, float weight_scale, void *y, int y_dtype, int32_t *acc_out,
                           const float *bias, const float *residual, cudaStream_t st)
 {
-    EncodeTiledFn enc = encode_tiled();
-    if (!enc) return fail(NSLQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     if ((acc_out && !aligned16(acc_out)) || !aligned16(y) || (bias && !aligned16(bias)) || (residual && !aligned16(residual)))
         return fail(NSLQ_ERR_ARG, "BitLinear GEMM: y, acc_out, bias and residual must be 16-byte aligned");
-    CUtensorMap tmap;
-    const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
-    const cuuint64_t gstride[1] = {(cuuint64_t)K};
-    const cuuint32_t box[2] = {(cuuint32_t)gemm::BK, (cuuint32_t)gemm::BM};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)q_perm, gdim, gstride, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(NSLQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for M=%lld K=%lld", (int)r, (long long)M, (long long)K);
     gemm::Params p{w, scale, rowsum, y, acc_out, bias, residual, M, N, K, y_dtype, weight_scale, 0, 0};
     // Tile width: the one that wastes fewer SM-rounds on this shape.
     const int sms = sm_count();
@@ -461,8 +466,8 @@ int ternary_gemm_dispatch(const uint8_t *w, const int8_t *q_perm, const float *s
         const int64_t rounds = (tiles + sms - 1) / sms;
         return (double)rounds * bn;
     };
-    if (rounds_cost(192) < rounds_cost(256)) return launch_gemm<192>(tmap, p, st);
-    return launch_gemm<256>(tmap, p, st);
+    if (rounds_cost(192) < rounds_cost(256)) return launch_gemm<192>(q_perm, p, st);
+    return launch_gemm<256>(q_perm, p, st);
 }
 
 // Reads and clears the status word the kernels set when a bounded wait expires.
