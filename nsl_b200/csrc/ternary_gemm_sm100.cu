@@ -9,7 +9,9 @@
 //               SWIZZLE_128B) and the still-packed 2-bit weight tile (BN rows x 32
 //               bytes) land in a ring of shared-memory stages; out-of-range rows
 //               and the K tail are zero-filled by the copy engine.
-//   warps 8-11  unpack: read the packed tile from shared memory, expand it in
+//   warps 8-15  unpack (two groups of four warps taking alternate stages, so one
+//               group's latency hides behind the other's): read the packed tile
+//               from shared memory, expand it in
 //               registers with (w >> s) & 0x03030303 -- one 32-bit word of packed
 //               bytes becomes one 16-byte group of u8 codes {0,1,2} -- and write it
 //               into the same stage in the K-major 128-byte-swizzled layout the
@@ -41,7 +43,7 @@ namespace gemm {
 
 constexpr int BM = 128;
 constexpr int BK = 128;                  // bytes of int8 along K per stage = one 128B swizzle row
-constexpr int THREADS = 384;
+constexpr int THREADS = 512;            // 16 warps: 0 TMA, 1 MMA, 4-7 epilogue, 8-15 unpack
 constexpr int A_BYTES = BM * BK;         // 16 KiB
 constexpr int STAGE_PAD = 36;            // floats per staged row (32 + 4: conflict-free 16-byte accesses)
 constexpr int STAGING_BYTES = 4 * 32 * STAGE_PAD * 4;
@@ -243,11 +245,12 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     } else if (warp >= 8) {
         // ---------------- unpack warps (packed tile -> u8 codes, swizzled K-major)
         constexpr int PER = BN * 2 / 128;            // 16-byte pieces of the packed tile per thread per stage
-        const int u = threadIdx.x - 256;
-        uint32_t it = 0;
+        const int u = threadIdx.x & 127;
+        const int group = (warp - 8) >> 2;           // group 0 takes even pipeline iterations, group 1 odd
         bool ok = true;
-        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int total_it = ((ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) * nkb;
+        for (int it = group; it < total_it && ok; it += 2) {
+            {
                 const int s = it % C::STAGES;
                 const uint32_t ph = (it / C::STAGES) & 1u;
                 // raw[s] completes only after the producer saw empty[s], so the codes
