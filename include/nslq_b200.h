@@ -131,6 +131,36 @@ int nslq_bitlinear_forward_quantized(const nslq_bitlinear_t *w, const int8_t *q_
                                      void *y, int y_dtype, int32_t *acc_out,
                                      const float *bias, const float *residual, void *stream);
 
+/*
+ * nslq_bitlinear_forward without a caller workspace.  (No counterpart in NSL: the
+ * reference has no GPU entry point for this path at all.)
+ *
+ * For hosts that cannot give the library device memory of their own accord: NSL's
+ * runtime routes every device allocation through its caching allocator and frees
+ * on its own schedule, so a plug-in has no buffer it may hold on to; a decode loop
+ * that must not stall cannot call cudaMalloc, which synchronises the whole device;
+ * a library loaded after the device was fully reserved has nothing left to ask
+ * for.  The scratch (quantised activations, scales, row sums) lives instead in a
+ * fixed area of nslq_noalloc_scratch_bytes() = 512 KiB inside the library's device
+ * image -- every GPU that loads the library carries it until the process ends --
+ * and this call allocates nothing, on the host or the device.
+ *
+ *  - Sizes: nslq_bitlinear_workspace_bytes(M, K) must fit the area (e.g. 16 tokens
+ *    of width 16384, or 128 of width 3200); larger requests return
+ *    NSLQ_ERR_WORKSPACE and say so.  No bias / residual / accumulator outputs.
+ *  - The first call on each device looks up the area's device address (with that
+ *    device current).  Make that first call before any stream capture begins.
+ *  - All calls on a device share the one area, and it keeps the previous call's
+ *    bytes.  Nothing needs clearing (each call overwrites what it reads), but two
+ *    calls whose kernels can overlap on the GPU -- different streams, or different
+ *    host threads on different streams -- race on it: keep them on one stream or
+ *    order them yourself.
+ *  - Results are identical to nslq_bitlinear_forward on the same inputs.
+ */
+int     nslq_bitlinear_forward_noalloc(const nslq_bitlinear_t *w, const void *x, int x_dtype, int64_t M,
+                                       void *y, int y_dtype, void *stream);
+int64_t nslq_noalloc_scratch_bytes(void);
+
 /* ========================================================================== */
 /* W4A16 (uint4 group-quantised weights, 16-bit activations)                   */
 /* ========================================================================== */

@@ -21,6 +21,8 @@ SIGNATURES = {
     "nslq_bitlinear_workspace_bytes": (i64, [i64, i64]),
     "nslq_bitlinear_forward": (i32, [vp, vp, i32, i64, vp, i32, vp, vp, vp, vp, i64, vp]),
     "nslq_bitlinear_forward_quantized": (i32, [vp, vp, vp, vp, i64, vp, i32, vp, vp, vp, vp]),
+    "nslq_bitlinear_forward_noalloc": (i32, [vp, vp, i32, i64, vp, i32, vp]),
+    "nslq_noalloc_scratch_bytes": (i64, []),
     "nslq_w4a16_create_nk": (i32, [vp, vp, i32, vp, i32, i64, i64, i64, C.POINTER(vp)]),
     "nslq_w4a16_create_awq_kn": (i32, [vp, vp, vp, i64, i64, i64, C.POINTER(vp)]),
     "nslq_w4a16_destroy": (None, [vp]),

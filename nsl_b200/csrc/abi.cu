@@ -56,12 +56,6 @@ static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * 
 
 using namespace nslq;
 
-struct nslq_bitlinear {
-    const uint8_t *packed;
-    int64_t N, K;
-    float weight_scale;
-};
-
 struct nslq_w4a16 {
     const uint8_t *codes;   // [N][K/2]
     uint8_t *codes_owned;   // non-null when the library made its own copy

@@ -7,6 +7,13 @@
 
 #include "../../include/nslq_b200.h"
 
+// The object behind nslq_bitlinear_t: a borrowed packed weight and its shape.
+struct nslq_bitlinear {
+    const uint8_t *packed;   // [N][K/4], NSL's packed ternary layout
+    int64_t N, K;
+    float weight_scale;
+};
+
 namespace nslq {
 
 // Records the calling thread's last error text and returns `code`.

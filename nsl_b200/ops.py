@@ -92,6 +92,16 @@ class BitLinear:
                                            _ptr(bias), _ptr(residual), _ptr(ws), ws.numel(), _stream()))
         return (y, acc) if return_acc else y
 
+    def forward_noalloc(self, x, out):
+        """nslq_bitlinear_forward_noalloc: the scratch is the library's built-in area, so the
+        call itself allocates nothing (x and out are the caller's)."""
+        _cuda2d(x, "x")
+        if x.shape[1] != self.K or tuple(out.shape) != (x.shape[0], self.N):
+            raise ValueError("shape mismatch")
+        check(lib().nslq_bitlinear_forward_noalloc(self._h, _ptr(x), _tag(x.dtype), x.shape[0], _ptr(out),
+                                                   _tag(out.dtype), _stream()))
+        return out
+
     def forward_quantized(self, qa, out_dtype=torch.float32, return_acc=False, bias=None, residual=None, out=None):
         """qa: the dict act_quant_i8 returns (uses q_perm, scale, rowsum)."""
         M = qa["scale"].shape[0]
