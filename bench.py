@@ -125,8 +125,10 @@ class DecodeGemv(Workload):
     name, unit, dtype = "bitlinear_decode_gemv_m1_n8640_k3200", "GB/s", "int8xint2->int32"
     N, K, M, LAYERS = 8640, 3200, 1, 64
 
-    def __init__(self, torch, ops, rank, world):
+    def __init__(self, torch, ops, rank, world, streams=1):
         self.torch, self.ops, self.rank, self.world = torch, ops, rank, world
+        self.streams = max(1, streams)
+        self.side = [torch.cuda.Stream() for _ in range(self.streams)] if self.streams > 1 else []
         gen = torch.Generator(device="cuda")
         gen.manual_seed(0)
         r0, rows = ops.shard_rows(self.N, world, rank)
@@ -140,13 +142,14 @@ class DecodeGemv(Workload):
         self.x_host = self.x.cpu().pin_memory()
         self.x_stage = torch.empty_like(self.x)
         self.y_local = torch.empty(self.M, rows, device="cuda")
+        self.y_side = [torch.empty(self.M, rows, device="cuda") for _ in self.side]
         self.y_full = torch.empty(world, self.M, rows, device="cuda") if world > 1 else None
         self.y_host = torch.empty(self.M, self.N, dtype=torch.float32).pin_memory()
         self.ws = torch.empty(int(ops.lib().nslq_bitlinear_workspace_bytes(self.M, self.K)), dtype=torch.uint8,
                               device="cuda")
         self.qa = ops.act_quant_i8(self.x, plain=False, perm=True)
         self.bytes_per_call = self.N * self.K // 4 + self.M * self.K * 4 + self.M * self.N * 4
-        self.launches_per_step = 2 * self.LAYERS
+        self.launches_per_step = self.LAYERS          # M <= 4: quantisation is fused into the GEMV kernel
         self.h2d, self.d2h = self.M * self.K * 4, self.M * self.N * 4
 
     def units_per_step(self):
@@ -159,18 +162,33 @@ class DecodeGemv(Workload):
             dist.all_gather_into_tensor(self.y_full, self.y_local)
 
     def step(self):
+        if self.streams > 1 and self.world == 1:
+            # the calls are independent (same x, distinct weights): issue them round-robin on
+            # several streams so that one call's weight stream overlaps another's tail
+            cur = self.torch.cuda.current_stream()
+            for st in self.side:
+                st.wait_stream(cur)
+            for i, layer in enumerate(self.layers):
+                j = i % self.streams
+                with self.torch.cuda.stream(self.side[j]):
+                    layer.forward(self.x, out=self.y_side[j], workspace=self.ws)   # M <= 4: workspace unused
+            for st in self.side:
+                cur.wait_stream(st)
+            return
         for layer in self.layers:
             self.one_call(layer, self.x)
 
-    def kernel_only(self):
-        for layer in self.layers:
-            layer.forward_quantized(self.qa, out=self.y_local)
+    kernel_name = "ternary_gemv_fused_kernel"
 
-    kernel_name = "ternary_gemv_kernel"
+    def kernel_only(self):
+        if self.world == 1:
+            return self.step()                        # the step is that kernel and nothing else
+        for layer in self.layers:                     # the GEMV launches without the all-gather
+            layer.forward(self.x, out=self.y_local, workspace=self.ws)
 
     def kernel_bytes(self):
-        # per launch, this rank's shard
-        return self.rows * self.K // 4 + self.M * self.K + self.M * self.rows * 4
+        # per launch, this rank's shard: packed W + x (fp32) + y (fp32)
+        return self.rows * self.K // 4 + self.M * self.K * 4 + self.M * self.rows * 4
 
     def e2e_step(self, i):
         layer = self.layers[i % self.LAYERS]
@@ -344,9 +362,14 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    from nsl_b200 import ops
+    from nsl_b200 import lib, ops
+    if args.no_pdl:
+        lib().nslq_set_dependent_launch(0)
     peaks = load_peaks()
-    wl = WORKLOADS[args.workload](torch, ops, rank, world)
+    if args.workload == "decode_gemv":
+        wl = DecodeGemv(torch, ops, rank, world, streams=args.streams)
+    else:
+        wl = WORKLOADS[args.workload](torch, ops, rank, world)
 
     use_graph = world == 1 and not args.no_graph
     step = wl.step
@@ -390,7 +413,7 @@ def run_ours(args):
             "metric": METRIC, "value": round(value, 2), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seed 0)",
-            "config": {"workload": wl.name, "cuda_graph": bool(graph), "l2": "inputs larger than L2 per step",
+            "config": {"workload": wl.name, "cuda_graph": bool(graph), "dependent_launch": not args.no_pdl, "streams": getattr(wl, "streams", 1), "l2": "inputs larger than L2 per step",
                        "parallelism": "column-sharded x%d + NCCL all-gather" % world if world > 1 else "single GPU"},
             "e2e": {"value": round(e2e_val, 3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
                     "d2h_bytes_per_step": wl.d2h},
@@ -449,6 +472,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-graph", action="store_true", help="issue launches directly instead of replaying a CUDA graph")
+    ap.add_argument("--streams", type=int, default=1,
+                    help="decode_gemv: issue the independent calls of a step round-robin on this many streams")
+    ap.add_argument("--no-pdl", action="store_true", help="launch kernels without the programmatic-dependent-launch attribute")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -53,6 +53,12 @@ const char *nslq_last_error(void);
  * *status (0 = no wait ever expired) and clears it.  Synchronises the device. */
 int nslq_device_status(int *status);
 
+/* Kernels are launched with the programmatic-dependent-launch attribute, so that
+ * a kernel's weight prefetch overlaps the tail of the kernel before it in the
+ * stream (each kernel waits for its predecessor before touching its inputs or
+ * outputs).  enable = 0 turns the attribute off process-wide; default on. */
+void nslq_set_dependent_launch(int enable);
+
 /* ========================================================================== */
 /* Stage 1: per-token absmax int8 activation quantisation                      */
 /* ========================================================================== */

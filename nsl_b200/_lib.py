@@ -14,6 +14,7 @@ vp, i64, i32, f32 = C.c_void_p, C.c_int64, C.c_int, C.c_float
 SIGNATURES = {
     "nslq_version": (i32, []),
     "nslq_last_error": (C.c_char_p, []),
+    "nslq_set_dependent_launch": (None, [i32]),
     "nslq_device_status": (i32, [C.POINTER(i32)]),
     "nslq_act_quant_i8": (i32, [vp, i32, i64, i64, vp, vp, vp, vp, vp]),
     "nslq_bitlinear_create": (i32, [vp, i64, i64, f32, C.POINTER(vp)]),

@@ -11,6 +11,7 @@
 namespace nslq {
 
 static thread_local char g_err[512] = "";
+int g_use_pdl = 1;
 
 int fail(int code, const char *fmt, ...)
 {
@@ -35,6 +36,9 @@ int ternary_gemv_dispatch(const uint8_t *, const int8_t *, const float *, const 
                           float, void *, int, int32_t *, const float *, const float *, cudaStream_t);
 int ternary_scalar_dispatch(const uint8_t *, const int8_t *, const float *, int64_t, int64_t, int64_t, float,
                             void *, int, int32_t *, const float *, const float *, cudaStream_t);
+bool ternary_gemv_fused_supported(const void *, const void *, int64_t, int64_t);
+int ternary_gemv_fused_dispatch(const uint8_t *, const void *, int, int, int64_t, int64_t, float, void *, int, int32_t *,
+                                const float *, const float *, cudaStream_t);
 bool ternary_gemm_supported(const void *, const void *, int64_t, int64_t, int64_t);
 int ternary_gemm_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int64_t, int64_t,
                           int64_t, float, void *, int, int32_t *, const float *, const float *, cudaStream_t);
@@ -116,6 +120,8 @@ int nslq_version(void) { return 100; }
 
 const char *nslq_last_error(void) { return g_err; }
 
+void nslq_set_dependent_launch(int enable) { g_use_pdl = enable ? 1 : 0; }
+
 int nslq_device_status(int *status)
 {
     if (!status) return fail(NSLQ_ERR_ARG, "nslq_device_status: null output");
@@ -195,6 +201,9 @@ int nslq_bitlinear_forward(const nslq_bitlinear_t *w, const void *x, int x_dtype
     int8_t *q = (int8_t *)workspace;
     float *scale = (float *)((char *)workspace + align_up(M * w->K, 256));
     int32_t *rowsum = (int32_t *)((char *)scale + align_up(M * 4, 256));
+    if (ternary_gemv_fused_supported(w->packed, x, M, w->K) && (x_dtype == NSLQ_DTYPE_F32 || aligned16(x)))
+        return ternary_gemv_fused_dispatch(w->packed, x, x_dtype, (int)M, w->N, w->K, w->weight_scale, y, y_dtype, acc_out,
+                                           bias, residual, st);
     const bool fast = (w->K % 64 == 0) && aligned16(w->packed);
     if (fast) {
         int rc = act_quant_dispatch(x, x_dtype, M, w->K, nullptr, q, scale, rowsum, st);

@@ -14,38 +14,6 @@ namespace nslq {
 
 constexpr int AQ_THREADS = 256;
 
-static __device__ __forceinline__ int quant_one(float x, float inv)
-{
-    float s = __fmul_rn(x, inv);
-    s = (s < -127.0f) ? -127.0f : ((s > 127.0f) ? 127.0f : s);  // NaN passes through
-    float t = truncf(s);
-    if (fabsf(s - t) >= 0.5f) t += copysignf(1.0f, s);           // half away from zero
-    return __float2int_rz(t);                                   // NaN -> 0
-}
-
-template <typename T> struct Vec4;
-template <> struct Vec4<float> {
-    static __device__ __forceinline__ float4 load(const float *row, int64_t v) {
-        return reinterpret_cast<const float4 *>(row)[v];
-    }
-};
-template <> struct Vec4<__half> {
-    static __device__ __forceinline__ float4 load(const __half *row, int64_t v) {
-        uint2 r = reinterpret_cast<const uint2 *>(row)[v];
-        float2 a = __half22float2(*reinterpret_cast<__half2 *>(&r.x));
-        float2 b = __half22float2(*reinterpret_cast<__half2 *>(&r.y));
-        return make_float4(a.x, a.y, b.x, b.y);
-    }
-};
-template <> struct Vec4<__nv_bfloat16> {
-    static __device__ __forceinline__ float4 load(const __nv_bfloat16 *row, int64_t v) {
-        uint2 r = reinterpret_cast<const uint2 *>(row)[v];
-        float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&r.x));
-        float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&r.y));
-        return make_float4(a.x, a.y, b.x, b.y);
-    }
-};
-
 static __device__ __forceinline__ float block_max(float v, float *smem)
 {
 #pragma unroll
@@ -115,20 +83,9 @@ act_quant_kernel(const T *__restrict__ x, int64_t K, int8_t *__restrict__ q_plai
             int q0 = zero_row ? 0 : quant_one(f.x, inv), q1 = zero_row ? 0 : quant_one(f.y, inv);
             int q2 = zero_row ? 0 : quant_one(f.z, inv), q3 = zero_row ? 0 : quant_one(f.w, inv);
             sum += q0 + q1 + q2 + q3;
-            uint32_t w = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) |
-                         ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+            const uint32_t w = pack4_i8(q0, q1, q2, q3);
             if (q_plain) reinterpret_cast<uint32_t *>(q_plain + r * K)[v] = w;
-            if (q_perm) {
-                // lane j of the quad holds k = 4j..4j+3 of a 16-group; output word i
-                // (written by lane i) is byte i of lanes 0..3: a 4x4 byte transpose.
-                const int lane = threadIdx.x & 31, qb = lane & ~3, i = lane & 3;
-                uint32_t w0 = __shfl_sync(mask, w, qb + 0), w1 = __shfl_sync(mask, w, qb + 1);
-                uint32_t w2 = __shfl_sync(mask, w, qb + 2), w3 = __shfl_sync(mask, w, qb + 3);
-                uint32_t lo = __byte_perm(w0, w1, 0x0040 + i * 0x0011);   // (w0.b[i], w1.b[i], -, -)
-                uint32_t hi = __byte_perm(w2, w3, 0x0040 + i * 0x0011);
-                uint32_t o = __byte_perm(lo, hi, 0x5410);
-                reinterpret_cast<uint32_t *>(q_perm + r * K)[v] = o;
-            }
+            if (q_perm) reinterpret_cast<uint32_t *>(q_perm + r * K)[v] = quad_transpose(w, mask);
         }
     } else {
         for (int64_t k = threadIdx.x; k < K; k += AQ_THREADS) {
@@ -154,8 +111,9 @@ static int launch_act_quant(const void *x, int64_t M, int64_t K, int8_t *q_plain
         return fail(NSLQ_ERR_SHAPE, "nslq_act_quant_i8: q_perm needs K %% 16 == 0 and 16-byte aligned buffers (K=%lld)",
                     (long long)K);
     dim3 grid((unsigned)M), block(AQ_THREADS);
-    if (vec) act_quant_kernel<T, true><<<grid, block, 0, st>>>((const T *)x, K, q_plain, q_perm, scale, rowsum);
-    else act_quant_kernel<T, false><<<grid, block, 0, st>>>((const T *)x, K, q_plain, q_perm, scale, rowsum);
+    cudaError_t e = vec ? launch_kernel(act_quant_kernel<T, true>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum)
+                        : launch_kernel(act_quant_kernel<T, false>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "act_quant_kernel: %s", cudaGetErrorString(e));
     return check_launch("act_quant_kernel");
 }
 

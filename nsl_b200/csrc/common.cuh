@@ -58,6 +58,86 @@ static __device__ __forceinline__ float bitlinear_finalize(int acc, float act_sc
 static __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 static __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Per-token absmax int8 quantisation of one value, the reference's arithmetic
+// (crates/nsl-codegen/tests/bitnet_reference_impl.rs:58-70): v = x*inv (inv = 127/scale,
+// IEEE divide), clamp to [-127,127], round half away from zero, saturating cast, NaN -> 0.
+static __device__ __forceinline__ int quant_one(float x, float inv)
+{
+    const float s = __fmul_rn(x, inv);
+    float t = truncf(s);
+    if (fabsf(s - t) >= 0.5f) t += copysignf(1.0f, s);   // half away from zero (false for NaN / inf)
+    // The float clamp of the reference commutes with the rounding: clamping the rounded integer
+    // gives the same value for every input, and the saturating conversion maps +-inf to the
+    // int extremes (then +-127) and NaN to 0, exactly as `clamp(..).round() as i8` does.
+    return max(-127, min(127, __float2int_rz(t)));
+}
+
+// Four consecutive elements of a row as fp32 (vector load; row must be 16-byte aligned for
+// fp32, 8-byte for the 16-bit types).
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float *row, int64_t v) {
+        return reinterpret_cast<const float4 *>(row)[v];
+    }
+};
+template <> struct Vec4<__half> {
+    static __device__ __forceinline__ float4 load(const __half *row, int64_t v) {
+        uint2 r = reinterpret_cast<const uint2 *>(row)[v];
+        float2 a = __half22float2(*reinterpret_cast<__half2 *>(&r.x));
+        float2 b = __half22float2(*reinterpret_cast<__half2 *>(&r.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16 *row, int64_t v) {
+        uint2 r = reinterpret_cast<const uint2 *>(row)[v];
+        float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&r.x));
+        float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&r.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
+
+// Four quantised values of lane j of a quad (k = 4j..4j+3 of a group of 16) -> the word this
+// lane stores in the consumption order (position 4i+j holds k = 4j+i): lane i gets byte i of
+// the four lanes' words, a 4x4 byte transpose across the quad.  `mask` names the
+// participating lanes (whole quads).
+static __device__ __forceinline__ uint32_t quad_transpose(uint32_t w, unsigned mask)
+{
+    const int lane = threadIdx.x & 31, qb = lane & ~3, i = lane & 3;
+    const uint32_t w0 = __shfl_sync(mask, w, qb + 0), w1 = __shfl_sync(mask, w, qb + 1);
+    const uint32_t w2 = __shfl_sync(mask, w, qb + 2), w3 = __shfl_sync(mask, w, qb + 3);
+    const uint32_t lo = __byte_perm(w0, w1, 0x0040 + i * 0x0011);   // (w0.b[i], w1.b[i], -, -)
+    const uint32_t hi = __byte_perm(w2, w3, 0x0040 + i * 0x0011);
+    return __byte_perm(lo, hi, 0x5410);
+}
+
+static __device__ __forceinline__ uint32_t pack4_i8(int q0, int q1, int q2, int q3)
+{
+    return (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
+           ((uint32_t)(q3 & 0xff) << 24);
+}
+
+// Launch with the programmatic-dependent-launch attribute (when enabled): the kernel may be
+// scheduled while the preceding kernel of the stream drains; it must call pdl_wait() before
+// it touches anything that kernel produced or still reads.
+extern int g_use_pdl;
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t st, Args &&...args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // 128-bit streaming load of weights that are read exactly once.
 static __device__ __forceinline__ uint4 ld_stream_u4(const void *p)
 {

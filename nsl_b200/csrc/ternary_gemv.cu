@@ -19,6 +19,11 @@
 //     ((scale/127) * (float)acc) * weight_scale with separately rounded steps
 //     (crates/nsl-codegen/src/bitnet/phases/finalize.rs:39-53).
 //
+// For M <= 4 the activation quantisation is fused in (ternary_gemv_fused_kernel): each
+// CTA issues its weight loads, then -- while they are in flight -- quantises the token
+// rows itself (absmax by warp shuffles, the reference's exact rounding) into shared memory
+// in the consumption order, so a decode-time linear is one launch and one trip to HBM.
+//
 // Also here: a scalar kernel for shapes the streaming kernel cannot take
 // (K % 64 != 0 or unaligned rows); same arithmetic, natural-order activations.
 #include "common.cuh"
@@ -32,6 +37,25 @@ static __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One 64-trit chunk of rows g and g+8 (ra, rb) against the matching 64 int8 activations of
+// one token tile (xq[0..3], consumption order): 8 MMAs, alternating between two accumulators
+// so that consecutive MMAs do not wait on each other.
+static __device__ __forceinline__ void chunk_mma(int (&acc0)[4], int (&acc1)[4], const uint4 &ra, const uint4 &rb,
+                                                 const uint4 (&xq)[4])
+{
+    const uint32_t wwa[4] = {ra.x, ra.y, ra.z, ra.w};
+    const uint32_t wwb[4] = {rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t a_i0 = (wwa[j] >> 6) & 0x03030303u, a_i1 = (wwa[j] >> 4) & 0x03030303u;
+        const uint32_t a_i2 = (wwa[j] >> 2) & 0x03030303u, a_i3 = wwa[j] & 0x03030303u;
+        const uint32_t b_i0 = (wwb[j] >> 6) & 0x03030303u, b_i1 = (wwb[j] >> 4) & 0x03030303u;
+        const uint32_t b_i2 = (wwb[j] >> 2) & 0x03030303u, b_i3 = wwb[j] & 0x03030303u;
+        mma_u8s8(acc0, a_i0, b_i0, a_i1, b_i1, xq[j].x, xq[j].y);
+        mma_u8s8(acc1, a_i2, b_i2, a_i3, b_i3, xq[j].z, xq[j].w);
+    }
 }
 
 struct GemvParams {
@@ -65,11 +89,11 @@ ternary_gemv_kernel(const GemvParams p)
     const uint8_t *wa = p.w + (n0 + g) * row_bytes;
     const uint8_t *wb = p.w + (n0 + g + 8) * row_bytes;
 
-    int acc[NT][4];
+    int acc[NT][4], acc1[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int r = 0; r < 4; ++r) acc[nt][r] = 0;
+        for (int r = 0; r < 4; ++r) { acc[nt][r] = 0; acc1[nt][r] = 0; }
 
     bool waited = false;
     for (int s0 = warp; s0 < nsteps; s0 += KW * UNROLL) {
@@ -82,7 +106,7 @@ ternary_gemv_kernel(const GemvParams p)
             rb[u] = (ok && rowb_ok) ? ld_stream_u4(wb + (int64_t)c * 16) : make_uint4(0, 0, 0, 0);
         }
         // Weights do not depend on the preceding kernel; the activations do.
-        if (!waited) { pdl_wait(); waited = true; }
+        if (!waited) { pdl_launch_dependents(); pdl_wait(); waited = true; }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int c = 4 * (s0 + u * KW) + t;
@@ -97,30 +121,16 @@ ternary_gemv_kernel(const GemvParams p)
                 for (int j = 0; j < 4; ++j)
                     xq[nt][j] = (ok && tok < p.M) ? __ldg(src + j) : make_uint4(0, 0, 0, 0);
             }
-            const uint32_t wwa[4] = {ra[u].x, ra[u].y, ra[u].z, ra[u].w};
-            const uint32_t wwb[4] = {rb[u].x, rb[u].y, rb[u].z, rb[u].w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t a_i0 = (wwa[j] >> 6) & 0x03030303u, a_i1 = (wwa[j] >> 4) & 0x03030303u;
-                const uint32_t a_i2 = (wwa[j] >> 2) & 0x03030303u, a_i3 = wwa[j] & 0x03030303u;
-                const uint32_t b_i0 = (wwb[j] >> 6) & 0x03030303u, b_i1 = (wwb[j] >> 4) & 0x03030303u;
-                const uint32_t b_i2 = (wwb[j] >> 2) & 0x03030303u, b_i3 = wwb[j] & 0x03030303u;
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    const uint32_t x0 = xq[nt][j].x, x1 = xq[nt][j].y, x2 = xq[nt][j].z, x3 = xq[nt][j].w;
-                    mma_u8s8(acc[nt], a_i0, b_i0, a_i1, b_i1, x0, x1);
-                    mma_u8s8(acc[nt], a_i2, b_i2, a_i3, b_i3, x2, x3);
-                }
-            }
+            for (int nt = 0; nt < NT; ++nt) chunk_mma(acc[nt], acc1[nt], ra[u], rb[u], xq[nt]);
         }
     }
     if (!waited) pdl_wait();
-    pdl_launch_dependents();
 
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int r = 0; r < 4; ++r) red[warp][nt][lane][r] = acc[nt][r];
+        for (int r = 0; r < 4; ++r) red[warp][nt][lane][r] = acc[nt][r] + acc1[nt][r];
     __syncthreads();
 
     // One output per thread-iteration; consecutive threads take consecutive rows.
@@ -138,6 +148,170 @@ ternary_gemv_kernel(const GemvParams p)
         if (p.acc_out) p.acc_out[o] = a;
         float v = bitlinear_finalize(a, p.scale[tok], p.weight_scale);
         if (p.bias) v = __fadd_rn(v, p.bias[n0 + row]);
+        if (p.residual) v = __fadd_rn(v, p.residual[o]);
+        store_out(p.y, p.y_dtype, o, v);
+    }
+}
+
+
+struct FusedParams {
+    const uint8_t *w;      // [N][K/4]
+    const void *x;         // [M][K] fp32 / fp16 / bf16
+    void *y;               // [M][N]
+    int32_t *acc_out;      // [M][N] or null
+    const float *bias;     // [N] or null
+    const float *residual; // [M][N] or null
+    int64_t N, K;
+    int M, y_dtype;
+    float weight_scale;
+};
+
+constexpr int FUSED_MAX_M = 4;
+
+// Decode kernel with the activation quantisation fused in (M <= 4).  A CTA owns TPC row tiles
+// of 16 output rows; each tile's K range is split over KW warps (threads = TPC*KW*32).  The
+// token rows are quantised once per CTA, so a wider CTA repeats less of that work.
+// Dynamic shared memory: [M*K int8 activations, consumption order][TPC*KW*32*4 int reduce]
+// [small per-token arrays].
+template <typename T, int KW, int TPC, int UNROLL>
+__global__ void __launch_bounds__(KW * TPC * 32)
+ternary_gemv_fused_kernel(const FusedParams p)
+{
+    constexpr int NW = KW * TPC, NTHR = NW * 32;
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = warp / KW, kw = warp % KW;
+    const int g = lane >> 2, t = lane & 3;
+    int8_t *q_s = reinterpret_cast<int8_t *>(smem);
+    int *red = reinterpret_cast<int *>(smem + (((size_t)p.M * p.K + 15) & ~(size_t)15));
+    float *part_f = reinterpret_cast<float *>(red + NW * 32 * 4);       // [NW][FUSED_MAX_M]
+    int *part_i = reinterpret_cast<int *>(part_f + NW * FUSED_MAX_M);    // [NW][FUSED_MAX_M]
+    float *scale_s = reinterpret_cast<float *>(part_i + NW * FUSED_MAX_M);
+    int *rowsum_s = reinterpret_cast<int *>(scale_s + FUSED_MAX_M);
+
+    const int64_t n0 = ((int64_t)blockIdx.x * TPC + tile) * 16;
+    const int64_t row_bytes = p.K >> 2;
+    const int nchunks = (int)(p.K >> 6);
+    const int nsteps = (nchunks + 3) >> 2;
+    const bool rowa_ok = (n0 + g) < p.N, rowb_ok = (n0 + g + 8) < p.N;
+    const uint8_t *wa = p.w + (n0 + g) * row_bytes;
+    const uint8_t *wb = p.w + (n0 + g + 8) * row_bytes;
+
+    uint4 ra[UNROLL], rb[UNROLL];
+    auto load_batch = [&](int s0) {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int c = 4 * (s0 + u * KW) + t;
+            const bool ok = c < nchunks;
+            ra[u] = (ok && rowa_ok) ? ld_stream_u4(wa + (int64_t)c * 16) : make_uint4(0, 0, 0, 0);
+            rb[u] = (ok && rowb_ok) ? ld_stream_u4(wb + (int64_t)c * 16) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    // Weights never depend on the preceding kernel: get them moving, let the next kernel of
+    // the stream start doing the same, and only then wait for our own inputs.
+    load_batch(kw);
+    pdl_launch_dependents();
+    pdl_wait();
+
+    // ---- quantise the M token rows into shared memory (same arithmetic as act_quant_kernel).
+    // Each thread keeps its share of a row in registers between the absmax pass and the
+    // rounding pass (XV float4 per thread covers K <= XV*4*NTHR; longer rows are re-read).
+    const T *x = reinterpret_cast<const T *>(p.x);
+    const int nvec = (int)(p.K >> 2);
+    constexpr int XV = (NTHR >= 512) ? 4 : 8;
+    for (int m = 0; m < p.M; ++m) {
+        const T *xr = x + (int64_t)m * p.K;
+        float4 xv[XV];
+        float mx = 0.0f;
+#pragma unroll
+        for (int i = 0; i < XV; ++i) {
+            const int v = i * NTHR + threadIdx.x;
+            xv[i] = (v < nvec) ? Vec4<T>::load(xr, v) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < XV; ++i)
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(xv[i].x), fabsf(xv[i].y)), fmaxf(fabsf(xv[i].z), fabsf(xv[i].w))));
+        for (int v = XV * NTHR + threadIdx.x; v < nvec; v += NTHR) {
+            const float4 f = Vec4<T>::load(xr, v);
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) part_f[warp * FUSED_MAX_M + m] = mx;
+        __syncthreads();
+        float scale = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) scale = fmaxf(scale, part_f[w * FUSED_MAX_M + m]);
+        const float inv = __fdiv_rn(127.0f, scale);
+        const bool zero_row = (scale == 0.0f);
+        if (threadIdx.x == 0) scale_s[m] = scale;
+        int sum = 0;
+        uint32_t *q_row = reinterpret_cast<uint32_t *>(q_s + (int64_t)m * p.K);
+        auto quant_store = [&](const float4 &f, int v, unsigned mask) {
+            const int q0 = zero_row ? 0 : quant_one(f.x, inv), q1 = zero_row ? 0 : quant_one(f.y, inv);
+            const int q2 = zero_row ? 0 : quant_one(f.z, inv), q3 = zero_row ? 0 : quant_one(f.w, inv);
+            sum += q0 + q1 + q2 + q3;
+            q_row[v] = quad_transpose(pack4_i8(q0, q1, q2, q3), mask);
+        };
+#pragma unroll
+        for (int i = 0; i < XV; ++i) {
+            const int v = i * NTHR + threadIdx.x;
+            const bool in = v < nvec;
+            const unsigned mask = __ballot_sync(0xffffffffu, in);   // whole quads: K % 64 == 0
+            if (in) quant_store(xv[i], v, mask);
+        }
+        for (int base = XV * NTHR; base < nvec; base += NTHR) {
+            const int v = base + threadIdx.x;
+            const bool in = v < nvec;
+            const unsigned mask = __ballot_sync(0xffffffffu, in);
+            if (in) quant_store(Vec4<T>::load(xr, v), v, mask);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) part_i[warp * FUSED_MAX_M + m] = sum;
+    }
+    __syncthreads();
+    if (threadIdx.x < p.M) {
+        int tot = 0;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) tot += part_i[w * FUSED_MAX_M + threadIdx.x];
+        rowsum_s[threadIdx.x] = tot;
+    }
+
+    // ---- stream K
+    int acc[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0};
+    for (int s0 = kw; s0 < nsteps; s0 += KW * UNROLL) {
+        if (s0 != kw) load_batch(s0);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int c = 4 * (s0 + u * KW) + t;
+            if (4 * (s0 + u * KW) >= nchunks) break;   // warp-uniform
+            uint4 xq[4];
+            const uint4 *src = reinterpret_cast<const uint4 *>(q_s + (int64_t)g * p.K + (int64_t)c * 64);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) xq[j] = (c < nchunks && g < p.M) ? src[j] : make_uint4(0, 0, 0, 0);
+            chunk_mma(acc, acc1, ra[u], rb[u], xq);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) red[(warp * 32 + lane) * 4 + r] = acc[r] + acc1[r];
+    __syncthreads();
+
+    // 16 rows x up to 4 tokens per tile; consecutive threads take consecutive rows
+    for (int e = threadIdx.x; e < TPC * 16 * FUSED_MAX_M; e += NTHR) {
+        const int tl = e / (16 * FUSED_MAX_M), row = e & 15, tok = (e >> 4) & (FUSED_MAX_M - 1);
+        const int64_t n = ((int64_t)blockIdx.x * TPC + tl) * 16 + row;
+        if (tok >= p.M || n >= p.N) continue;
+        const int src_lane = (row & 7) * 4 + (tok >> 1);
+        const int src_reg = ((row >> 3) << 1) | (tok & 1);
+        int a = 0;
+#pragma unroll
+        for (int w = 0; w < KW; ++w) a += red[((tl * KW + w) * 32 + src_lane) * 4 + src_reg];
+        a -= rowsum_s[tok];
+        const int64_t o = (int64_t)tok * p.N + n;
+        if (p.acc_out) p.acc_out[o] = a;
+        float v = bitlinear_finalize(a, scale_s[tok], p.weight_scale);
+        if (p.bias) v = __fadd_rn(v, p.bias[n]);
         if (p.residual) v = __fadd_rn(v, p.residual[o]);
         store_out(p.y, p.y_dtype, o, v);
     }
@@ -177,7 +351,8 @@ template <int KW, int NT>
 static int launch_gemv(const GemvParams &p, cudaStream_t st)
 {
     const unsigned tiles = (unsigned)((p.N + 15) / 16);
-    ternary_gemv_kernel<KW, NT, 4><<<tiles, KW * 32, 0, st>>>(p);
+    cudaError_t e = launch_kernel(ternary_gemv_kernel<KW, NT, 4>, dim3(tiles), dim3(KW * 32), 0, st, p);
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "ternary_gemv_kernel: %s", cudaGetErrorString(e));
     return check_launch("ternary_gemv_kernel");
 }
 
@@ -200,6 +375,58 @@ int ternary_gemv_dispatch(const uint8_t *w, const int8_t *q_perm, const float *s
     return wide ? launch_gemv<8, 2>(p, st) : launch_gemv<4, 2>(p, st);
 }
 
+template <typename T, int KW, int TPC>
+static int launch_fused(const FusedParams &p, cudaStream_t st)
+{
+    constexpr int NW = KW * TPC;
+    const size_t smem = (((size_t)p.M * p.K + 15) & ~(size_t)15) + (size_t)NW * 32 * 4 * 4 + (size_t)NW * FUSED_MAX_M * 8 + FUSED_MAX_M * 8;
+    static size_t reserved = 0;
+    if (smem > 48 * 1024 && smem > reserved) {
+        if (cudaFuncSetAttribute(ternary_gemv_fused_kernel<T, KW, TPC, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return fail(NSLQ_ERR_CUDA, "ternary_gemv_fused_kernel: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(cudaGetLastError()));
+        reserved = smem;
+    }
+    const unsigned ctas = (unsigned)((p.N + 16 * TPC - 1) / (16 * TPC));
+    cudaError_t e = launch_kernel(ternary_gemv_fused_kernel<T, KW, TPC, 4>, dim3(ctas), dim3(NW * 32), smem, st, p);
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "ternary_gemv_fused_kernel: %s", cudaGetErrorString(e));
+    return check_launch("ternary_gemv_fused_kernel");
+}
+
+template <typename T>
+static int pick_fused(const FusedParams &p, cudaStream_t st)
+{
+    const int nsteps = (int)((p.K / 64 + 3) / 4);
+    const bool wide = nsteps > 16;                    // long rows: 8 warps split K
+    const int64_t tiles = (p.N + 15) / 16;
+    // widest CTA that still leaves about one CTA per SM
+    if (!wide) {
+        if (tiles >= 4 * 120) return launch_fused<T, 4, 4>(p, st);
+        if (tiles >= 2 * 120) return launch_fused<T, 4, 2>(p, st);
+        return launch_fused<T, 4, 1>(p, st);
+    }
+    if (tiles >= 2 * 120) return launch_fused<T, 8, 2>(p, st);
+    return launch_fused<T, 8, 1>(p, st);
+}
+
+// x [M][K] in its own dtype, M <= 4, K % 64 == 0, 16-byte aligned x and w, M*K <= 160 KiB.
+bool ternary_gemv_fused_supported(const void *w, const void *x, int64_t M, int64_t K)
+{
+    return M >= 1 && M <= FUSED_MAX_M && (K % 64 == 0) && aligned16(w) && aligned16(x) && M * K <= 160 * 1024;
+}
+
+int ternary_gemv_fused_dispatch(const uint8_t *w, const void *x, int x_dtype, int M, int64_t N, int64_t K,
+                                float weight_scale, void *y, int y_dtype, int32_t *acc_out, const float *bias,
+                                const float *residual, cudaStream_t st)
+{
+    FusedParams p{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale};
+    switch (x_dtype) {
+    case NSLQ_DTYPE_F32: return pick_fused<float>(p, st);
+    case NSLQ_DTYPE_FP16: return pick_fused<__half>(p, st);
+    case NSLQ_DTYPE_BF16: return pick_fused<__nv_bfloat16>(p, st);
+    default: return fail(NSLQ_ERR_ARG, "BitLinear: x_dtype %d not in {F32,FP16,BF16}", x_dtype);
+    }
+}
+
 int ternary_scalar_dispatch(const uint8_t *w, const int8_t *q_plain, const float *scale, int64_t M,
                             int64_t N, int64_t K, float weight_scale, void *y, int y_dtype,
                             int32_t *acc_out, const float *bias, const float *residual,
@@ -207,8 +434,9 @@ int ternary_scalar_dispatch(const uint8_t *w, const int8_t *q_plain, const float
 {
     dim3 grid((unsigned)((N + 127) / 128), (unsigned)M);
     if (M > 65535) return fail(NSLQ_ERR_UNSUPPORTED, "scalar BitLinear kernel: M=%lld > 65535", (long long)M);
-    ternary_scalar_kernel<<<grid, 128, 0, st>>>(w, q_plain, scale, y, acc_out, bias, residual, N, K,
-                                                y_dtype, weight_scale);
+    cudaError_t e = launch_kernel(ternary_scalar_kernel, grid, dim3(128), 0, st, w, q_plain, scale, y, acc_out, bias, residual,
+                                  N, K, y_dtype, weight_scale);
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "ternary_scalar_kernel: %s", cudaGetErrorString(e));
     return check_launch("ternary_scalar_kernel");
 }
 

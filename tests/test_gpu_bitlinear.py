@@ -143,3 +143,54 @@ def test_errors(ops):
     small = torch.empty(256, dtype=torch.uint8, device="cuda")
     with pytest.raises(NslqError):
         layer.forward(torch.zeros(64, 64, device="cuda"), workspace=small)
+
+
+@pytest.mark.parametrize("dt", ["float16", "bfloat16", "float32"])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5])
+def test_fused_decode_kernel_input_dtypes(ops, oracle, dt, M):
+    """M <= 4 runs the kernel with the activation quantisation fused in; it must equal the
+    two-kernel path (M = 5 here) and the oracle for every activation dtype."""
+    rng = np.random.default_rng(400 + M)
+    N, K = 208, 1216
+    x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).to(getattr(torch, dt)).cuda()
+    x_np = x.float().cpu().numpy()
+    trits = rng.integers(-1, 2, size=(N, K)).astype(np.int8)
+    packed = oracle.np_pack_trits_nk(trits)
+    layer = ops.BitLinear(dev(packed), 0.11)
+    y, acc = layer.forward(x, return_acc=True)
+    torch.cuda.synchronize()
+    _, _, acc_ref, y_ref = oracle.bitlinear_forward_packed(x_np, packed, N, 0.11)
+    assert np.array_equal(host(acc), acc_ref) and bits_equal(host(y), y_ref)
+    qa = ops.act_quant_i8(x, plain=False, perm=True)          # the unfused route on the same input
+    assert torch.equal(layer.forward_quantized(qa), y)
+
+
+def test_fused_kernel_adversarial_rows(ops, oracle):
+    K, N = 64, 40
+    rows = [np.zeros(K, np.float32)]
+    r = np.full(K, 127.0, np.float32); r[1:9] = [0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 0.49999997, -0.49999997]; rows.append(r)
+    r = np.linspace(-1, 1, K).astype(np.float32); r[3] = np.nan; rows.append(r)
+    r = np.ones(K, np.float32); r[7] = np.inf; rows.append(r)
+    x = np.stack(rows)
+    rng = np.random.default_rng(8)
+    packed = oracle.np_pack_trits_nk(rng.integers(-1, 2, size=(N, K)).astype(np.int8))
+    y, acc = run(ops, x, packed, 1.0)
+    _, _, acc_ref, y_ref = oracle.bitlinear_forward_packed(x, packed, N, 1.0)
+    assert np.array_equal(acc, acc_ref)
+    assert np.array_equal(np.isnan(y), np.isnan(y_ref)) and bits_equal(np.nan_to_num(y), np.nan_to_num(y_ref))
+
+
+def test_dependent_launch_switch_changes_nothing(ops, oracle):
+    from nsl_b200 import lib
+    rng = np.random.default_rng(12)
+    M, N, K = 6, 320, 1024
+    x = dev(rng.standard_normal((M, K)).astype(np.float32))
+    layer = ops.BitLinear(dev(oracle.np_pack_trits_nk(rng.integers(-1, 2, size=(N, K)).astype(np.int8))), 0.2)
+    try:
+        lib().nslq_set_dependent_launch(0)
+        a = [layer.forward(x) for _ in range(3)][-1].clone()
+    finally:
+        lib().nslq_set_dependent_launch(1)
+    b = [layer.forward(x) for _ in range(3)][-1]
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
