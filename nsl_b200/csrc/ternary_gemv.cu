@@ -9,12 +9,13 @@
 //   * a CTA owns 16 output rows; its warps split K in steps of 256 (4 lanes of a
 //     quad x 64 trits = one uint4 each, for rows g and g+8 of the tile);
 //   * a 32-bit word w of packed bytes b0..b3 yields, for i = 0..3,
-//     (w >> (6-2i)) & 0x03030303 = codes of k = 4j+i for byte j: four u8x4 MMA
-//     operand registers per word, no per-trit work.  The quantised activations
-//     are stored in the matching order (position 4i+j of every 16 holds k = 4j+i),
-//     so registers line up with no shuffles;
-//   * mma.sync.m16n8k32.u8.s8 accumulates sum_k q*code exactly in int32 for up to
-//     8 tokens per MMA; acc = that - rowsum(q) because code = trit + 1;
+//     w & (0x03030303 << (6-2i)) = the codes of k = 4j+i for byte j, times 4^(3-i):
+//     four u8x4 MMA operand registers per word for one AND each, no per-trit work.
+//     The quantised activations are stored in the matching order (position 4i+j of
+//     every 16 holds k = 4j+i), so registers line up with no shuffles;
+//   * mma.sync.m16n8k32.u8.s8 accumulates sum_k q*code*4^(3-i) exactly in int32, one
+//     accumulator per position class i, for up to 8 tokens per MMA; the classes are
+//     shifted back (exact) and summed; acc = that - rowsum(q) because code = trit + 1;
 //   * the K-split partials are reduced through shared memory and finalised as
 //     ((scale/127) * (float)acc) * weight_scale with separately rounded steps
 //     (crates/nsl-codegen/src/bitnet/phases/finalize.rs:39-53).
@@ -39,22 +40,41 @@ static __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Accumulators of one token tile: class i collects the trits in position i of their byte,
+// whose codes are used as they sit in the byte, i.e. scaled by 64, 16, 4, 1.
+struct Acc4 { int v[4][4]; };
+
+static __device__ __forceinline__ void acc_zero(Acc4 &a)
+{
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) a.v[i][r] = 0;
+}
+// sum_k q*code for fragment register r: every class is an exact multiple of its scale.
+static __device__ __forceinline__ int acc_value(const Acc4 &a, int r)
+{
+    return (a.v[0][r] >> 6) + (a.v[1][r] >> 4) + (a.v[2][r] >> 2) + a.v[3][r];
+}
+
 // One 64-trit chunk of rows g and g+8 (ra, rb) against the matching 64 int8 activations of
-// one token tile (xq[0..3], consumption order): 8 MMAs, alternating between two accumulators
-// so that consecutive MMAs do not wait on each other.
-static __device__ __forceinline__ void chunk_mma(int (&acc0)[4], int (&acc1)[4], const uint4 &ra, const uint4 &rb,
-                                                 const uint4 (&xq)[4])
+// one token tile (xq[0..3], consumption order): 8 MMAs.  A packed word w holds trit i of byte
+// j in bits 8j+6-2i; `w & (0x03030303 << (6-2i))` is therefore the four codes of position i,
+// each multiplied by 4^(3-i), still a valid u8 -- one AND per operand register and no shift.
+// An MMA pairs the same position class of two words so that its sum has a single scale.
+static __device__ __forceinline__ void chunk_mma(Acc4 &acc, const uint4 &ra, const uint4 &rb, const uint4 (&xq)[4])
 {
     const uint32_t wwa[4] = {ra.x, ra.y, ra.z, ra.w};
     const uint32_t wwb[4] = {rb.x, rb.y, rb.z, rb.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t a_i0 = (wwa[j] >> 6) & 0x03030303u, a_i1 = (wwa[j] >> 4) & 0x03030303u;
-        const uint32_t a_i2 = (wwa[j] >> 2) & 0x03030303u, a_i3 = wwa[j] & 0x03030303u;
-        const uint32_t b_i0 = (wwb[j] >> 6) & 0x03030303u, b_i1 = (wwb[j] >> 4) & 0x03030303u;
-        const uint32_t b_i2 = (wwb[j] >> 2) & 0x03030303u, b_i3 = wwb[j] & 0x03030303u;
-        mma_u8s8(acc0, a_i0, b_i0, a_i1, b_i1, xq[j].x, xq[j].y);
-        mma_u8s8(acc1, a_i2, b_i2, a_i3, b_i3, xq[j].z, xq[j].w);
+    for (int jp = 0; jp < 4; jp += 2) {
+        const uint32_t x0[4] = {xq[jp].x, xq[jp].y, xq[jp].z, xq[jp].w};
+        const uint32_t x1[4] = {xq[jp + 1].x, xq[jp + 1].y, xq[jp + 1].z, xq[jp + 1].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t mask = 0x03030303u << (6 - 2 * i);
+            mma_u8s8(acc.v[i], wwa[jp] & mask, wwb[jp] & mask, wwa[jp + 1] & mask, wwb[jp + 1] & mask, x0[i], x1[i]);
+        }
     }
 }
 
@@ -89,11 +109,9 @@ ternary_gemv_kernel(const GemvParams p)
     const uint8_t *wa = p.w + (n0 + g) * row_bytes;
     const uint8_t *wb = p.w + (n0 + g + 8) * row_bytes;
 
-    int acc[NT][4], acc1[NT][4];
+    Acc4 acc[NT];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) { acc[nt][r] = 0; acc1[nt][r] = 0; }
+    for (int nt = 0; nt < NT; ++nt) acc_zero(acc[nt]);
 
     bool waited = false;
     for (int s0 = warp; s0 < nsteps; s0 += KW * UNROLL) {
@@ -122,7 +140,7 @@ ternary_gemv_kernel(const GemvParams p)
                     xq[nt][j] = (ok && tok < p.M) ? __ldg(src + j) : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) chunk_mma(acc[nt], acc1[nt], ra[u], rb[u], xq[nt]);
+            for (int nt = 0; nt < NT; ++nt) chunk_mma(acc[nt], ra[u], rb[u], xq[nt]);
         }
     }
     if (!waited) pdl_wait();
@@ -130,7 +148,7 @@ ternary_gemv_kernel(const GemvParams p)
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int r = 0; r < 4; ++r) red[warp][nt][lane][r] = acc[nt][r] + acc1[nt][r];
+        for (int r = 0; r < 4; ++r) red[warp][nt][lane][r] = acc_value(acc[nt], r);
     __syncthreads();
 
     // One output per thread-iteration; consecutive threads take consecutive rows.
@@ -279,7 +297,8 @@ ternary_gemv_fused_kernel(const FusedParams p)
     }
 
     // ---- stream K
-    int acc[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0};
+    Acc4 acc;
+    acc_zero(acc);
     for (int s0 = kw; s0 < nsteps; s0 += KW * UNROLL) {
         if (s0 != kw) load_batch(s0);
 #pragma unroll
@@ -290,11 +309,11 @@ ternary_gemv_fused_kernel(const FusedParams p)
             const uint4 *src = reinterpret_cast<const uint4 *>(q_s + (int64_t)g * p.K + (int64_t)c * 64);
 #pragma unroll
             for (int j = 0; j < 4; ++j) xq[j] = (c < nchunks && g < p.M) ? src[j] : make_uint4(0, 0, 0, 0);
-            chunk_mma(acc, acc1, ra[u], rb[u], xq);
+            chunk_mma(acc, ra[u], rb[u], xq);
         }
     }
 #pragma unroll
-    for (int r = 0; r < 4; ++r) red[(warp * 32 + lane) * 4 + r] = acc[r] + acc1[r];
+    for (int r = 0; r < 4; ++r) red[(warp * 32 + lane) * 4 + r] = acc_value(acc, r);
     __syncthreads();
 
     // 16 rows x up to 4 tokens per tile; consecutive threads take consecutive rows
@@ -375,19 +394,19 @@ int ternary_gemv_dispatch(const uint8_t *w, const int8_t *q_perm, const float *s
     return wide ? launch_gemv<8, 2>(p, st) : launch_gemv<4, 2>(p, st);
 }
 
-template <typename T, int KW, int TPC>
+template <typename T, int KW, int TPC, int UNROLL = 4>
 static int launch_fused(const FusedParams &p, cudaStream_t st)
 {
     constexpr int NW = KW * TPC;
     const size_t smem = (((size_t)p.M * p.K + 15) & ~(size_t)15) + (size_t)NW * 32 * 4 * 4 + (size_t)NW * FUSED_MAX_M * 8 + FUSED_MAX_M * 8;
     static size_t reserved = 0;
     if (smem > 48 * 1024 && smem > reserved) {
-        if (cudaFuncSetAttribute(ternary_gemv_fused_kernel<T, KW, TPC, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(ternary_gemv_fused_kernel<T, KW, TPC, UNROLL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return fail(NSLQ_ERR_CUDA, "ternary_gemv_fused_kernel: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(cudaGetLastError()));
         reserved = smem;
     }
     const unsigned ctas = (unsigned)((p.N + 16 * TPC - 1) / (16 * TPC));
-    cudaError_t e = launch_kernel(ternary_gemv_fused_kernel<T, KW, TPC, 4>, dim3(ctas), dim3(NW * 32), smem, st, p);
+    cudaError_t e = launch_kernel(ternary_gemv_fused_kernel<T, KW, TPC, UNROLL>, dim3(ctas), dim3(NW * 32), smem, st, p);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "ternary_gemv_fused_kernel: %s", cudaGetErrorString(e));
     return check_launch("ternary_gemv_fused_kernel");
 }
