@@ -42,12 +42,16 @@ int ternary_gemv_fused_dispatch(const uint8_t *, const void *, int, int, int64_t
 bool ternary_gemm_supported(const void *, const void *, int64_t, int64_t, int64_t);
 int ternary_gemm_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int64_t, int64_t,
                           int64_t, float, void *, int, int32_t *, const float *, const float *, cudaStream_t);
-int device_status_read(int *);
+int ternary_gemm_status(int *);
+int w4a16_gemm_status(int *);
 bool w4a16_gemv_supported(const void *, const void *, int, int64_t, int64_t);
 int w4a16_gemv_dispatch(const uint8_t *, const float *, const float *, int64_t, int64_t, int, int, const void *,
                         int, int, void *, int, cudaStream_t);
 int w4a16_scalar_dispatch(const uint8_t *, const float *, const float *, int64_t, int64_t, int, int, const void *,
                           int, int64_t, void *, int, cudaStream_t);
+bool w4a16_gemm_supported(const void *, const void *, int, int, int64_t, int64_t, int64_t, int64_t);
+int w4a16_gemm_dispatch(const uint8_t *, const float *, const float *, int64_t, int64_t, int, int, const void *, int64_t,
+                        void *, int, cudaStream_t);
 
 static inline int out_elem_size(int dt)
 {
@@ -67,6 +71,7 @@ struct nslq_w4a16 {
     float *zc;              // [N][G] owned, zero point in code units
     int64_t N, K;
     int G, gs;
+    int zp_integer;         // zero points are whole numbers (QuantizedTensor form), not AWQ float zeros
 };
 
 // ------------------------------------------------------------------ small table kernels
@@ -127,7 +132,12 @@ int nslq_device_status(int *status)
     if (!status) return fail(NSLQ_ERR_ARG, "nslq_device_status: null output");
     if (cudaDeviceSynchronize() != cudaSuccess)
         return fail(NSLQ_ERR_CUDA, "nslq_device_status: %s", cudaGetErrorString(cudaGetLastError()));
-    return device_status_read(status);
+    int a = 0, b = 0;
+    int rc = ternary_gemm_status(&a);
+    if (rc) return rc;
+    if ((rc = w4a16_gemm_status(&b))) return rc;
+    *status = a ? a : b;
+    return NSLQ_OK;
 }
 
 int nslq_act_quant_i8(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q_plain, int8_t *q_perm,
@@ -241,6 +251,7 @@ int nslq_w4a16_create_nk(const uint8_t *codes, const void *scales, int scale_dty
     nslq_w4a16 *h = (nslq_w4a16 *)calloc(1, sizeof(nslq_w4a16));
     if (!h) return fail(NSLQ_ERR_ARG, "nslq_w4a16_create_nk: out of host memory");
     h->codes = codes; h->N = N; h->K = K; h->gs = (int)group_size; h->G = (int)((K + group_size - 1) / group_size);
+    h->zp_integer = 1;
     if ((rc = w4_alloc_tables(h))) { nslq_w4a16_destroy(h); return rc; }
     const int64_t n = N * h->G;
     const unsigned blocks = (unsigned)((n + 255) / 256);
@@ -300,6 +311,8 @@ int nslq_w4a16_forward(const nslq_w4a16_t *w, const void *x, int x_dtype, int64_
     if (M < 0) return fail(NSLQ_ERR_SHAPE, "nslq_w4a16_forward: M=%lld", (long long)M);
     if (M == 0) return NSLQ_OK;
     cudaStream_t st = (cudaStream_t)stream;
+    if (M > 16 && w4a16_gemm_supported(w->codes, x, x_dtype, w->zp_integer, M, w->N, w->K, w->gs))
+        return w4a16_gemm_dispatch(w->codes, w->scale, w->zc, w->N, w->K, w->G, w->gs, x, M, y, y_dtype, st);
     if (w4a16_gemv_supported(w->codes, x, x_dtype, w->K, w->gs)) {
         for (int64_t m0 = 0; m0 < M; m0 += 16) {
             const int mc = (int)((M - m0) < 16 ? (M - m0) : 16);

@@ -31,15 +31,13 @@
 // Every mbarrier wait is bounded in time; on expiry the kernel records a status
 // word (read with nslq_device_status) and falls through to the common teardown,
 // which frees its TMEM.  No spin is unbounded.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "sm100_common.cuh"
 
 namespace nslq {
 
-__device__ int g_device_status = 0;   // 0 = ok; else (role << 8 | site) of the first wait that expired
-
 namespace gemm {
+
+using namespace sm100;
 
 constexpr int BM = 128;
 constexpr int BK = 128;                  // bytes of int8 along K per stage = one 128B swizzle row
@@ -47,7 +45,6 @@ constexpr int THREADS = 512;            // 16 warps: 0 TMA, 1 MMA, 4-7 epilogue,
 constexpr int A_BYTES = BM * BK;         // 16 KiB
 constexpr int STAGE_PAD = 36;            // floats per staged row (32 + 4: conflict-free 16-byte accesses)
 constexpr int STAGING_BYTES = 4 * 32 * STAGE_PAD * 4;
-constexpr unsigned long long WAIT_NS = 2000000000ull;   // 2 s per wait, then give up
 
 template <int BN> struct Cfg {
     static constexpr int B_BYTES = BN * BK;          // unpacked u8 codes
@@ -74,86 +71,6 @@ struct Params {
     float weight_scale;
     int tiles_m, tiles_n;
 };
-
-// ---------------------------------------------------------------- PTX wrappers
-static __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-static __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-static __device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-static __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-static __device__ __forceinline__ unsigned long long globaltimer_ns()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait: true when the phase completed, false after WAIT_NS (status word set).
-static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int site)
-{
-    unsigned long long t0 = 0;
-    for (uint32_t spin = 0;; ++spin) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((spin & 63u) == 63u) {
-            const unsigned long long now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_NS) { atomicCAS(&g_device_status, 0, site); return false; }
-        }
-    }
-}
-static __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tmap, int x, int y, uint32_t bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-static __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-static __device__ __forceinline__ void umma_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-static __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-static __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-static __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// K-major, 128-byte swizzle: 8-row groups 1024 B apart (SBO), LBO unused (=1), version 1.
-static __device__ __forceinline__ uint64_t smem_desc(uint32_t addr)
-{
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
 
 // ---------------------------------------------------------------- kernel
 template <int BN>
@@ -377,58 +294,12 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 }  // namespace gemm
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled()
-{
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
-static int sm_count()
-{
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    }
-    return n;
-}
-
 // The tensor-core path needs whole 16-byte vectors everywhere: K % 64 == 0 (packed
 // rows and TMA strides), N % 4 == 0 (vector stores) and aligned base pointers.
 bool ternary_gemm_supported(const void *w, const void *q_perm, int64_t M, int64_t N, int64_t K)
 {
     return (K % 64 == 0) && (N % 4 == 0) && aligned16(w) && aligned16(q_perm) && M > 0 && M < (1ll << 31) &&
            N < (1ll << 31) && K < (1ll << 31);
-}
-
-static int make_map_2d(CUtensorMap *m, const void *ptr, uint64_t inner_bytes, uint64_t rows, uint32_t box_inner,
-                       uint32_t box_rows, CUtensorMapSwizzle swz)
-{
-    EncodeTiledFn enc = encode_tiled();
-    if (!enc) return fail(NSLQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    const cuuint64_t gdim[2] = {inner_bytes, rows};
-    const cuuint64_t gstride[1] = {inner_bytes};
-    const cuuint32_t box[2] = {box_inner, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), gdim, gstride, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS)
-        return fail(NSLQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for %llu x %llu bytes", (int)r,
-                    (unsigned long long)rows, (unsigned long long)inner_bytes);
-    return NSLQ_OK;
 }
 
 template <int BN>
@@ -443,14 +314,14 @@ static int launch_gemm(const void *q_perm, gemm::Params &p, cudaStream_t st)
         attr_set = true;
     }
     CUtensorMap tmap_a, tmap_w;
-    int rc = make_map_2d(&tmap_a, q_perm, (uint64_t)p.K, (uint64_t)p.M, gemm::BK, gemm::BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    int rc = sm100::make_map_2d(&tmap_a, q_perm, (uint64_t)p.K, (uint64_t)p.M, gemm::BK, gemm::BM, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    rc = make_map_2d(&tmap_w, p.w, (uint64_t)(p.K / 4), (uint64_t)p.N, gemm::BK / 4, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
+    rc = sm100::make_map_2d(&tmap_w, p.w, (uint64_t)(p.K / 4), (uint64_t)p.N, gemm::BK / 4, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     p.tiles_m = (int)((p.M + gemm::BM - 1) / gemm::BM);
     p.tiles_n = (int)((p.N + BN - 1) / BN);
     const int tiles = p.tiles_m * p.tiles_n;
-    const int grid = tiles < sm_count() ? tiles : sm_count();
+    const int grid = tiles < sm100::sm_count() ? tiles : sm100::sm_count();
     gemm::ternary_gemm_kernel<BN><<<grid, gemm::THREADS, C::SMEM, st>>>(tmap_a, tmap_w, p);
     return check_launch("ternary_gemm_kernel");
 }
@@ -463,7 +334,7 @@ int ternary_gemm_dispatch(const uint8_t *w, const int8_t *q_perm, const float *s
         return fail(NSLQ_ERR_ARG, "BitLinear GEMM: y, acc_out, bias and residual must be 16-byte aligned");
     gemm::Params p{w, scale, rowsum, y, acc_out, bias, residual, M, N, K, y_dtype, weight_scale, 0, 0};
     // Tile width: the one that wastes fewer SM-rounds on this shape.
-    const int sms = sm_count();
+    const int sms = sm100::sm_count();
     auto rounds_cost = [&](int bn) {
         const int64_t tiles = ((M + gemm::BM - 1) / gemm::BM) * ((N + bn - 1) / bn);
         const int64_t rounds = (tiles + sms - 1) / sms;
@@ -473,15 +344,7 @@ int ternary_gemm_dispatch(const uint8_t *w, const int8_t *q_perm, const float *s
     return launch_gemm<256>(q_perm, p, st);
 }
 
-// Reads and clears the status word the kernels set when a bounded wait expires.
-int device_status_read(int *out)
-{
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess)
-        return fail(NSLQ_ERR_CUDA, "nslq_device_status: %s", cudaGetErrorString(cudaGetLastError()));
-    if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
-    *out = v;
-    return NSLQ_OK;
-}
+// The status word of this translation unit's kernels (see sm100::read_wait_status).
+int ternary_gemm_status(int *out) { return sm100::read_wait_status(out); }
 
 }  // namespace nslq
