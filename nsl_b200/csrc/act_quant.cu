@@ -1,8 +1,8 @@
 // Stage 1: per-token absmax int8 activation quantisation.
 //
-// One CTA per token row.  Pass 1 reduces max|x| with warp shuffles (then across
-// warps through shared memory); pass 2 re-reads the row (it is still in L1/L2),
-// quantises with the reference's exact arithmetic and writes the int8 row in the
+// One CTA per token row.  The row is read once into registers; max|x| is reduced
+// with warp shuffles (then across warps through shared memory); the row is then
+// quantised from registers with the reference's exact arithmetic and written in the
 // natural order and/or the order the matmul kernels consume, plus scale and sum.
 //
 // Arithmetic follows crates/nsl-codegen/tests/bitnet_reference_impl.rs:46-70 of
@@ -43,7 +43,7 @@ static __device__ __forceinline__ int block_sum(int v, int *smem)
 
 // VEC = true: K % 16 == 0 and 16-byte aligned rows; four elements per thread per
 // iteration, quads of lanes cover one group of 16 k (needed for q_perm).
-template <typename T, bool VEC>
+template <typename T, bool VEC, int XV>
 __global__ void __launch_bounds__(AQ_THREADS)
 act_quant_kernel(const T *__restrict__ x, int64_t K, int8_t *__restrict__ q_plain,
                  int8_t *__restrict__ q_perm, float *__restrict__ scale_out,
@@ -55,10 +55,24 @@ act_quant_kernel(const T *__restrict__ x, int64_t K, int8_t *__restrict__ q_plai
     const T *row = x + r * K;
     pdl_wait();
 
+    // VEC path: the thread's share of the row stays in registers between the absmax pass and
+    // the rounding pass (XV float4 per thread: K <= XV*4*AQ_THREADS; longer rows re-read the
+    // tail, which is still in L1/L2).  XV is 4 or 12: short rows keep registers low so that more
+    // rows are in flight per SM.
+    const int nvec = VEC ? (int)(K >> 2) : 0;
+    float4 xv[VEC ? XV : 1];
     float m = 0.0f;
     if (VEC) {
-        for (int64_t v = threadIdx.x; v < K / 4; v += AQ_THREADS) {
-            float4 f = Vec4<T>::load(row, v);
+#pragma unroll
+        for (int i = 0; i < XV; ++i) {
+            const int v = i * AQ_THREADS + threadIdx.x;
+            xv[i] = (v < nvec) ? Vec4<T>::load(row, v) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < XV; ++i)
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(xv[i].x), fabsf(xv[i].y)), fmaxf(fabsf(xv[i].z), fabsf(xv[i].w))));
+        for (int v = XV * AQ_THREADS + threadIdx.x; v < nvec; v += AQ_THREADS) {
+            const float4 f = Vec4<T>::load(row, v);
             m = fmaxf(m, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
         }
     } else {
@@ -71,21 +85,28 @@ act_quant_kernel(const T *__restrict__ x, int64_t K, int8_t *__restrict__ q_plai
 
     int sum = 0;
     if (VEC) {
-        // K/4 is a multiple of 4 and AQ_THREADS is a multiple of 4, so the four
-        // lanes of a quad are always inside the row together.
-        for (int64_t base = 0; base < K / 4; base += AQ_THREADS) {
-            const int64_t v = base + threadIdx.x;
-            const bool in = v < K / 4;
-            // lanes that are inside the row (whole quads); the shuffles below name exactly these
-            const unsigned mask = __ballot_sync(0xffffffffu, in);
-            if (!in) continue;
-            float4 f = Vec4<T>::load(row, v);
-            int q0 = zero_row ? 0 : quant_one(f.x, inv), q1 = zero_row ? 0 : quant_one(f.y, inv);
-            int q2 = zero_row ? 0 : quant_one(f.z, inv), q3 = zero_row ? 0 : quant_one(f.w, inv);
+        // K/4 is a multiple of 4 and AQ_THREADS is a multiple of 4, so the four lanes of a quad
+        // are always inside the row together; `mask` names exactly the lanes inside.
+        auto quant_store = [&](const float4 &f, int v, unsigned mask) {
+            const int q0 = zero_row ? 0 : quant_one(f.x, inv), q1 = zero_row ? 0 : quant_one(f.y, inv);
+            const int q2 = zero_row ? 0 : quant_one(f.z, inv), q3 = zero_row ? 0 : quant_one(f.w, inv);
             sum += q0 + q1 + q2 + q3;
             const uint32_t w = pack4_i8(q0, q1, q2, q3);
             if (q_plain) reinterpret_cast<uint32_t *>(q_plain + r * K)[v] = w;
             if (q_perm) reinterpret_cast<uint32_t *>(q_perm + r * K)[v] = quad_transpose(w, mask);
+        };
+#pragma unroll
+        for (int i = 0; i < XV; ++i) {
+            const int v = i * AQ_THREADS + threadIdx.x;
+            const bool in = v < nvec;
+            const unsigned mask = __ballot_sync(0xffffffffu, in);
+            if (in) quant_store(xv[i], v, mask);
+        }
+        for (int base = XV * AQ_THREADS; base < nvec; base += AQ_THREADS) {
+            const int v = base + threadIdx.x;
+            const bool in = v < nvec;
+            const unsigned mask = __ballot_sync(0xffffffffu, in);
+            if (in) quant_store(Vec4<T>::load(row, v), v, mask);
         }
     } else {
         for (int64_t k = threadIdx.x; k < K; k += AQ_THREADS) {
@@ -111,8 +132,10 @@ static int launch_act_quant(const void *x, int64_t M, int64_t K, int8_t *q_plain
         return fail(NSLQ_ERR_SHAPE, "nslq_act_quant_i8: q_perm needs K %% 16 == 0 and 16-byte aligned buffers (K=%lld)",
                     (long long)K);
     dim3 grid((unsigned)M), block(AQ_THREADS);
-    cudaError_t e = vec ? launch_kernel(act_quant_kernel<T, true>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum)
-                        : launch_kernel(act_quant_kernel<T, false>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
+    cudaError_t e;
+    if (!vec) e = launch_kernel(act_quant_kernel<T, false, 1>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
+    else if (K <= 4 * 4 * AQ_THREADS) e = launch_kernel(act_quant_kernel<T, true, 4>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
+    else e = launch_kernel(act_quant_kernel<T, true, 12>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "act_quant_kernel: %s", cudaGetErrorString(e));
     return check_launch("act_quant_kernel");
 }

@@ -296,19 +296,24 @@ ternary_gemv_fused_kernel(const FusedParams p)
         rowsum_s[threadIdx.x] = tot;
     }
 
-    // ---- stream K
+    // ---- stream K.  A lane whose token does not exist reads a block of zeros with stride 0, so
+    // the loop has no selects; a chunk index past the row only meets zero weights.
+    uint4 *zero_blk = reinterpret_cast<uint4 *>(rowsum_s + FUSED_MAX_M);
+    if (threadIdx.x < 4) zero_blk[threadIdx.x] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    const uint4 *qrow = (g < p.M) ? reinterpret_cast<const uint4 *>(q_s + (size_t)g * p.K) + t * 4 : zero_blk;
+    const int qstride = (g < p.M) ? 16 : 0;
     Acc4 acc;
     acc_zero(acc);
     for (int s0 = kw; s0 < nsteps; s0 += KW * UNROLL) {
         if (s0 != kw) load_batch(s0);
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int c = 4 * (s0 + u * KW) + t;
-            if (4 * (s0 + u * KW) >= nchunks) break;   // warp-uniform
+            const int sidx = s0 + u * KW;
+            if (4 * sidx >= nchunks) break;   // warp-uniform
             uint4 xq[4];
-            const uint4 *src = reinterpret_cast<const uint4 *>(q_s + (int64_t)g * p.K + (int64_t)c * 64);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) xq[j] = (c < nchunks && g < p.M) ? src[j] : make_uint4(0, 0, 0, 0);
+            for (int j = 0; j < 4; ++j) xq[j] = qrow[sidx * qstride + j];
             chunk_mma(acc, ra[u], rb[u], xq);
         }
     }
@@ -398,7 +403,7 @@ template <typename T, int KW, int TPC, int UNROLL = 4>
 static int launch_fused(const FusedParams &p, cudaStream_t st)
 {
     constexpr int NW = KW * TPC;
-    const size_t smem = (((size_t)p.M * p.K + 15) & ~(size_t)15) + (size_t)NW * 32 * 4 * 4 + (size_t)NW * FUSED_MAX_M * 8 + FUSED_MAX_M * 8;
+    const size_t smem = (((size_t)p.M * p.K + 15) & ~(size_t)15) + (size_t)NW * 32 * 4 * 4 + (size_t)NW * FUSED_MAX_M * 8 + FUSED_MAX_M * 8 + 64;
     static size_t reserved = 0;
     if (smem > 48 * 1024 && smem > reserved) {
         if (cudaFuncSetAttribute(ternary_gemv_fused_kernel<T, KW, TPC, UNROLL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
