@@ -14,8 +14,12 @@ configurations):
   w4a16_m1 / w4a16_m16 / w4a16_m256
                 W4A16, N=11008, K=4096, group 128; one step = 24 (M=1,16) or 8 (M=256) calls over
                 distinct weights (> L2); GB/s for M=1,16, TFLOPS for M=256.
+  bitnet3b_b1 / _b8 / _b64
+                BitNet b1.58-3B-shaped decoder (26 layers, hidden 3200, FFN 8640, vocab 32002), random
+                ternary weights, 512-token prompt, 256 greedy decode steps in one CUDA graph; every
+                projection through the C ABI, the rest PyTorch; value in decode tok/s.
 One JSON line is printed by rank 0; at N=1 the default run appends the other workloads' figures
-under "also".  With --gpus N > 1 (launched by torchrun) the weights are column-sharded over the
+under "also" and the decoder's under "decoder".  With --gpus N > 1 (launched by torchrun) the weights are column-sharded over the
 ranks, x is replicated and each output is all-gathered with NCCL: total work is fixed ("strong").
 
 --impl reference times the reference's CPU arithmetic for the same workload (the C restatement
@@ -464,9 +468,66 @@ def cpu_arm(key, threads, budget_s):
     return W4A16.cpu_baseline_m(int(key[7:]), threads, budget_s)
 
 
-WORKLOAD_KEYS = ["prefill_gemm", "decode_gemv", "w4a16_m1", "w4a16_m4", "w4a16_m8", "w4a16_m16", "w4a16_m256"]
+WORKLOAD_KEYS = ["prefill_gemm", "decode_gemv", "w4a16_m1", "w4a16_m4", "w4a16_m8", "w4a16_m16", "w4a16_m256",
+                 "bitnet3b_b1", "bitnet3b_b8", "bitnet3b_b64"]
 DEFAULT_WORKLOAD = "prefill_gemm"
 META = {"prefill_gemm": PrefillGemm, "decode_gemv": DecodeGemv}
+
+
+# ----------------------------------------------------------------------------- decoder workload
+def run_decoder(torch, batch, peaks, prompt=512, steps=256, warm=8):
+    """BitNet b1.58-3B-shaped decoder (configs[3]): random ternary weights, uniform-random prompt ids,
+    greedy decode.  Returns decode / prefill tokens per second and the HBM figures of a decode step."""
+    from nsl_b200 import decoder
+    cfg = decoder.BitNetConfig()
+    model = decoder.BitNetDecoder(cfg, batch, prompt + steps + warm + 8)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0)
+    ids_host = torch.randint(0, cfg.vocab, (batch, prompt), generator=torch.Generator().manual_seed(0)).pin_memory()
+    ids = ids_host.cuda()
+    model.prefill(ids)                                   # warm-up (lazy initialisation, workspaces)
+    torch.cuda.synchronize()
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    e0.record()
+    model.prefill(ids)
+    e1.record()
+    torch.cuda.synchronize()
+    prefill_ms = e0.elapsed_time(e1)
+    model.capture()
+    model.decode(warm)
+    torch.cuda.synchronize()
+    e1.record()
+    model.decode(steps)
+    e2.record()
+    torch.cuda.synchronize()
+    dec_ms = e1.elapsed_time(e2)
+    step_ms = dec_ms / steps
+    ctx_mid = prompt + warm + steps // 2
+    step_bytes = model.step_bytes(ctx_mid)
+    ach = step_bytes / (step_ms * 1e-3) / 1e9
+    # host to host: prompt ids from pinned memory, prefill, then every step's tokens read back
+    tok_host = torch.empty(batch, dtype=torch.long).pin_memory()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ids2 = ids_host.cuda(non_blocking=True)
+    model.prefill(ids2)
+    for _ in range(steps):
+        model.graph.replay()
+        tok_host.copy_(model.tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e2e_s = time.perf_counter() - t0
+    out = {"workload": "bitnet_b158_3b_decoder_b%d_prompt%d_decode%d" % (batch, prompt, steps),
+           "decode_tok_s": round(batch * steps / (dec_ms * 1e-3), 1), "ms_per_decode_step": round(step_ms, 4),
+           "prefill_tok_s": round(batch * prompt / (prefill_ms * 1e-3), 1), "prefill_ms": round(prefill_ms, 2),
+           "e2e_tok_s": round(batch * (steps) / e2e_s, 1),
+           "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": round(ach / peaks["hbm_gbs"], 4), "bytes_per_step": step_bytes,
+                        "note": "ternary weights + bf16 lm_head + KV read at mid-run context; attention, norms, "
+                                "RoPE and sampling are PyTorch"},
+           "ceiling_tok_s": round(batch / (step_bytes / (peaks["hbm_gbs"] * 1e9)), 1)}
+    del model
+    torch.cuda.empty_cache()
+    return out
 
 
 # ----------------------------------------------------------------------------- measurement
@@ -524,6 +585,12 @@ def run_ours(args):
     peaks = load_peaks()
     use_graph = not args.no_graph            # NCCL collectives are captured into the graph as well
 
+    if args.workload.startswith("bitnet3b_b"):
+        out = run_decoder(torch, int(args.workload[10:]), peaks)
+        out.update({"metric": METRIC, "value": out["decode_tok_s"], "unit": "tok/s", "n_gpus": 1,
+                    "higher_is_better": True, "data": "synthetic (seed 0)", "dtype": "int8 x int2 -> int32"})
+        print(json.dumps(out))
+        return
     wl = make_workload(args.workload, torch, ops, rank, world, streams=args.streams)
     sampler = ClockSampler(local) if rank == 0 else None
     m = measure(torch, wl, args.steps, args.warmup, use_graph, dist, sampler)
@@ -562,6 +629,7 @@ def run_ours(args):
             del w2
             torch.cuda.empty_cache()
         line["also"] = also
+        line["decoder"] = [run_decoder(torch, b, peaks) for b in (1, 8, 64)]
     if rank == 0:
         line["device_status"] = status
         print(json.dumps(line))

@@ -1,0 +1,166 @@
+"""Decoder harness for the model-shaped workloads of the benchmark (BitNet b1.58-3B shape).
+
+Everything that is NOT a quantized linear -- embedding, RMSNorm, RoPE, attention over the KV
+cache, greedy sampling, the bf16 lm_head -- is plain PyTorch, on purpose: those pieces are outside
+the quantized-linear path this library replaces (NSL has them in stdlib/nsl/nn/{norms,rope,gqa}.nsl
+and stdlib/nsl/inference/generate.nsl).  Every projection of every layer (q, k, v, o, gate, up,
+down) runs through nsl_b200.ops.BitLinear, i.e. the C ABI.  Weights are random ternary (no
+checkpoint is available offline), so the numbers are throughput numbers, not quality numbers.
+
+One decode step is captured in a single CUDA graph: the position and the current tokens live in
+device tensors that the graph itself advances, so 256 steps are 256 replays.
+"""
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import ops
+
+
+class BitNetConfig:
+    def __init__(self, layers=26, hidden=3200, heads=32, head_dim=100, ffn=8640, vocab=32002, rope_theta=10000.0,
+                 eps=1e-5):
+        self.layers, self.hidden, self.heads, self.head_dim = layers, hidden, heads, head_dim
+        self.ffn, self.vocab, self.rope_theta, self.eps = ffn, vocab, rope_theta, eps
+
+    def ternary_bytes_per_layer(self):
+        return (4 * self.hidden * self.hidden + 3 * self.hidden * self.ffn) // 4
+
+
+def _ternary(n, k, gen):
+    c = torch.randint(0, 3, (n, k // 4, 4), device="cuda", dtype=torch.uint8, generator=gen)
+    return ((c[..., 0] << 6) | (c[..., 1] << 4) | (c[..., 2] << 2) | c[..., 3]).contiguous()
+
+
+def _rms_norm(x, w, eps):
+    return F.rms_norm(x.float(), (x.shape[-1],), w, eps).to(x.dtype)
+
+
+def _rope(x, cos, sin):
+    """x [B, H, T, D]; cos/sin [T, D/2] (rotate-half convention)."""
+    d = x.shape[-1] // 2
+    x1, x2 = x[..., :d].float(), x[..., d:].float()
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1).to(x.dtype)
+
+
+class BitNetDecoder:
+    """Random-init decoder of the given shape; act dtype bf16, KV cache bf16."""
+
+    def __init__(self, cfg, batch, max_ctx, seed=0):
+        self.cfg, self.B, self.max_ctx = cfg, batch, max_ctx
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(seed)
+        h, f, hd = cfg.hidden, cfg.ffn, cfg.heads * cfg.head_dim
+        dt = torch.bfloat16
+        self.embed = (torch.randn(cfg.vocab, h, device="cuda", generator=gen) * 0.02).to(dt)
+        self.lm_head = (torch.randn(cfg.vocab, h, device="cuda", generator=gen) * 0.02).to(dt)
+        self.final_norm = torch.ones(h, device="cuda")
+        self.layers = []
+        for _ in range(cfg.layers):
+            L = {"n1": torch.ones(h, device="cuda"), "n2": torch.ones(h, device="cuda")}
+            for name, (n, k) in {"q": (hd, h), "k": (hd, h), "v": (hd, h), "o": (h, hd), "gate": (f, h), "up": (f, h),
+                                 "down": (h, f)}.items():
+                L[name] = ops.BitLinear(_ternary(n, k, gen), 1.0 / math.sqrt(k))
+            self.layers.append(L)
+        half = cfg.head_dim // 2
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(half, device="cuda").float() / half))
+        ang = torch.arange(max_ctx, device="cuda").float()[:, None] * inv[None, :]
+        self.cos, self.sin = ang.cos(), ang.sin()
+        self.k_cache = torch.zeros(cfg.layers, batch, cfg.heads, max_ctx, cfg.head_dim, device="cuda", dtype=dt)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        self.pos = torch.zeros(1, device="cuda", dtype=torch.long)       # next position to write
+        self.tokens = torch.zeros(batch, device="cuda", dtype=torch.long)
+        self.key_index = torch.arange(max_ctx, device="cuda")
+        self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.graph = None
+
+    # ------------------------------------------------------------------ linears through the C ABI
+    def _lin(self, layer, x2d):
+        return layer.forward(x2d, out_dtype=torch.bfloat16)
+
+    def _lin_shared(self, layers, x2d):
+        """Several projections of one input: quantise once when the rows go down the two-kernel path."""
+        M = x2d.shape[0]
+        if M <= 4:          # decode kernel with the quantisation fused in: one launch per projection
+            return [l.forward(x2d, out_dtype=torch.bfloat16) for l in layers]
+        qa = ops.act_quant_i8(x2d, plain=False, perm=True)
+        return [l.forward_quantized(qa, out_dtype=torch.bfloat16) for l in layers]
+
+    # ------------------------------------------------------------------ prefill
+    def prefill(self, ids):
+        """ids [B, T]; fills the KV cache, leaves pos = T and tokens = greedy next token."""
+        cfg, B, T = self.cfg, ids.shape[0], ids.shape[1]
+        x = self.embed[ids]                                               # [B, T, h]
+        cos, sin = self.cos[:T], self.sin[:T]
+        for li, L in enumerate(self.layers):
+            hn = _rms_norm(x, L["n1"], cfg.eps).reshape(B * T, cfg.hidden)
+            q, k, v = self._lin_shared([L["q"], L["k"], L["v"]], hn)
+            q = _rope(q.view(B, T, cfg.heads, cfg.head_dim).transpose(1, 2), cos, sin)
+            k = _rope(k.view(B, T, cfg.heads, cfg.head_dim).transpose(1, 2), cos, sin)
+            v = v.view(B, T, cfg.heads, cfg.head_dim).transpose(1, 2)
+            self.k_cache[li, :, :, :T] = k
+            self.v_cache[li, :, :, :T] = v
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+            a = a.transpose(1, 2).reshape(B * T, cfg.heads * cfg.head_dim)
+            x = x + self._lin(L["o"], a).view(B, T, cfg.hidden)
+            hn = _rms_norm(x, L["n2"], cfg.eps).reshape(B * T, cfg.hidden)
+            g, u = self._lin_shared([L["gate"], L["up"]], hn)
+            x = x + self._lin(L["down"], (F.silu(g.float()) * u.float()).to(torch.bfloat16)).view(B, T, cfg.hidden)
+        last = _rms_norm(x[:, -1], self.final_norm, cfg.eps)
+        self.tokens.copy_((last @ self.lm_head.t()).argmax(-1))
+        self.pos.fill_(T)
+
+    # ------------------------------------------------------------------ one decode step (graph-capturable)
+    def _step(self):
+        cfg, B = self.cfg, self.B
+        x = self.embed[self.tokens]                                       # [B, h]
+        cos, sin = self.cos[self.pos], self.sin[self.pos]                 # [1, D/2]
+        mask = (self.key_index <= self.pos).view(1, 1, 1, self.max_ctx)   # keys 0..pos are visible
+        for li, L in enumerate(self.layers):
+            hn = _rms_norm(x, L["n1"], cfg.eps)
+            q, k, v = self._lin_shared([L["q"], L["k"], L["v"]], hn)
+            q = _rope(q.view(B, cfg.heads, 1, cfg.head_dim), cos, sin)
+            k = _rope(k.view(B, cfg.heads, 1, cfg.head_dim), cos, sin)
+            self.k_cache[li].index_copy_(2, self.pos, k)
+            self.v_cache[li].index_copy_(2, self.pos, v.view(B, cfg.heads, 1, cfg.head_dim))
+            # single-query attention as two batched matmuls on the cache in place (no copies of K/V)
+            sc = torch.matmul(q, self.k_cache[li].transpose(-1, -2)).float() * self.sm_scale
+            pr = torch.softmax(sc.masked_fill(~mask, float("-inf")), -1).to(torch.bfloat16)
+            a = torch.matmul(pr, self.v_cache[li])
+            x = x + self._lin(L["o"], a.reshape(B, cfg.heads * cfg.head_dim))
+            hn = _rms_norm(x, L["n2"], cfg.eps)
+            g, u = self._lin_shared([L["gate"], L["up"]], hn)
+            x = x + self._lin(L["down"], (F.silu(g.float()) * u.float()).to(torch.bfloat16))
+        logits = _rms_norm(x, self.final_norm, cfg.eps) @ self.lm_head.t()
+        self.tokens.copy_(logits.argmax(-1))
+        self.pos.add_(1)
+
+    def capture(self):
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        keep_pos, keep_tok = self.pos.clone(), self.tokens.clone()
+        with torch.cuda.stream(s):
+            self._step()                      # warm-up outside the graph (allocations, lazy init)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self.pos.copy_(keep_pos)
+        self.tokens.copy_(keep_tok)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._step()
+        self.pos.copy_(keep_pos)
+        self.tokens.copy_(keep_tok)
+
+    def decode(self, steps):
+        if self.graph is None:
+            self.capture()
+        for _ in range(steps):
+            self.graph.replay()
+
+    def step_bytes(self, ctx):
+        """Algorithmic HBM bytes of one decode step at context length ctx."""
+        cfg = self.cfg
+        w = cfg.layers * cfg.ternary_bytes_per_layer() + cfg.vocab * cfg.hidden * 2
+        kv = self.B * cfg.layers * 2 * ctx * cfg.heads * cfg.head_dim * 2
+        return w + kv
