@@ -1,0 +1,95 @@
+/*
+ * nsl_shims.h -- entry points with NSL's own calling convention (i64 handles that are raw
+ * pointers to NSL's #[repr(C)] structs), forwarding to the CUDA kernels of libnslq_b200.
+ *
+ * These are what the Rust runtime would call from the GPU arm of its existing functions; the
+ * struct mirrors below are checked against NSL's field order with static_asserts in
+ * nsl_b200/csrc/nsl_shims.cu.  Differences from the CPU originals, all forced by ownership
+ * (docs/abi/README.md:100-113 of NSL: tensors are allocated and freed by the Rust allocator):
+ * the result tensor is passed in by the caller (`out`), already allocated on the device with
+ * shape [M,N] and dtype f32, instead of being returned; on success the functions return `out`.
+ */
+#ifndef NSL_SHIMS_H
+#define NSL_SHIMS_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* crates/nsl-runtime/src/tensor/mod.rs:202-224 */
+typedef struct NslTensor {
+    uint32_t magic;        /* 0x4E534C54 "NSLT" when live */
+    void    *data;         /* device pointer when device > 0 */
+    int64_t *shape;        /* host */
+    int64_t *strides;      /* host */
+    int64_t  ndim;
+    int64_t  len;
+    int64_t  refcount;
+    uint8_t  device;       /* 0 = CPU, 1+ = CUDA device id (1-based) */
+    uint16_t dtype;        /* 0 f64, 1 f32, 2 fp16, 3 bf16, 4 int8, 9 i32 */
+    uint8_t  owns_data;
+    int64_t  data_owner;
+    uint8_t  slab_managed;
+    int64_t  tape_id;
+} NslTensor;
+
+/* crates/nsl-runtime/src/quantize.rs:27-51 (buffers in host memory, as the reference allocates them) */
+typedef struct NslQuantizedTensor {
+    uint8_t *data;
+    float   *scale;
+    uint8_t *zero_point;
+    int64_t *shape;
+    int64_t  ndim;
+    int64_t  dtype;        /* 0 = INT8, 1 = INT4 */
+    int64_t  granularity;  /* 0 tensor, 1 channel, 2 group */
+    int64_t  gran_axis;
+    int64_t  group_size;
+    int64_t  num_scales;
+    int64_t  refcount;
+} NslQuantizedTensor;
+
+/* crates/nsl-runtime/src/awq.rs:29-45 (buffers in host memory) */
+typedef struct NslAwqPackedWeight {
+    uint8_t *data;
+    double  *scales;
+    double  *zeros;
+    int64_t  k, n, group_size, num_groups;
+    int64_t  refcount;
+} NslAwqPackedWeight;
+
+/*
+ * GPU arm of nsl_awq_matmul (crates/nsl-runtime/src/awq.rs:261-310): input [M,K] on the device
+ * (f32, fp16 or bf16), packed = NslAwqPackedWeight* (host buffers; uploaded and re-laid out once,
+ * cached by pointer).  Null pointers: message on stderr and 0, like the original.
+ */
+int64_t nsl_awq_matmul_cuda(int64_t input, int64_t packed, int64_t group_size, int64_t out);
+/* GPU arm of nsl_gptq_matmul (crates/nsl-runtime/src/gptq.rs:646-653): same computation. */
+int64_t nsl_gptq_matmul_cuda(int64_t input, int64_t packed, int64_t group_size, int64_t bits, int64_t out);
+
+/*
+ * GPU arm of nsl_qtensor_matmul_mixed (crates/nsl-runtime/src/quantize.rs:547-585): x [...,K] on
+ * the device @ dequantize(qw [K,N]); every dtype/granularity the original accepts.  Like the
+ * original it prints and aborts when qw is not 2-D or the inner dimensions differ.
+ */
+int64_t nsl_qtensor_matmul_mixed_cuda(int64_t x, int64_t qw, int64_t out);
+
+/* Drops the device copy cached for a weight (call from nsl_awq_free / nsl_qtensor_free). */
+void nsl_quant_forget_cuda(int64_t weight);
+
+/*
+ * BitLinear: NSL has no runtime entry point for it (crates/nsl-codegen/tests/bitnet_logit_match.rs:44-52),
+ * so this trio is new.  pack: `packed_bytes` = LoadedTernaryWeight.packed_bytes in HOST memory
+ * ([out_dim][hidden_dim/4], crates/nsl-codegen/src/bitnet/loader.rs:47-56), uploaded once; returns a
+ * handle or 0.  forward: x [M,hidden] on the device (f32/fp16/bf16), out [M,out_dim] on the device
+ * (f32/fp16/bf16); returns out or 0.
+ */
+int64_t nsl_bitlinear_pack(int64_t packed_bytes, int64_t out_dim, int64_t hidden_dim, double weight_scale);
+int64_t nsl_bitlinear_forward(int64_t handle, int64_t x, int64_t out);
+void    nsl_bitlinear_free(int64_t handle);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NSL_SHIMS_H */

@@ -207,6 +207,42 @@ int nslq_w4a16_forward(const nslq_w4a16_t *w, const void *x, int x_dtype, int64_
                        void *y, int y_dtype, void *stream);
 
 /* ========================================================================== */
+/* Pack-at-load: the reference's weight quantisers, on the GPU                 */
+/* ========================================================================== */
+/*
+ * quantize_float_to_ternary (crates/nsl-codegen/src/bitnet/loader.rs:126-193):
+ * scale = (sum |w|, added sequentially in f32) / numel; trit = round_half_away(
+ * clamp(w / (scale > 0 ? scale : 1), -1, 1)); four trits per byte, HIGH-BITS-FIRST.
+ * The sum keeps the reference's order (one thread adds), so `packed` and `*scale`
+ * are the reference's bytes.  w: numel elements (F32 / FP16 / BF16), numel % 4 == 0
+ * (the reference's AlignmentError otherwise); packed: numel/4 bytes; scale: one
+ * float in device memory (it is the weight_scale of nslq_bitlinear_create).
+ */
+int nslq_ternary_quantize_pack(const void *w, int w_dtype, int64_t numel, uint8_t *packed, float *scale,
+                               void *stream);
+
+/*
+ * nsl_qtensor_quantize for INT4, per-group along axis 1 of a [N,K] tensor
+ * (crates/nsl-runtime/src/quantize.rs:224-266, :366-417): f64 arithmetic, scale =
+ * (max-min)/15 (stored f32), zp = round(-min/scale) clamped, q = round(x/scale+zp)
+ * clamped; the constant-group branch of compute_scale_zp included.  Outputs are what
+ * nslq_w4a16_create_nk takes: codes [N*K/2] (low nibble = even k), scale f32 [N,G],
+ * zero_point u8 [N,G].  w: F64 or F32; K and group_size even.
+ */
+int nslq_int4_quantize_nk(const void *w, int w_dtype, int64_t N, int64_t K, int64_t group_size,
+                          uint8_t *codes, float *scale, uint8_t *zero_point, void *stream);
+
+/*
+ * awq_quantize_cpu (crates/nsl-runtime/src/awq.rs:104-144): weight [K,N] (F64 or F32),
+ * groups along K per column, scale = (max-min)/15 (1.0 if the range is < 1e-10),
+ * zero = min, q = clamp(round((v-zero)/scale), 0, 15); nibble index row*N+col.  Outputs
+ * are what nslq_w4a16_create_awq_kn takes: data [K*N/2], scales/zeros f64 [G*N].
+ * K*N must be a multiple of 8.
+ */
+int nslq_awq_quantize_kn(const void *w, int w_dtype, int64_t K, int64_t N, int64_t group_size,
+                         uint8_t *data, double *scales, double *zeros, void *stream);
+
+/* ========================================================================== */
 /* Column-parallel sharding                                                    */
 /* ========================================================================== */
 /*

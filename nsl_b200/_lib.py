@@ -28,7 +28,21 @@ SIGNATURES = {
     "nslq_w4a16_create_awq_kn": (i32, [vp, vp, vp, i64, i64, i64, C.POINTER(vp)]),
     "nslq_w4a16_destroy": (None, [vp]),
     "nslq_w4a16_forward": (i32, [vp, vp, i32, i64, vp, i32, vp]),
+    "nslq_ternary_quantize_pack": (i32, [vp, i32, i64, vp, vp, vp]),
+    "nslq_int4_quantize_nk": (i32, [vp, i32, i64, i64, i64, vp, vp, vp, vp]),
+    "nslq_awq_quantize_kn": (i32, [vp, i32, i64, i64, i64, vp, vp, vp, vp]),
     "nslq_shard_rows": (i32, [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]),
+}
+
+# Entry points with NSL's own calling convention (include/nsl_shims.h): i64 handles in, i64 out.
+SHIM_SIGNATURES = {
+    "nsl_awq_matmul_cuda": (i64, [i64, i64, i64, i64]),
+    "nsl_gptq_matmul_cuda": (i64, [i64, i64, i64, i64, i64]),
+    "nsl_qtensor_matmul_mixed_cuda": (i64, [i64, i64, i64]),
+    "nsl_quant_forget_cuda": (None, [i64]),
+    "nsl_bitlinear_pack": (i64, [i64, i64, i64, C.c_double]),
+    "nsl_bitlinear_forward": (i64, [i64, i64, i64]),
+    "nsl_bitlinear_free": (None, [i64]),
 }
 
 _lib = None
@@ -49,7 +63,7 @@ def lib():
                 "libnslq_b200.so is missing (%s): build it with `python -m nsl_b200.build`; "
                 "this package has no CPU or PyTorch fallback" % LIB_PATH)
         l = C.CDLL(LIB_PATH)
-        for name, (res, args) in SIGNATURES.items():
+        for name, (res, args) in list(SIGNATURES.items()) + list(SHIM_SIGNATURES.items()):
             fn = getattr(l, name)
             fn.restype = res
             fn.argtypes = args

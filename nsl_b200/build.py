@@ -7,7 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnslq_b200.so")
 
-SOURCES = ["abi.cu", "act_quant.cu", "ternary_gemv.cu", "ternary_gemm_sm100.cu", "w4a16_gemv.cu", "w4a16_gemm_sm100.cu", "noalloc.cu"]
+SOURCES = ["abi.cu", "act_quant.cu", "ternary_gemv.cu", "ternary_gemm_sm100.cu", "w4a16_gemv.cu", "w4a16_gemm_sm100.cu", "noalloc.cu", "pack_at_load.cu", "nsl_shims.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -29,6 +29,7 @@ def needs_build():
     t = os.path.getmtime(LIB)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
     deps.append(os.path.join(HERE, "..", "include", "nslq_b200.h"))
+    deps.append(os.path.join(HERE, "..", "include", "nsl_shims.h"))
     deps.append(os.path.abspath(__file__))
     return any(os.path.getmtime(d) > t for d in deps)
 

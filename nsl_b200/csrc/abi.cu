@@ -53,6 +53,10 @@ bool w4a16_gemm_supported(const void *, const void *, int, int, int64_t, int64_t
 int w4a16_gemm_dispatch(const uint8_t *, const float *, const float *, int64_t, int64_t, int, int, const void *, int64_t,
                         void *, int, cudaStream_t);
 
+int ternary_quantize_pack_dispatch(const void *, int, int64_t, uint8_t *, float *, cudaStream_t);
+int int4_quantize_nk_dispatch(const void *, int, int64_t, int64_t, int64_t, uint8_t *, float *, uint8_t *, cudaStream_t);
+int awq_quantize_kn_dispatch(const void *, int, int64_t, int64_t, int64_t, uint8_t *, double *, double *, cudaStream_t);
+
 static inline int out_elem_size(int dt)
 {
     return dt == NSLQ_DTYPE_F32 ? 4 : (dt == NSLQ_DTYPE_FP16 || dt == NSLQ_DTYPE_BF16) ? 2 : 0;
@@ -324,6 +328,32 @@ int nslq_w4a16_forward(const nslq_w4a16_t *w, const void *x, int x_dtype, int64_
         return NSLQ_OK;
     }
     return w4a16_scalar_dispatch(w->codes, w->scale, w->zc, w->N, w->K, w->G, w->gs, x, x_dtype, M, y, y_dtype, st);
+}
+
+int nslq_ternary_quantize_pack(const void *w, int w_dtype, int64_t numel, uint8_t *packed, float *scale, void *stream)
+{
+    if (!w || !packed || !scale) return fail(NSLQ_ERR_ARG, "nslq_ternary_quantize_pack: null argument");
+    if (numel <= 0) return fail(NSLQ_ERR_SHAPE, "nslq_ternary_quantize_pack: numel=%lld", (long long)numel);
+    if (numel % 4 != 0) return fail(NSLQ_ERR_SHAPE, "nslq_ternary_quantize_pack: numel %lld is not a multiple of 4", (long long)numel);
+    return ternary_quantize_pack_dispatch(w, w_dtype, numel, packed, scale, (cudaStream_t)stream);
+}
+
+int nslq_int4_quantize_nk(const void *w, int w_dtype, int64_t N, int64_t K, int64_t group_size, uint8_t *codes,
+                          float *scale, uint8_t *zero_point, void *stream)
+{
+    if (!w || !codes || !scale || !zero_point) return fail(NSLQ_ERR_ARG, "nslq_int4_quantize_nk: null argument");
+    if (N <= 0 || K <= 0 || group_size <= 0) return fail(NSLQ_ERR_SHAPE, "nslq_int4_quantize_nk: N=%lld K=%lld group=%lld", (long long)N, (long long)K, (long long)group_size);
+    if (K % 2 != 0 || group_size % 2 != 0) return fail(NSLQ_ERR_SHAPE, "nslq_int4_quantize_nk: K and group_size must be even (K=%lld group=%lld)", (long long)K, (long long)group_size);
+    return int4_quantize_nk_dispatch(w, w_dtype, N, K, group_size, codes, scale, zero_point, (cudaStream_t)stream);
+}
+
+int nslq_awq_quantize_kn(const void *w, int w_dtype, int64_t K, int64_t N, int64_t group_size, uint8_t *data,
+                         double *scales, double *zeros, void *stream)
+{
+    if (!w || !data || !scales || !zeros) return fail(NSLQ_ERR_ARG, "nslq_awq_quantize_kn: null argument");
+    if (N <= 0 || K <= 0 || group_size <= 0) return fail(NSLQ_ERR_SHAPE, "nslq_awq_quantize_kn: K=%lld N=%lld group=%lld", (long long)K, (long long)N, (long long)group_size);
+    if ((K * N) % 8 != 0) return fail(NSLQ_ERR_SHAPE, "nslq_awq_quantize_kn: K*N = %lld must be a multiple of 8", (long long)(K * N));
+    return awq_quantize_kn_dispatch(w, w_dtype, K, N, group_size, data, scales, zeros, (cudaStream_t)stream);
 }
 
 int nslq_shard_rows(int64_t N, int world, int rank, int64_t *row0, int64_t *rows)

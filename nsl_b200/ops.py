@@ -149,6 +149,40 @@ class W4A16:
         return y
 
 
+def ternary_quantize_pack(w):
+    """Float weight [out, in] -> (packed uint8 [out, in/4], scale tensor[1]) with the reference loader's arithmetic."""
+    if not w.is_cuda or not w.is_contiguous():
+        raise ValueError("w must be a contiguous CUDA tensor")
+    packed = torch.empty(w.shape[0], w.shape[1] // 4, dtype=torch.uint8, device=w.device)
+    scale = torch.empty(1, dtype=torch.float32, device=w.device)
+    check(lib().nslq_ternary_quantize_pack(_ptr(w), _tag(w.dtype), w.numel(), _ptr(packed), _ptr(scale), _stream()))
+    return packed, scale
+
+
+def int4_quantize_nk(w, group_size):
+    """[N,K] f32/f64 -> (codes [N,K/2], scale f32 [N,G], zero_point u8 [N,G]), the QuantizedTensor form."""
+    N, K = w.shape
+    G = (K + group_size - 1) // group_size
+    codes = torch.empty(N, K // 2, dtype=torch.uint8, device=w.device)
+    scale = torch.empty(N, G, dtype=torch.float32, device=w.device)
+    zp = torch.empty(N, G, dtype=torch.uint8, device=w.device)
+    check(lib().nslq_int4_quantize_nk(_ptr(w), _tag(w.dtype), N, K, group_size, _ptr(codes), _ptr(scale), _ptr(zp),
+                                      _stream()))
+    return codes, scale, zp
+
+
+def awq_quantize_kn(w, group_size):
+    """[K,N] f32/f64 -> (data [K*N/2], scales f64 [G*N], zeros f64 [G*N]), the AwqPackedWeight form."""
+    K, N = w.shape
+    G = (K + group_size - 1) // group_size
+    data = torch.empty(K * N // 2, dtype=torch.uint8, device=w.device)
+    scales = torch.empty(G * N, dtype=torch.float64, device=w.device)
+    zeros = torch.empty(G * N, dtype=torch.float64, device=w.device)
+    check(lib().nslq_awq_quantize_kn(_ptr(w), _tag(w.dtype), K, N, group_size, _ptr(data), _ptr(scales), _ptr(zeros),
+                                     _stream()))
+    return data, scales, zeros
+
+
 def device_status():
     """Nonzero if a bounded wait inside a kernel expired since the last call (then cleared)."""
     v = C.c_int()

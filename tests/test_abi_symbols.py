@@ -15,8 +15,8 @@ def built():
     return build.build()
 
 
-def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "nslq_b200.h")).read()
+def declared_symbols(header="nslq_b200.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(nslq?_[a-z0-9_]+)\s*\(", text)))
 
@@ -32,6 +32,20 @@ def test_header_symbols_are_exported(built):
 def test_ctypes_table_matches_header(built):
     from nsl_b200 import _lib
     assert sorted(_lib.SIGNATURES) == declared_symbols()
+    assert sorted(_lib.SHIM_SIGNATURES) == declared_symbols("nsl_shims.h")
+    l = C.CDLL(built)
+    assert not [n for n in declared_symbols("nsl_shims.h") if not hasattr(l, n)]
+
+
+def test_shim_null_handling_without_gpu(built):
+    """awq family: message + 0 on null, as the reference does (awq.rs:266)."""
+    from nsl_b200 import _lib
+    l = _lib.lib()
+    assert l.nsl_awq_matmul_cuda(0, 0, 128, 0) == 0
+    assert l.nsl_bitlinear_pack(0, 16, 64, 1.0) == 0
+    assert l.nsl_bitlinear_forward(0, 0, 0) == 0
+    l.nsl_bitlinear_free(0)
+    l.nsl_quant_forget_cuda(12345)
 
 
 def test_argument_checks_without_gpu(built):
