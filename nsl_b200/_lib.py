@@ -6,7 +6,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libnslq_b200.so")
+# NSLQ_LIB points at another build of the same library (kernel experiments); default: the in-tree build
+LIB_PATH = os.environ.get("NSLQ_LIB") or os.path.join(_HERE, "libnslq_b200.so")
 
 vp, i64, i32, f32 = C.c_void_p, C.c_int64, C.c_int, C.c_float
 

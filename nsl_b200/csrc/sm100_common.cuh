@@ -54,6 +54,17 @@ static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, 
         }
     }
 }
+// True in exactly one lane of a converged warp; the compiler keeps the guarded code on the uniform path.
+static __device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
 static __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tmap, int x, int y, uint32_t bar)
 {
     asm volatile(
