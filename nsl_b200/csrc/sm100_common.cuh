@@ -109,9 +109,9 @@ static __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[1
         : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-// Writes 32 consecutive 32-bit columns of this thread's TMEM lane (the warp's lane quadrant) and
-// waits until the store has been performed.
-static __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32])
+// Writes 32 consecutive 32-bit columns of this thread's TMEM lane (the warp's lane quadrant);
+// tmem_st_wait() returns once the thread's stores have been performed.
+static __device__ __forceinline__ void tmem_st32_issue(uint32_t taddr, const uint32_t (&r)[32])
 {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -121,8 +121,8 @@ static __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t 
           "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
           "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+static __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // Integer MMA with the A operand (M = 128 rows, one per TMEM lane, four 8-bit K elements per
 // 32-bit column) in tensor memory and the B operand described in shared memory.
 static __device__ __forceinline__ void umma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)

@@ -50,14 +50,21 @@ using namespace sm100;
 constexpr int BW = 128;                  // weight rows per tile = MMA M = TMEM lanes
 constexpr int BK = 128;                  // bytes of int8 along K per k-block = one 128B swizzle row
 constexpr int THREADS = 640;            // 20 warps: 0 TMA, 1 MMA, 4-7 and 16-19 epilogue, 8-15 unpack
-constexpr int P_BYTES = BW * (BK / 4);   // packed 2-bit weight tile as it sits in global memory: 4 KiB
 
 template <int BT> struct Cfg {
     static_assert(BT == 128 || BT == 192, "token tile");
-    static constexpr int X_BYTES = BT * BK;                           // activation tile
+    // k-blocks (128 k) per pipeline step.  One step costs the MMA warp one barrier round trip and
+    // two commits whatever its size, and with one k-block per step that overhead, not the tensor
+    // pipe, set the pace; the wide tile has TMEM columns for single k-block stages only.
+    static constexpr int KS = (BT == 128) ? 2 : 1;
+    static constexpr int X_SUB = BT * BK;                             // one 128-byte-swizzled activation sub-tile
+    static constexpr int X_BYTES = KS * X_SUB;
+    static constexpr int PK_ROW = KS * (BK / 4);                      // packed bytes per weight row and step
+    static constexpr int P_BYTES = BW * PK_ROW;                       // packed 2-bit weight tile as it sits in global memory
     static constexpr int T_BYTES = X_BYTES + P_BYTES;                 // one copy stage, multiple of 1024
-    static constexpr int TS = (BT == 192) ? 6 : 8;                    // copy stages in flight
-    static constexpr int AS = (512 - 2 * BT) / 32;                    // TMEM operand stages (32 columns each): 4 or 8
+    static constexpr int TS = (BT == 192) ? 6 : 5;                    // copy stages in flight
+    static constexpr int A_COLS = 32 * KS;                            // TMEM columns per operand stage
+    static constexpr int AS = (512 - 2 * BT) / A_COLS;                // TMEM operand stages: 4
     static constexpr int HALF_T = BT / 2;                             // tokens per epilogue warp
     static constexpr int SCALE_BYTES = 8 * HALF_T * 8;                // per epilogue warp: scale/127 and row sum per token
     static constexpr int BAR_BYTES = 512;
@@ -73,7 +80,7 @@ template <int BT> struct Cfg {
     static __device__ __forceinline__ uint32_t acc_col(uint32_t buf) { return BT == 128 ? buf * 128u : buf * 256u; }
     static __device__ __forceinline__ uint32_t a_col(uint32_t a)
     {
-        return BT == 128 ? 256u + 32u * a : 192u + 32u * (a & 1u) + 256u * (a >> 1);
+        return BT == 128 ? 256u + (uint32_t)A_COLS * a : 192u + 32u * (a & 1u) + 256u * (a >> 1);
     }
 };
 
@@ -174,27 +181,35 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     uint8_t *base_ptr = smem_raw + (base - raw);
     float *scale_ptr = reinterpret_cast<float *>(base_ptr + C::TS * C::T_BYTES);
     const uint32_t bars = base + C::TS * C::T_BYTES + C::SCALE_BYTES;
-    // barrier map (8 bytes each): raw[t] (copy stage landed), tfree[t] (copy stage consumed: four
-    // unpack warps + the MMAs' commit), afull[a] (codes stored in TMEM), afree[a] (MMAs of the operand
-    // stage retired), acc_full[2], acc_empty[2]; then the TMEM slot
-    constexpr int NBAR = 2 * C::TS + 2 * C::AS + 4;
+    // barrier map (8 bytes each): raw[t] (copy stage landed), pfree[t] (packed tile of the copy stage
+    // read by the four unpack warps), afull[a] (codes stored in TMEM), done[8] (MMAs of step i retired,
+    // i mod 8: ONE commit per step, which frees both the copy stage i mod TS and the operand stage
+    // i mod AS -- a second commit per step cost the issuing thread ~190 cycles), acc_full[2],
+    // acc_empty[2]; then the TMEM slot.  A waiter of done[] is at most TS steps behind the commit it
+    // waits for and the ring has 8 > TS entries, so the phase it tests cannot have been overtaken.
+    constexpr int ND = 8;
+    static_assert(C::TS < ND && C::AS < ND, "done ring too short");
+    constexpr int NBAR = 2 * C::TS + C::AS + ND + 4;
     static_assert(NBAR * 8 + 8 <= C::BAR_BYTES, "barrier area");
     auto raw_bar = [&](int t) { return bars + 8u * t; };
-    auto tfree_bar = [&](int t) { return bars + 8u * (C::TS + t); };
+    auto pfree_bar = [&](int t) { return bars + 8u * (C::TS + t); };
     auto afull_bar = [&](int a) { return bars + 8u * (2 * C::TS + a); };
-    auto afree_bar = [&](int a) { return bars + 8u * (2 * C::TS + C::AS + a); };
-    auto accf_bar = [&](int b) { return bars + 8u * (2 * C::TS + 2 * C::AS + b); };
-    auto acce_bar = [&](int b) { return bars + 8u * (2 * C::TS + 2 * C::AS + 2 + b); };
+    auto done_bar = [&](uint32_t i) { return bars + 8u * (2 * C::TS + C::AS + (i & (ND - 1))); };
+    auto accf_bar = [&](int b) { return bars + 8u * (2 * C::TS + C::AS + ND + b); };
+    auto acce_bar = [&](int b) { return bars + 8u * (2 * C::TS + C::AS + ND + 2 + b); };
+    // parity of the phase of done[i mod 8] that step i completes
+    auto done_par = [&](uint32_t i) { return (i / ND) & 1u; };
     const uint32_t slot = bars + 8u * NBAR;
     volatile uint32_t *slot_ptr = reinterpret_cast<volatile uint32_t *>(base_ptr + C::TS * C::T_BYTES + C::SCALE_BYTES + 8 * NBAR);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nkb = (int)((p.K + BK - 1) / BK);
+    const int nkb = (int)((p.K + BK * C::KS - 1) / (BK * C::KS));   // pipeline steps per tile
     const int ntiles = p.tiles_t * p.tiles_w;
 
     if (threadIdx.x == 0) {
-        for (int t = 0; t < C::TS; ++t) { mbar_init(raw_bar(t), 1); mbar_init(tfree_bar(t), 5); }
-        for (int a = 0; a < C::AS; ++a) { mbar_init(afull_bar(a), 4); mbar_init(afree_bar(a), 1); }
+        for (int t = 0; t < C::TS; ++t) { mbar_init(raw_bar(t), 1); mbar_init(pfree_bar(t), 4); }
+        for (int a = 0; a < C::AS; ++a) mbar_init(afull_bar(a), 4);
+        for (int i = 0; i < ND; ++i) mbar_init(done_bar(i), 1);
         for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 256); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -213,42 +228,52 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         // ---------------- TMA producer (activation tile + packed weight tile)
         if (lane == 0) {
             int s = 0;
-            uint32_t ph = 0;
+            uint32_t ph = 0, it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % p.tiles_t) * BT, n0 = (tile / p.tiles_t) * BW;
-                for (int kb = 0; kb < nkb; ++kb) {
-                    if (!(ok = mbar_wait(tfree_bar(s), ph ^ 1u, 0x101))) break;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    if (it >= (uint32_t)C::TS) {       // the stage's previous user: step it - TS
+                        if (!(ok = mbar_wait(done_bar(it - C::TS), done_par(it - C::TS), 0x101))) break;
+                        if (!(ok = mbar_wait(pfree_bar(s), ph ^ 1u, 0x102))) break;
+                    }
                     const uint32_t st = base + s * C::T_BYTES;
                     mbar_arrive_expect_tx(raw_bar(s), C::T_BYTES);
-                    tma_load_2d(st, &tmap_x, kb * BK, m0, raw_bar(s));
-                    tma_load_2d(st + C::X_BYTES, &tmap_w, kb * (BK / 4), n0, raw_bar(s));
+#pragma unroll
+                    for (int ks = 0; ks < C::KS; ++ks)
+                        tma_load_2d(st + ks * C::X_SUB, &tmap_x, (kb * C::KS + ks) * BK, m0, raw_bar(s));
+                    tma_load_2d(st + C::X_BYTES, &tmap_w, kb * C::PK_ROW, n0, raw_bar(s));
                     if (++s == C::TS) { s = 0; ph ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer (whole warp in the loop, one elected lane issues)
+        // ---------------- MMA issuer.  The whole warp runs the loop in uniform control flow and one
+        // elected lane issues: measured here, eight MMAs issue in ~120 cycles from a converged warp
+        // and in ~450 from a lone diverged lane.
         const bool leader = elect_one();
+        uint32_t a = 0, aph = 0, t = 0, it = 0;
         int s = 0;
-        uint32_t a = 0, aph = 0, t = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
             const uint32_t buf = t & 1u, cph = (t >> 1) & 1u;
             if (!(ok = mbar_wait(acce_bar(buf), cph ^ 1u, 0x201))) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + C::acc_col(buf);
-            for (int kb = 0; kb < nkb; ++kb) {
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
                 if (!(ok = mbar_wait(afull_bar(a), aph, 0x203))) break;    // codes stored (and the copy stage landed)
                 tc_fence_after();
                 if (leader) {
-                    const uint64_t bdesc = smem_desc(base + s * C::T_BYTES);
                     const uint32_t a_tmem = tmem_base + C::a_col(a);
+                    // MMAs of this step that hold any k < K (the last step of a tile may be part empty)
+                    const int64_t k_left = p.K - (int64_t)kb * (BK * C::KS);
+                    const int nmma = k_left >= BK * C::KS ? 4 * C::KS : (int)((k_left + 31) / 32);
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4)   // 32 bytes of K per MMA: 8 TMEM columns, descriptor start + 2 (16-byte units)
-                        umma_i8_ts(d_tmem, a_tmem + 8u * k4, bdesc + 2u * k4, C::IDESC, (kb | k4) != 0);
-                    umma_commit(tfree_bar(s));
-                    umma_commit(afree_bar(a));
+                    for (int k4 = 0; k4 < 4 * C::KS; ++k4) {   // 32 bytes of K per MMA: 8 TMEM columns, descriptor start + 2 (16-byte units)
+                        const uint64_t bdesc = smem_desc(base + s * C::T_BYTES + (k4 >> 2) * C::X_SUB);
+                        if (k4 < nmma) umma_i8_ts(d_tmem, a_tmem + 8u * k4, bdesc + 2u * (k4 & 3), C::IDESC, (kb | k4) != 0);
+                    }
+                    umma_commit(done_bar(it));
                 }
                 if (++s == C::TS) s = 0;
                 if (++a == C::AS) { a = 0; aph ^= 1u; }
@@ -266,23 +291,30 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         uint32_t a = group % C::AS, sph = 0, aph = 0;
         for (int it = group; it < total_it && ok; it += 2) {
             if (!(ok = mbar_wait(raw_bar(s), sph, 0x301))) break;                            // packed tile landed
-            const uint4 *pk = reinterpret_cast<const uint4 *>(base_ptr + s * C::T_BYTES + C::X_BYTES + row * 32);
-            const uint4 p0 = pk[0], p1 = pk[1];
-            const uint32_t wv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-            uint32_t r[32];
+            const uint4 *pk = reinterpret_cast<const uint4 *>(base_ptr + s * C::T_BYTES + C::X_BYTES + row * C::PK_ROW);
+            uint4 pv[2 * C::KS];
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                r[4 * g + 0] = (wv[g] >> 6) & 0x03030303u; r[4 * g + 1] = (wv[g] >> 4) & 0x03030303u;
-                r[4 * g + 2] = (wv[g] >> 2) & 0x03030303u; r[4 * g + 3] = wv[g] & 0x03030303u;
-            }
-            if (!(ok = mbar_wait(afree_bar(a), aph ^ 1u, 0x302))) break;                     // operand stage reusable
+            for (int i = 0; i < 2 * C::KS; ++i) pv[i] = pk[i];
+            if (it >= C::AS && !(ok = mbar_wait(done_bar(it - C::AS), done_par(it - C::AS), 0x302))) break;   // operand stage reusable
             tc_fence_after();
-            tmem_st32(tmem_base + ((uint32_t)(q * 32) << 16) + C::a_col(a), r);
+#pragma unroll
+            for (int h = 0; h < C::KS; ++h) {                                                // one k-block: 32 bytes -> 32 columns
+                const uint32_t wv[8] = {pv[2 * h].x, pv[2 * h].y, pv[2 * h].z, pv[2 * h].w,
+                                        pv[2 * h + 1].x, pv[2 * h + 1].y, pv[2 * h + 1].z, pv[2 * h + 1].w};
+                uint32_t r[32];
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    r[4 * g + 0] = (wv[g] >> 6) & 0x03030303u; r[4 * g + 1] = (wv[g] >> 4) & 0x03030303u;
+                    r[4 * g + 2] = (wv[g] >> 2) & 0x03030303u; r[4 * g + 3] = wv[g] & 0x03030303u;
+                }
+                tmem_st32_issue(tmem_base + ((uint32_t)(q * 32) << 16) + C::a_col(a) + 32u * h, r);
+            }
+            tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(afull_bar(a));
-                mbar_arrive(tfree_bar(s));
+                mbar_arrive(pfree_bar(s));
             }
             if ((s += 2) >= C::TS) { s -= C::TS; sph ^= 1u; }
             if ((a += 2) >= (uint32_t)C::AS) { a -= C::AS; aph ^= 1u; }
@@ -362,7 +394,7 @@ static int launch_gemm(const void *q_perm, gemm::Params &p, cudaStream_t st)
     CUtensorMap tmap_x, tmap_w;
     int rc = sm100::make_map_2d(&tmap_x, q_perm, (uint64_t)p.K, (uint64_t)p.M, gemm::BK, BT, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    rc = sm100::make_map_2d(&tmap_w, p.w, (uint64_t)(p.K / 4), (uint64_t)p.N, gemm::BK / 4, gemm::BW, CU_TENSOR_MAP_SWIZZLE_NONE);
+    rc = sm100::make_map_2d(&tmap_w, p.w, (uint64_t)(p.K / 4), (uint64_t)p.N, C::PK_ROW, gemm::BW, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     p.tiles_t = (int)((p.M + BT - 1) / BT);
     p.tiles_w = (int)((p.N + gemm::BW - 1) / gemm::BW);
