@@ -39,6 +39,13 @@ int ternary_scalar_dispatch(const uint8_t *, const int8_t *, const float *, int6
 bool ternary_gemv_fused_supported(const void *, const void *, int64_t, int64_t);
 int ternary_gemv_fused_dispatch(const uint8_t *, const void *, int, int, int64_t, int64_t, float, void *, int, int32_t *,
                                 const float *, const float *, cudaStream_t);
+bool ternary_stream_supported(const void *, const void *, int64_t, int64_t, int64_t);
+int ternary_stream_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int, int64_t, int64_t,
+                            float, void *, int, int32_t *, const float *, const float *, cudaStream_t);
+bool ternary_stream_fused_supported(const void *, const void *, int, int64_t, int64_t, int64_t);
+int ternary_stream_fused_dispatch(const uint8_t *, const void *, int, int, int64_t, int64_t, float, void *, int, int32_t *,
+                                  const float *, const float *, cudaStream_t);
+int ternary_stream_status(int *);
 bool ternary_gemm_supported(const void *, const void *, int64_t, int64_t, int64_t);
 int ternary_gemm_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int64_t, int64_t,
                           int64_t, float, void *, int, int32_t *, const float *, const float *, cudaStream_t);
@@ -136,11 +143,12 @@ int nslq_device_status(int *status)
     if (!status) return fail(NSLQ_ERR_ARG, "nslq_device_status: null output");
     if (cudaDeviceSynchronize() != cudaSuccess)
         return fail(NSLQ_ERR_CUDA, "nslq_device_status: %s", cudaGetErrorString(cudaGetLastError()));
-    int a = 0, b = 0;
+    int a = 0, b = 0, c = 0;
     int rc = ternary_gemm_status(&a);
     if (rc) return rc;
     if ((rc = w4a16_gemm_status(&b))) return rc;
-    *status = a ? a : b;
+    if ((rc = ternary_stream_status(&c))) return rc;
+    *status = a ? a : (b ? b : c);
     return NSLQ_OK;
 }
 
@@ -190,6 +198,14 @@ int nslq_bitlinear_forward_quantized(const nslq_bitlinear_t *w, const int8_t *q_
     const int es = out_elem_size(y_dtype);
     for (int64_t m0 = 0; m0 < M; m0 += 16) {
         const int mc = (int)((M - m0) < 16 ? (M - m0) : 16);
+        if (ternary_stream_supported(w->packed, q_perm + m0 * w->K, mc, w->N, w->K)) {
+            int rc = ternary_stream_dispatch(w->packed, q_perm + m0 * w->K, scale + m0, rowsum + m0, mc, w->N, w->K,
+                                             w->weight_scale, (char *)y + m0 * w->N * es, y_dtype,
+                                             acc_out ? acc_out + m0 * w->N : nullptr, bias,
+                                             residual ? residual + m0 * w->N : nullptr, st);
+            if (rc) return rc;
+            continue;
+        }
         int rc = ternary_gemv_dispatch(w->packed, q_perm + m0 * w->K, scale + m0, rowsum + m0, mc, w->N, w->K,
                                        w->weight_scale, (char *)y + m0 * w->N * es, y_dtype,
                                        acc_out ? acc_out + m0 * w->N : nullptr, bias,
@@ -215,6 +231,9 @@ int nslq_bitlinear_forward(const nslq_bitlinear_t *w, const void *x, int x_dtype
     int8_t *q = (int8_t *)workspace;
     float *scale = (float *)((char *)workspace + align_up(M * w->K, 256));
     int32_t *rowsum = (int32_t *)((char *)scale + align_up(M * 4, 256));
+    if (ternary_stream_fused_supported(w->packed, x, x_dtype, M, w->N, w->K))
+        return ternary_stream_fused_dispatch(w->packed, x, x_dtype, (int)M, w->N, w->K, w->weight_scale, y, y_dtype, acc_out,
+                                             bias, residual, st);
     if (ternary_gemv_fused_supported(w->packed, x, M, w->K) && (x_dtype == NSLQ_DTYPE_F32 || aligned16(x)))
         return ternary_gemv_fused_dispatch(w->packed, x, x_dtype, (int)M, w->N, w->K, w->weight_scale, y, y_dtype, acc_out,
                                            bias, residual, st);
