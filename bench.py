@@ -291,9 +291,11 @@ class DecodeGemv(Workload):
         self.ws = torch.empty(int(ops.lib().nslq_bitlinear_workspace_bytes(self.M, self.K)), dtype=torch.uint8,
                               device="cuda")
         self.kernel_launches = self.LAYERS
-        self.launches_per_step = self.LAYERS                   # M <= 4: quantisation is fused into the GEMV kernel
+        # M <= 4 (<= 2 on the tensor-memory kernel): the quantisation is fused into the decode kernel
+        self.launches_per_step = self.LAYERS * (1 if self.M <= 2 else 2)
         self.h2d, self.d2h = self.M * self.K * 4, self.M * self.N * 4
-        self.l2_note = "64 distinct 6.9 MB weights per step (442 MB > L2)"
+        mb = self.N * self.K / 4e6
+        self.l2_note = "%d distinct %.1f MB weights per step (%.0f MB > L2)" % (self.LAYERS, mb, self.LAYERS * mb)
 
     def units_per_step(self):
         return self.LAYERS * self.BYTES_PER_CALL / 1e9
@@ -349,7 +351,24 @@ class DecodeGemv(Workload):
             n += 1
         dt = (time.perf_counter() - t0) / n
         return {"value": round(cls.BYTES_PER_CALL / dt / 1e9, 4), "unit": "GB/s", "cores": threads, "kind": "port",
-                "sample": "%d full [1,3200]x[8640,3200] calls, %.2f ms each" % (n, dt * 1e3)}, dt
+                "sample": "%d full [%d,%d]x[%d,%d] calls, %.2f ms each" % (n, cls.M, cls.K, cls.N, cls.K, dt * 1e3)}, dt
+
+
+class DecodeGemvVocab(DecodeGemv):
+    """The same decode call on the decoder's largest matrix shape (vocabulary projection, 25.6 MB
+    packed): large enough for the tensor-memory streaming kernel."""
+    key, name = "decode_gemv_vocab", "bitlinear_decode_gemv_m1_n32002_k3200"
+    kernel_name = "ternary_decode_kernel"
+    N, K, M, LAYERS = 32002, 3200, 1, 16
+    BYTES_PER_CALL = 32002 * 3200 // 4 + 3200 * 4 + 32002 * 4
+
+
+class DecodeGemvVocabM16(DecodeGemv):
+    """Sixteen tokens against the same matrix (batched decode): act_quant + the streaming kernel."""
+    key, name = "decode_gemv_vocab_m16", "bitlinear_decode_m16_n32002_k3200"
+    kernel_name = "ternary_decode_kernel"
+    N, K, M, LAYERS = 32002, 3200, 16, 16
+    BYTES_PER_CALL = 32002 * 3200 // 4 + 16 * 3200 * 4 + 16 * 32002 * 4
 
 
 class W4A16(Workload):
@@ -453,8 +472,8 @@ class W4A16(Workload):
 def make_workload(key, torch, ops, rank, world, streams=1):
     if key == "prefill_gemm":
         return PrefillGemm(torch, ops, rank, world)
-    if key == "decode_gemv":
-        return DecodeGemv(torch, ops, rank, world, streams=streams)
+    if key in DECODE_CLASSES:
+        return DECODE_CLASSES[key](torch, ops, rank, world, streams=streams)
     if key.startswith("w4a16_m"):
         return W4A16(torch, ops, rank, world, M=int(key[7:]))
     raise SystemExit("unknown workload %s" % key)
@@ -463,15 +482,16 @@ def make_workload(key, torch, ops, rank, world, streams=1):
 def cpu_arm(key, threads, budget_s):
     if key == "prefill_gemm":
         return PrefillGemm.cpu_baseline(threads, budget_s)
-    if key == "decode_gemv":
-        return DecodeGemv.cpu_baseline(threads, budget_s)
+    if key in DECODE_CLASSES:
+        return DECODE_CLASSES[key].cpu_baseline(threads, budget_s)
     return W4A16.cpu_baseline_m(int(key[7:]), threads, budget_s)
 
 
-WORKLOAD_KEYS = ["prefill_gemm", "decode_gemv", "w4a16_m1", "w4a16_m4", "w4a16_m8", "w4a16_m16", "w4a16_m256",
+DECODE_CLASSES = {c.key: c for c in (DecodeGemv, DecodeGemvVocab, DecodeGemvVocabM16)}
+WORKLOAD_KEYS = ["prefill_gemm", "decode_gemv", "decode_gemv_vocab", "decode_gemv_vocab_m16", "w4a16_m1", "w4a16_m4", "w4a16_m8", "w4a16_m16", "w4a16_m256",
                  "bitnet3b_b1", "bitnet3b_b8", "bitnet3b_b64"]
 DEFAULT_WORKLOAD = "prefill_gemm"
-META = {"prefill_gemm": PrefillGemm, "decode_gemv": DecodeGemv}
+META = {"prefill_gemm": PrefillGemm, **DECODE_CLASSES}
 
 
 # ----------------------------------------------------------------------------- decoder workload
@@ -617,8 +637,8 @@ def run_ours(args):
     # the other configurations of the metric, shorter runs, single GPU only
     if world == 1 and args.workload == DEFAULT_WORKLOAD and not args.no_also:
         also = []
-        for key, streams in (("decode_gemv", 1), ("decode_gemv", 4), ("w4a16_m1", 1), ("w4a16_m16", 1),
-                             ("w4a16_m256", 1)):
+        for key, streams in (("decode_gemv", 1), ("decode_gemv", 4), ("decode_gemv_vocab", 1), ("decode_gemv_vocab_m16", 1),
+                             ("w4a16_m1", 1), ("w4a16_m16", 1), ("w4a16_m256", 1)):
             w2 = make_workload(key, torch, ops, rank, world, streams=streams)
             m2 = measure(torch, w2, max(10, args.steps // 3), 3, use_graph, None, None, want_e2e=True)
             r2 = w2.roofline(peaks, m2["kernel_ms"])

@@ -39,13 +39,13 @@ int ternary_scalar_dispatch(const uint8_t *, const int8_t *, const float *, int6
 bool ternary_gemv_fused_supported(const void *, const void *, int64_t, int64_t);
 int ternary_gemv_fused_dispatch(const uint8_t *, const void *, int, int, int64_t, int64_t, float, void *, int, int32_t *,
                                 const float *, const float *, cudaStream_t);
-bool ternary_stream_supported(const void *, const void *, int64_t, int64_t, int64_t);
-int ternary_stream_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int, int64_t, int64_t,
+bool ternary_decode_supported(const void *, const void *, int64_t, int64_t, int64_t);
+int ternary_decode_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int, int64_t, int64_t,
                             float, void *, int, int32_t *, const float *, const float *, cudaStream_t);
-bool ternary_stream_fused_supported(const void *, const void *, int, int64_t, int64_t, int64_t);
-int ternary_stream_fused_dispatch(const uint8_t *, const void *, int, int, int64_t, int64_t, float, void *, int, int32_t *,
+bool ternary_decode_fused_supported(const void *, const void *, int, int64_t, int64_t, int64_t);
+int ternary_decode_fused_dispatch(const uint8_t *, const void *, int, int, int64_t, int64_t, float, void *, int, int32_t *,
                                   const float *, const float *, cudaStream_t);
-int ternary_stream_status(int *);
+int ternary_decode_status(int *);
 bool ternary_gemm_supported(const void *, const void *, int64_t, int64_t, int64_t);
 int ternary_gemm_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int64_t, int64_t,
                           int64_t, float, void *, int, int32_t *, const float *, const float *, cudaStream_t);
@@ -63,6 +63,19 @@ int w4a16_gemm_dispatch(const uint8_t *, const float *, const float *, int64_t, 
 int ternary_quantize_pack_dispatch(const void *, int, int64_t, uint8_t *, float *, cudaStream_t);
 int int4_quantize_nk_dispatch(const void *, int, int64_t, int64_t, int64_t, uint8_t *, float *, uint8_t *, cudaStream_t);
 int awq_quantize_kn_dispatch(const void *, int, int64_t, int64_t, int64_t, uint8_t *, double *, double *, cudaStream_t);
+
+// Which decode kernel for M <= 16 tokens.  The tensor-memory kernel (ternary_decode_kernel) streams
+// at 4-5 TB/s but has ~5 us of start-up (TMEM allocation, token staging, pipeline fill); the
+// register-staged kernels (ternary_gemv*.cu) start in ~2 us and stream at 1-2 TB/s.  Measured
+// crossovers on B200 (K = 3200): 13 MB of packed weights at M = 1, 10 MB at M = 4, 28 MB at M = 8,
+// none at M = 16 (the tensor-memory kernel wins from the smallest size).
+static inline bool decode_pays(int64_t M, int64_t N, int64_t K)
+{
+    const double mb = (double)N * (double)K / 4.0 / 1.0e6;
+    if (M > 8) return true;
+    if (M > 4) return mb >= 28.0;
+    return mb >= 12.0;
+}
 
 static inline int out_elem_size(int dt)
 {
@@ -147,7 +160,7 @@ int nslq_device_status(int *status)
     int rc = ternary_gemm_status(&a);
     if (rc) return rc;
     if ((rc = w4a16_gemm_status(&b))) return rc;
-    if ((rc = ternary_stream_status(&c))) return rc;
+    if ((rc = ternary_decode_status(&c))) return rc;
     *status = a ? a : (b ? b : c);
     return NSLQ_OK;
 }
@@ -198,8 +211,8 @@ int nslq_bitlinear_forward_quantized(const nslq_bitlinear_t *w, const int8_t *q_
     const int es = out_elem_size(y_dtype);
     for (int64_t m0 = 0; m0 < M; m0 += 16) {
         const int mc = (int)((M - m0) < 16 ? (M - m0) : 16);
-        if (ternary_stream_supported(w->packed, q_perm + m0 * w->K, mc, w->N, w->K)) {
-            int rc = ternary_stream_dispatch(w->packed, q_perm + m0 * w->K, scale + m0, rowsum + m0, mc, w->N, w->K,
+        if (decode_pays(mc, w->N, w->K) && ternary_decode_supported(w->packed, q_perm + m0 * w->K, mc, w->N, w->K)) {
+            int rc = ternary_decode_dispatch(w->packed, q_perm + m0 * w->K, scale + m0, rowsum + m0, mc, w->N, w->K,
                                              w->weight_scale, (char *)y + m0 * w->N * es, y_dtype,
                                              acc_out ? acc_out + m0 * w->N : nullptr, bias,
                                              residual ? residual + m0 * w->N : nullptr, st);
@@ -231,10 +244,11 @@ int nslq_bitlinear_forward(const nslq_bitlinear_t *w, const void *x, int x_dtype
     int8_t *q = (int8_t *)workspace;
     float *scale = (float *)((char *)workspace + align_up(M * w->K, 256));
     int32_t *rowsum = (int32_t *)((char *)scale + align_up(M * 4, 256));
-    if (ternary_stream_fused_supported(w->packed, x, x_dtype, M, w->N, w->K))
-        return ternary_stream_fused_dispatch(w->packed, x, x_dtype, (int)M, w->N, w->K, w->weight_scale, y, y_dtype, acc_out,
+    if (decode_pays(M, w->N, w->K) && ternary_decode_fused_supported(w->packed, x, x_dtype, M, w->N, w->K))
+        return ternary_decode_fused_dispatch(w->packed, x, x_dtype, (int)M, w->N, w->K, w->weight_scale, y, y_dtype, acc_out,
                                              bias, residual, st);
-    if (ternary_gemv_fused_supported(w->packed, x, M, w->K) && (x_dtype == NSLQ_DTYPE_F32 || aligned16(x)))
+    if (!decode_pays(M, w->N, w->K) && ternary_gemv_fused_supported(w->packed, x, M, w->K) &&
+        (x_dtype == NSLQ_DTYPE_F32 || aligned16(x)))
         return ternary_gemv_fused_dispatch(w->packed, x, x_dtype, (int)M, w->N, w->K, w->weight_scale, y, y_dtype, acc_out,
                                            bias, residual, st);
     const bool fast = (w->K % 64 == 0) && aligned16(w->packed);

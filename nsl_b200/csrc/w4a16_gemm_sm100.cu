@@ -132,21 +132,24 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer
-        if (lane == 0) {
-            uint32_t it = 0, t = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
-                const uint32_t buf = t & 1u, aph = (t >> 1) & 1u;
-                if (!(ok = mbar_wait(acce_bar(buf), aph ^ 1u, 0x1201))) break;
+        // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues (MMAs
+        // issue several times faster from a converged warp than from a lone diverged lane).  It
+        // waits only for the dequantised weights: they are published after the copy stage was
+        // seen complete, so the activation tile of the same stage has landed too.
+        const bool leader = elect_one();
+        uint32_t it = 0, t = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
+            const uint32_t buf = t & 1u, aph = (t >> 1) & 1u;
+            if (!(ok = mbar_wait(acce_bar(buf), aph ^ 1u, 0x1201))) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + buf * 256u;
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % C::STAGES;
+                const uint32_t ph = (it / C::STAGES) & 1u;
+                if (!(ok = mbar_wait(full_bar(s), ph, 0x1203))) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * 256u;
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int s = it % C::STAGES;
-                    const uint32_t ph = (it / C::STAGES) & 1u;
-                    if (!(ok = mbar_wait(raw_bar(s), ph, 0x1202))) break;
-                    if (!(ok = mbar_wait(full_bar(s), ph, 0x1203))) break;
-                    tc_fence_after();
+                if (leader) {
                     const uint32_t a_addr = base + s * C::STAGE_BYTES;
                     const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(a_addr + A_BYTES);
 #pragma unroll
@@ -154,8 +157,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         umma_f16(d_tmem, adesc + 2u * k4, bdesc + 2u * k4, C::IDESC, (kb | k4) != 0);
                     umma_commit(empty_bar(s));
                 }
-                if (ok) umma_commit(accf_bar(buf));
             }
+            if (ok && leader) umma_commit(accf_bar(buf));
         }
     } else if (warp >= 8) {
         // ---------------- dequantise warps (two groups on alternate stages)
@@ -222,6 +225,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
             const uint32_t buf = t & 1u, aph = (t >> 1) & 1u;
             const int64_t m0 = (int64_t)(tile % p.tiles_m) * BM, n0 = (int64_t)(tile / p.tiles_m) * BN;
+            const bool interior = (m0 + BM <= p.M) && (n0 + BN <= p.N);   // no bounds tests inside the tile
             if (!(ok = mbar_wait(accf_bar(buf), aph, 0x1401))) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u;
@@ -244,7 +248,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     const int rl = 4 * i + (lane >> 3);
                     const int64_t m = m0 + q * 32 + rl;
                     const float4 v = *reinterpret_cast<const float4 *>(patch + rl * STAGE_PAD + (lane & 7) * 4);
-                    if (m < p.M && ncol < p.N) {
+                    if (interior || (m < p.M && ncol < p.N)) {
                         const int64_t o = m * p.N + ncol;
                         if (p.y_dtype == NSLQ_DTYPE_F32) {
                             *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.y) + o) = v;
