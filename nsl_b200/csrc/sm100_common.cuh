@@ -47,6 +47,10 @@ static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, 
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
+        // Back off: a failed try_wait comes back at once, and a dozen warps polling flat out (unpack,
+        // epilogue, issuer, producer all wait most of the time) take the issue slots of the few
+        // warps that have work.
+        if (spin >= 2u) __nanosleep(spin < 16u ? 20u : 64u);
         if ((spin & 63u) == 63u) {
             const unsigned long long now = globaltimer_ns();
             if (t0 == 0) t0 = now;
