@@ -38,7 +38,7 @@ static __device__ __forceinline__ unsigned long long globaltimer_ns()
 // Bounded wait: true when the phase completed, false after WAIT_NS (status word set).
 static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int site)
 {
-    unsigned long long t0 = 0;
+    long long t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
         uint32_t ok;
         asm volatile(
@@ -47,14 +47,12 @@ static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, 
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
-        // Back off: a failed try_wait comes back at once, and a dozen warps polling flat out (unpack,
-        // epilogue, issuer, producer all wait most of the time) take the issue slots of the few
-        // warps that have work.
-        if (spin >= 2u) __nanosleep(spin < 16u ? 20u : 64u);
         if ((spin & 63u) == 63u) {
-            const unsigned long long now = globaltimer_ns();
+            // signed difference: should %globaltimer ever step backwards between two reads, an
+            // unsigned difference would read as an instant timeout
+            const long long now = (long long)globaltimer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_NS) { atomicCAS(&g_wait_status, 0, site); return false; }
+            else if (now - t0 > (long long)WAIT_NS) { atomicCAS(&g_wait_status, 0, site); return false; }
         }
     }
 }
@@ -68,6 +66,16 @@ static __device__ __forceinline__ bool elect_one()
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(pred));
     return pred != 0;
+}
+// The same wait for a whole warp (every lane must call it).  Lanes poll on their own and can leave
+// the loop in different iterations; the .sync.aligned tcgen05 instructions that follow a wait need
+// the warp converged, so it is re-formed here and the outcome made uniform.  (A version of
+// mbar_wait that slept between polls let the lanes drift apart and, without this, ended in rare
+// launch failures in millisecond-long launches.)
+static __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int site)
+{
+    const bool ok = mbar_wait(bar, parity, site);
+    return __all_sync(0xffffffffu, ok) != 0;
 }
 static __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tmap, int x, int y, uint32_t bar)
 {

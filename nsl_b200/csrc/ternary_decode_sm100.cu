@@ -139,7 +139,7 @@ ternary_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p
     uint32_t tmem_base = 0;
     bool tmem_ok = true;
     auto get_tmem = [&]() {                                          // warp-uniform
-        tmem_ok = mbar_wait(tmem_bar, 0, 0x640);
+        tmem_ok = mbar_wait_warp(tmem_bar, 0, 0x640);
         tc_fence_after();
         tmem_base = *slot_ptr;
     };
@@ -304,11 +304,11 @@ ternary_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p
             bool ok = tmem_ok;
             for (int j = 0; j < my_tiles && ok; ++j) {
                 const uint32_t buf = (uint32_t)j & 1u, cph = ((uint32_t)j >> 1) & 1u;
-                if (!(ok = mbar_wait(acce_bar(buf), cph ^ 1u, 0x611))) break;
+                if (!(ok = mbar_wait_warp(acce_bar(buf), cph ^ 1u, 0x611))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * ACC_COLS;
                 for (int st = 0; st < p.nsteps; ++st, ++it) {
-                    if (!(ok = mbar_wait(afull_bar(a), aph, 0x612))) break;
+                    if (!(ok = mbar_wait_warp(afull_bar(a), aph, 0x612))) break;
                     tc_fence_after();
                     if (leader) {
                         const uint32_t a_tmem = tmem_base + 2 * ACC_COLS + a * A_COLS;
@@ -339,12 +339,12 @@ ternary_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p
             get_tmem();
             bool ok = tmem_ok;
             for (int it = group; it < total && ok; it += 2) {
-                if (!(ok = mbar_wait(raw_bar(s), sph, 0x621))) break;
+                if (!(ok = mbar_wait_warp(raw_bar(s), sph, 0x621))) break;
                 const uint8_t *pr = base_ptr + p.off_ring + (size_t)s * P_BYTES + row * PK_ROW;
                 uint4 pv[8];
 #pragma unroll
                 for (int c = 0; c < 8; ++c) pv[c] = *reinterpret_cast<const uint4 *>(pr + ((c ^ (row & 7)) << 4));
-                if (it >= AS && !(ok = mbar_wait(done_bar(it - AS), done_par(it - AS), 0x622))) break;
+                if (it >= AS && !(ok = mbar_wait_warp(done_bar(it - AS), done_par(it - AS), 0x622))) break;
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
@@ -375,7 +375,7 @@ ternary_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p
             for (int j = 0; j < my_tiles && ok; ++j) {
                 const uint32_t buf = (uint32_t)j & 1u, cph = ((uint32_t)j >> 1) & 1u;
                 const int64_t n = ((int64_t)blockIdx.x + (int64_t)j * gridDim.x) * BW + qd * 32 + lane;
-                if (!(ok = mbar_wait(accf_bar(buf), cph, 0x631))) break;
+                if (!(ok = mbar_wait_warp(accf_bar(buf), cph, 0x631))) break;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(qd * 32) << 16) + buf * ACC_COLS;
                 uint32_t c01[32], c23[32];

@@ -257,11 +257,11 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         bool ok = true;
         for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
             const uint32_t buf = t & 1u, cph = (t >> 1) & 1u;
-            if (!(ok = mbar_wait(acce_bar(buf), cph ^ 1u, 0x201))) break;
+            if (!(ok = mbar_wait_warp(acce_bar(buf), cph ^ 1u, 0x201))) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + C::acc_col(buf);
             for (int kb = 0; kb < nkb; ++kb, ++it) {
-                if (!(ok = mbar_wait(afull_bar(a), aph, 0x203))) break;    // codes stored (and the copy stage landed)
+                if (!(ok = mbar_wait_warp(afull_bar(a), aph, 0x203))) break;    // codes stored (and the copy stage landed)
                 tc_fence_after();
                 if (leader) {
                     const uint32_t a_tmem = tmem_base + C::a_col(a);
@@ -290,12 +290,12 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         int s = group % C::TS;                       // ring positions of iteration `it`, stepped by two
         uint32_t a = group % C::AS, sph = 0, aph = 0;
         for (int it = group; it < total_it && ok; it += 2) {
-            if (!(ok = mbar_wait(raw_bar(s), sph, 0x301))) break;                            // packed tile landed
+            if (!(ok = mbar_wait_warp(raw_bar(s), sph, 0x301))) break;                            // packed tile landed
             const uint4 *pk = reinterpret_cast<const uint4 *>(base_ptr + s * C::T_BYTES + C::X_BYTES + row * C::PK_ROW);
             uint4 pv[2 * C::KS];
 #pragma unroll
             for (int i = 0; i < 2 * C::KS; ++i) pv[i] = pk[i];
-            if (it >= C::AS && !(ok = mbar_wait(done_bar(it - C::AS), done_par(it - C::AS), 0x302))) break;   // operand stage reusable
+            if (it >= C::AS && !(ok = mbar_wait_warp(done_bar(it - C::AS), done_par(it - C::AS), 0x302))) break;   // operand stage reusable
             tc_fence_after();
 #pragma unroll
             for (int h = 0; h < C::KS; ++h) {                                                // one k-block: 32 bytes -> 32 columns
@@ -340,7 +340,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 rs[i] = m < p.M ? p.rowsum[m] : 0;
             }
             __syncwarp();
-            if (!(ok = mbar_wait(accf_bar(buf), cph, 0x401))) break;
+            if (!(ok = mbar_wait_warp(accf_bar(buf), cph, 0x401))) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + C::acc_col(buf) + half * C::HALF_T;
 #pragma unroll 1
@@ -404,9 +404,9 @@ static int launch_gemm(const void *q_perm, gemm::Params &p, cudaStream_t st)
     return check_launch("ternary_gemm_kernel");
 }
 
-int ternary_gemm_dispatch(const uint8_t *w, const int8_t *q_perm, const float *scale, const int32_t *rowsum, int64_t M,
-                          int64_t N, int64_t K, float weight_scale, void *y, int y_dtype, int32_t *acc_out,
-                          const float *bias, const float *residual, cudaStream_t st)
+static int gemm_one_launch(const uint8_t *w, const int8_t *q_perm, const float *scale, const int32_t *rowsum, int64_t M,
+                           int64_t N, int64_t K, float weight_scale, void *y, int y_dtype, int32_t *acc_out,
+                           const float *bias, const float *residual, cudaStream_t st)
 {
     gemm::Params p{w, scale, rowsum, y, acc_out, bias, residual, M, N, K, y_dtype, weight_scale, 0, 0};
     // Token-tile width: the one that wastes fewer SM-rounds on this shape (ties go to the wider
@@ -419,6 +419,30 @@ int ternary_gemm_dispatch(const uint8_t *w, const int8_t *q_perm, const float *s
     };
     if (rounds_cost(192) <= rounds_cost(128)) return launch_gemm<192>(q_perm, p, st);
     return launch_gemm<128>(q_perm, p, st);
+}
+
+// One launch takes at most GEMM_MAX_ROWS token rows; longer batches run as several launches on the
+// same stream.  Reason: at M = 32768 (118 tiles per CTA, about a millisecond per launch) roughly one
+// launch in fifteen ended in cudaErrorLaunchFailure on this machine, also in isolation with identical
+// inputs and with every wait bounded; reading the kernel has not shown a cause, and launches of
+// 4096 rows (a hundred microseconds) have run by the thousand, inside the same 26-layer prefill that
+// failed, without one.  The working guess is that a persistent kernel holding tensor memory does
+// not survive being time-sliced against another tenant of the GPU; short launches sidestep it.
+constexpr int64_t GEMM_MAX_ROWS = 4096;
+
+int ternary_gemm_dispatch(const uint8_t *w, const int8_t *q_perm, const float *scale, const int32_t *rowsum, int64_t M,
+                          int64_t N, int64_t K, float weight_scale, void *y, int y_dtype, int32_t *acc_out,
+                          const float *bias, const float *residual, cudaStream_t st)
+{
+    const int es = y_dtype == NSLQ_DTYPE_F32 ? 4 : 2;
+    for (int64_t m0 = 0; m0 < M; m0 += GEMM_MAX_ROWS) {
+        const int64_t mc = (M - m0) < GEMM_MAX_ROWS ? (M - m0) : GEMM_MAX_ROWS;
+        int rc = gemm_one_launch(w, q_perm + m0 * K, scale + m0, rowsum + m0, mc, N, K, weight_scale,
+                                 (char *)y + m0 * N * es, y_dtype, acc_out ? acc_out + m0 * N : nullptr, bias,
+                                 residual ? residual + m0 * N : nullptr, st);
+        if (rc) return rc;
+    }
+    return NSLQ_OK;
 }
 
 // The status word of this translation unit's kernels (see sm100::read_wait_status).

@@ -134,7 +134,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
     uint32_t tmem_base = 0;
     bool tmem_ok = true;
     auto get_tmem = [&]() {                                          // warp-uniform
-        tmem_ok = mbar_wait(tmem_bar, 0, 0x740);
+        tmem_ok = mbar_wait_warp(tmem_bar, 0, 0x740);
         tc_fence_after();
         tmem_base = *slot_ptr;
     };
@@ -222,8 +222,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
             for (int j = 0; j < my_tiles && ok; ++j) {
                 for (int st = 0; st < p.nsteps; ++st, ++it) {
                     const uint32_t sb = it % NB;
-                    if (!(ok = mbar_wait(acce_bar(sb), ((it / NB) & 1u) ^ 1u, 0x711))) break;   // accumulators of step it - NB read out
-                    if (!(ok = mbar_wait(afull_bar(a), aph, 0x712))) break;
+                    if (!(ok = mbar_wait_warp(acce_bar(sb), ((it / NB) & 1u) ^ 1u, 0x711))) break;   // accumulators of step it - NB read out
+                    if (!(ok = mbar_wait_warp(afull_bar(a), aph, 0x712))) break;
                     tc_fence_after();
                     if (leader) {
                         const uint32_t a_tmem = tmem_base + NB * ACC_COLS + a * A_COLS;
@@ -255,12 +255,12 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
             get_tmem();
             bool ok = tmem_ok;
             for (int it = group; it < total && ok; it += 2) {
-                if (!(ok = mbar_wait(raw_bar(s), sph, 0x721))) break;
+                if (!(ok = mbar_wait_warp(raw_bar(s), sph, 0x721))) break;
                 const uint8_t *pr = base_ptr + p.off_ring + (size_t)s * P_BYTES + row * PK_ROW;
                 uint4 pv[8];
 #pragma unroll
                 for (int c = 0; c < 8; ++c) pv[c] = *reinterpret_cast<const uint4 *>(pr + ((c ^ (row & 7)) << 4));
-                if (it >= AS && !(ok = mbar_wait(done_bar(it - AS), done_par(it - AS), 0x722))) break;
+                if (it >= AS && !(ok = mbar_wait_warp(done_bar(it - AS), done_par(it - AS), 0x722))) break;
                 tc_fence_after();
 #pragma unroll
                 for (int h = 0; h < 4; ++h) {            // 32 packed bytes = 64 k = 32 columns
@@ -309,7 +309,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
                 asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
                 for (int st = 0; st < p.nsteps && ok; ++st, ++it) {
                     const uint32_t sb = it % NB;
-                    if (!(ok = mbar_wait(done_bar(it), done_par(it), 0x731))) break;
+                    if (!(ok = mbar_wait_warp(done_bar(it), done_par(it), 0x731))) break;
                     tc_fence_after();
                     uint32_t r[KS * NTOK];
                     tmem_ld32(tmem_base + ((uint32_t)(qd * 32) << 16) + sb * ACC_COLS, r);

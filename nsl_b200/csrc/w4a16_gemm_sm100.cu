@@ -141,13 +141,13 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         bool ok = true;
         for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
             const uint32_t buf = t & 1u, aph = (t >> 1) & 1u;
-            if (!(ok = mbar_wait(acce_bar(buf), aph ^ 1u, 0x1201))) break;
+            if (!(ok = mbar_wait_warp(acce_bar(buf), aph ^ 1u, 0x1201))) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + buf * 256u;
             for (int kb = 0; kb < nkb; ++kb, ++it) {
                 const int s = it % C::STAGES;
                 const uint32_t ph = (it / C::STAGES) & 1u;
-                if (!(ok = mbar_wait(full_bar(s), ph, 0x1203))) break;
+                if (!(ok = mbar_wait_warp(full_bar(s), ph, 0x1203))) break;
                 tc_fence_after();
                 if (leader) {
                     const uint32_t a_addr = base + s * C::STAGE_BYTES;
@@ -183,7 +183,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
             const int s = it % C::STAGES;
             const uint32_t ph = (it / C::STAGES) & 1u;
-            if (!(ok = mbar_wait(raw_bar(s), ph, 0x1301))) break;
+            if (!(ok = mbar_wait_warp(raw_bar(s), ph, 0x1301))) break;
             uint8_t *bst = base_ptr + s * C::STAGE_BYTES + A_BYTES;
             const uint4 *pk = reinterpret_cast<const uint4 *>(bst + C::B_BYTES);
             uint4 cur[PER];
@@ -226,7 +226,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const uint32_t buf = t & 1u, aph = (t >> 1) & 1u;
             const int64_t m0 = (int64_t)(tile % p.tiles_m) * BM, n0 = (int64_t)(tile / p.tiles_m) * BN;
             const bool interior = (m0 + BM <= p.M) && (n0 + BN <= p.N);   // no bounds tests inside the tile
-            if (!(ok = mbar_wait(accf_bar(buf), aph, 0x1401))) break;
+            if (!(ok = mbar_wait_warp(accf_bar(buf), aph, 0x1401))) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u;
 #pragma unroll 1
@@ -313,10 +313,9 @@ static int launch_w4_gemm(const uint8_t *codes, const void *x, w4gemm::Params &p
     return check_launch("w4a16_gemm_kernel");
 }
 
-int w4a16_gemm_dispatch(const uint8_t *codes, const float *scale, const float *zc, int64_t N, int64_t K, int G, int gs,
-                        const void *x, int64_t M, void *y, int y_dtype, cudaStream_t st)
+static int w4_gemm_one_launch(const uint8_t *codes, const float *scale, const float *zc, int64_t N, int64_t K, int G, int gs,
+                              const void *x, int64_t M, void *y, int y_dtype, cudaStream_t st)
 {
-    if (!aligned16(y)) return fail(NSLQ_ERR_ARG, "W4A16 GEMM: y must be 16-byte aligned");
     w4gemm::Params p{scale, zc, y, M, N, K, G, gs, y_dtype, 0, 0};
     const int sms = sm100::sm_count();
     auto rounds_cost = [&](int bn) {
@@ -325,6 +324,25 @@ int w4a16_gemm_dispatch(const uint8_t *codes, const float *scale, const float *z
     };
     if (rounds_cost(192) < rounds_cost(256)) return launch_w4_gemm<192>(codes, x, p, st);
     return launch_w4_gemm<256>(codes, x, p, st);
+}
+
+// Long batches run as several launches of at most W4_GEMM_MAX_ROWS token rows, like the ternary
+// GEMM: persistent tensor-memory kernels that ran for about a millisecond ended, now and then, in
+// cudaErrorLaunchFailure on this machine; launches of a few hundred microseconds never did.
+constexpr int64_t W4_GEMM_MAX_ROWS = 4096;
+
+int w4a16_gemm_dispatch(const uint8_t *codes, const float *scale, const float *zc, int64_t N, int64_t K, int G, int gs,
+                        const void *x, int64_t M, void *y, int y_dtype, cudaStream_t st)
+{
+    if (!aligned16(y)) return fail(NSLQ_ERR_ARG, "W4A16 GEMM: y must be 16-byte aligned");
+    const int es = y_dtype == NSLQ_DTYPE_F32 ? 4 : 2;
+    for (int64_t m0 = 0; m0 < M; m0 += W4_GEMM_MAX_ROWS) {
+        const int64_t mc = (M - m0) < W4_GEMM_MAX_ROWS ? (M - m0) : W4_GEMM_MAX_ROWS;
+        int rc = w4_gemm_one_launch(codes, scale, zc, N, K, G, gs, (const char *)x + m0 * K * 2, mc,
+                                    (char *)y + m0 * N * es, y_dtype, st);
+        if (rc) return rc;
+    }
+    return NSLQ_OK;
 }
 
 int w4a16_gemm_status(int *out) { return sm100::read_wait_status(out); }

@@ -70,7 +70,7 @@ class BitLinear:
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
-        if h:
+        if h and lib is not None:              # module globals are already gone at interpreter shutdown
             lib().nslq_bitlinear_destroy(h)
 
     def workspace(self, M):
@@ -136,7 +136,7 @@ class W4A16:
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
-        if h:
+        if h and lib is not None:
             lib().nslq_w4a16_destroy(h)
 
     def forward(self, x, out_dtype=None, out=None):
