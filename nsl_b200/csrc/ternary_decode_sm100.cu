@@ -17,7 +17,7 @@
 //   class i of all eight packed words.
 //
 // Persistent, warp-specialised, one CTA per SM, tiles of 128 weight rows:
-//   warp 0      TMA producer: per step ONE cp.async.bulk.tensor copy (no multicast) of 128 rows x
+//   warp 0      TMA producer: per step ONE cp.async.bulk.tensor copy (this CTA only) of 128 rows x
 //               128 packed bytes (512 k), SWIZZLE_128B so that the per-row reads of the unpack
 //               threads are conflict-free; a ring of up to 8 stages (128 KiB in flight per SM).
 //   warps 8-15  unpack, two groups of four warps on alternate steps: a thread owns a weight row,

@@ -14,10 +14,10 @@
 //
 // Persistent, warp-specialised kernel, one CTA per SM, tiles of 128 weight rows x BT tokens:
 //
-//   warp 0      TMA producer: per k-block, two cp.async.bulk.tensor copies (2-D, no
-//               multicast) into a ring of copy stages: the int8 activation tile (BT
-//               tokens x 128 k, SWIZZLE_128B) and the packed weight tile (128 rows x 32
-//               bytes); out-of-range rows and the K tail are zero-filled.
+//   warp 0      TMA producer: per step, cp.async.bulk.tensor copies (2-D, this CTA only)
+//               into a ring of copy stages: the int8 activation tile (BT tokens x 128 k
+//               per k-block, SWIZZLE_128B) and the packed weight tile (128 rows x 32
+//               bytes per k-block); out-of-range rows and the K tail are zero-filled.
 //   warps 8-15  unpack, two groups of four warps (one warp per TMEM lane quadrant) taking
 //               alternate k-blocks: each thread reads the 32 packed bytes of its weight
 //               row, expands them with (w >> s) & 0x03030303 into 32 words of u8 codes

@@ -19,7 +19,7 @@
 //   (2^-24 relative) is ~1e-5 of a typical block result: far inside the 1e-2 / 1e-3 bars.
 //
 // Persistent, warp-specialised, one CTA per SM, tiles of 128 weight rows:
-//   warp 0      TMA producer: per step one cp.async.bulk.tensor copy (no multicast) of 128 rows x
+//   warp 0      TMA producer: per step one cp.async.bulk.tensor copy (this CTA only) of 128 rows x
 //               128 packed bytes (256 k), SWIZZLE_128B, ring of up to 8 stages.
 //   warp 2      allocates tensor memory while the others already work.
 //   all but 0,2 stage the tokens (permute, block sums); then warp 1 issues the MMAs (converged
