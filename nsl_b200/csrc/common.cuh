@@ -64,12 +64,18 @@ static __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("g
 static __device__ __forceinline__ int quant_one(float x, float inv)
 {
     const float s = __fmul_rn(x, inv);
-    float t = truncf(s);
-    if (fabsf(s - t) >= 0.5f) t += copysignf(1.0f, s);   // half away from zero (false for NaN / inf)
+    // Round half away from zero as trunc(s + copysign(0.5, s)).  The sum is exact or rounds inside
+    // the same integer interval for every |s| >= 0.5 (s and s + 0.5 share a binade or the sum lands
+    // on a representable value one ulp below the next integer); only below 0.5, where s has finer
+    // ulps than the sum, can the addition round up to 1.0 -- those values round to 0 and are taken
+    // out first.  One conversion instead of a trunc and a conversion: the quantisers are bound by
+    // issued instructions, and conversions issue at a quarter of the ALU rate.
+    const float h = __int_as_float((__float_as_int(s) & 0x80000000) | 0x3f000000);      // copysign(0.5, s)
+    const int r = fabsf(s) < 0.5f ? 0 : __float2int_rz(__fadd_rn(s, h));               // saturating; NaN -> 0
     // The float clamp of the reference commutes with the rounding: clamping the rounded integer
     // gives the same value for every input, and the saturating conversion maps +-inf to the
     // int extremes (then +-127) and NaN to 0, exactly as `clamp(..).round() as i8` does.
-    return max(-127, min(127, __float2int_rz(t)));
+    return max(-127, min(127, r));
 }
 
 // Four consecutive elements of a row as fp32 (vector load; row must be 16-byte aligned for
