@@ -7,6 +7,10 @@ and stdlib/nsl/inference/generate.nsl).  Every projection of every layer (q, k, 
 down) runs through nsl_b200.ops.BitLinear, i.e. the C ABI.  Weights are random ternary (no
 checkpoint is available offline), so the numbers are throughput numbers, not quality numbers.
 
+The residual stream is kept in fp32: the norms then need no casts, and the residual additions ride
+in the BitLinear epilogue (`residual=`, added in fp32 after `weight_scale`, as NSL's finalize phase
+orders it, crates/nsl-codegen/src/bitnet/phases/finalize.rs:55-80) instead of being separate kernels.
+
 One decode step is captured in a single CUDA graph: the position and the current tokens live in
 device tensors that the graph itself advances, so 256 steps are 256 replays.
 """
@@ -34,7 +38,8 @@ def _ternary(n, k, gen):
 
 
 def _rms_norm(x, w, eps):
-    return F.rms_norm(x.float(), (x.shape[-1],), w, eps).to(x.dtype)
+    """fp32 in, fp32 out (one kernel)."""
+    return F.rms_norm(x, (x.shape[-1],), w, eps)
 
 
 def _rope(x, cos, sin):
@@ -76,8 +81,9 @@ class BitNetDecoder:
         self.graph = None
 
     # ------------------------------------------------------------------ linears through the C ABI
-    def _lin(self, layer, x2d):
-        return layer.forward(x2d, out_dtype=torch.bfloat16)
+    def _lin(self, layer, x2d, residual):
+        """fp32 output with the fp32 residual added in the epilogue."""
+        return layer.forward(x2d, out_dtype=torch.float32, residual=residual)
 
     def _lin_shared(self, layers, x2d):
         """Several projections of one input: quantise once when the rows go down the two-kernel path."""
@@ -91,10 +97,10 @@ class BitNetDecoder:
     def prefill(self, ids):
         """ids [B, T]; fills the KV cache, leaves pos = T and tokens = greedy next token."""
         cfg, B, T = self.cfg, ids.shape[0], ids.shape[1]
-        x = self.embed[ids]                                               # [B, T, h]
+        x = self.embed[ids].float().reshape(B * T, cfg.hidden)            # residual stream, fp32
         cos, sin = self.cos[:T], self.sin[:T]
         for li, L in enumerate(self.layers):
-            hn = _rms_norm(x, L["n1"], cfg.eps).reshape(B * T, cfg.hidden)
+            hn = _rms_norm(x, L["n1"], cfg.eps)
             q, k, v = self._lin_shared([L["q"], L["k"], L["v"]], hn)
             q = _rope(q.view(B, T, cfg.heads, cfg.head_dim).transpose(1, 2), cos, sin)
             k = _rope(k.view(B, T, cfg.heads, cfg.head_dim).transpose(1, 2), cos, sin)
@@ -103,18 +109,18 @@ class BitNetDecoder:
             self.v_cache[li, :, :, :T] = v
             a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
             a = a.transpose(1, 2).reshape(B * T, cfg.heads * cfg.head_dim)
-            x = x + self._lin(L["o"], a).view(B, T, cfg.hidden)
-            hn = _rms_norm(x, L["n2"], cfg.eps).reshape(B * T, cfg.hidden)
+            x = self._lin(L["o"], a, x)
+            hn = _rms_norm(x, L["n2"], cfg.eps)
             g, u = self._lin_shared([L["gate"], L["up"]], hn)
-            x = x + self._lin(L["down"], (F.silu(g.float()) * u.float()).to(torch.bfloat16)).view(B, T, cfg.hidden)
-        last = _rms_norm(x[:, -1], self.final_norm, cfg.eps)
+            x = self._lin(L["down"], F.silu(g) * u, x)
+        last = _rms_norm(x.view(B, T, cfg.hidden)[:, -1], self.final_norm, cfg.eps).to(torch.bfloat16)
         self.tokens.copy_((last @ self.lm_head.t()).argmax(-1))
         self.pos.fill_(T)
 
     # ------------------------------------------------------------------ one decode step (graph-capturable)
     def _step(self):
         cfg, B = self.cfg, self.B
-        x = self.embed[self.tokens]                                       # [B, h]
+        x = self.embed[self.tokens].float()                               # [B, h] residual stream, fp32
         cos, sin = self.cos[self.pos], self.sin[self.pos]                 # [1, D/2]
         mask = (self.key_index <= self.pos).view(1, 1, 1, self.max_ctx)   # keys 0..pos are visible
         for li, L in enumerate(self.layers):
@@ -128,11 +134,11 @@ class BitNetDecoder:
             sc = torch.matmul(q, self.k_cache[li].transpose(-1, -2)).float() * self.sm_scale
             pr = torch.softmax(sc.masked_fill(~mask, float("-inf")), -1).to(torch.bfloat16)
             a = torch.matmul(pr, self.v_cache[li])
-            x = x + self._lin(L["o"], a.reshape(B, cfg.heads * cfg.head_dim))
+            x = self._lin(L["o"], a.reshape(B, cfg.heads * cfg.head_dim), x)
             hn = _rms_norm(x, L["n2"], cfg.eps)
             g, u = self._lin_shared([L["gate"], L["up"]], hn)
-            x = x + self._lin(L["down"], (F.silu(g.float()) * u.float()).to(torch.bfloat16))
-        logits = _rms_norm(x, self.final_norm, cfg.eps) @ self.lm_head.t()
+            x = self._lin(L["down"], F.silu(g) * u, x)
+        logits = _rms_norm(x, self.final_norm, cfg.eps).to(torch.bfloat16) @ self.lm_head.t()
         self.tokens.copy_(logits.argmax(-1))
         self.pos.add_(1)
 
