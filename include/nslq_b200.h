@@ -84,6 +84,24 @@ int nslq_act_quant_i8(const void *x, int x_dtype, int64_t M, int64_t K,
                       int8_t *q_plain, int8_t *q_perm, float *scale, int32_t *rowsum,
                       void *stream);
 
+/*
+ * RMSNorm fused in front of the quantisation: the `fused_rmsnorm` prologue that NSL's BitNet
+ * kernel config names but never emits (crates/nsl-codegen/src/bitnet/config.rs:23-31).
+ *
+ *   rms[r] = sqrt(sum_k x[r,k]^2 / K + eps)           f64, like nsl_tensor_rmsnorm
+ *   h[r,k] = (f32)(x[r,k] / rms[r] * weight[k])       (crates/nsl-runtime/src/tensor/mod.rs:3016-3035)
+ *   then scale/q/rowsum of h exactly as nslq_act_quant_i8.
+ *
+ * weight: f32 [K].  h_out (f32 [M,K]) may be NULL: the normalised row then never reaches memory.
+ * K must be a multiple of 16 and at most 12288; all buffers 16-byte aligned.  The sum of squares
+ * is a tree reduction (the reference adds sequentially), so h can differ from the reference in
+ * the last bit of a few elements; everything after h is exact.
+ */
+int nslq_rmsnorm_act_quant_i8(const void *x, int x_dtype, const float *weight, double eps,
+                              int64_t M, int64_t K, float *h_out,
+                              int8_t *q_plain, int8_t *q_perm, float *scale, int32_t *rowsum,
+                              void *stream);
+
 /* ========================================================================== */
 /* BitLinear (ternary W1.58 A8)                                                */
 /* ========================================================================== */

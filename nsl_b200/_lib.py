@@ -9,7 +9,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # NSLQ_LIB points at another build of the same library (kernel experiments); default: the in-tree build
 LIB_PATH = os.environ.get("NSLQ_LIB") or os.path.join(_HERE, "libnslq_b200.so")
 
-vp, i64, i32, f32 = C.c_void_p, C.c_int64, C.c_int, C.c_float
+vp, i64, i32, f32, f64 = C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_double
 
 # name -> (restype, argtypes); every symbol include/nslq_b200.h declares.
 SIGNATURES = {
@@ -18,6 +18,7 @@ SIGNATURES = {
     "nslq_set_dependent_launch": (None, [i32]),
     "nslq_device_status": (i32, [C.POINTER(i32)]),
     "nslq_act_quant_i8": (i32, [vp, i32, i64, i64, vp, vp, vp, vp, vp]),
+    "nslq_rmsnorm_act_quant_i8": (i32, [vp, i32, vp, f64, i64, i64, vp, vp, vp, vp, vp, vp]),
     "nslq_bitlinear_create": (i32, [vp, i64, i64, f32, C.POINTER(vp)]),
     "nslq_bitlinear_destroy": (None, [vp]),
     "nslq_bitlinear_workspace_bytes": (i64, [i64, i64]),

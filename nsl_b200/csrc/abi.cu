@@ -31,6 +31,8 @@ int check_launch(const char *what)
 
 // kernels (other translation units)
 int act_quant_dispatch(const void *, int, int64_t, int64_t, int8_t *, int8_t *, float *, int32_t *, cudaStream_t);
+int rmsnorm_act_quant_dispatch(const void *, int, const float *, double, int64_t, int64_t, float *, int8_t *, int8_t *,
+                               float *, int32_t *, cudaStream_t);
 bool ternary_gemv_supported(const void *, const void *, int64_t);
 int ternary_gemv_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int, int64_t, int64_t,
                           float, void *, int, int32_t *, const float *, const float *, cudaStream_t);
@@ -191,6 +193,12 @@ int nslq_act_quant_i8(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *
                       float *scale, int32_t *rowsum, void *stream)
 {
     return act_quant_dispatch(x, x_dtype, M, K, q_plain, q_perm, scale, rowsum, (cudaStream_t)stream);
+}
+
+int nslq_rmsnorm_act_quant_i8(const void *x, int x_dtype, const float *weight, double eps, int64_t M, int64_t K,
+                              float *h_out, int8_t *q_plain, int8_t *q_perm, float *scale, int32_t *rowsum, void *stream)
+{
+    return rmsnorm_act_quant_dispatch(x, x_dtype, weight, eps, M, K, h_out, q_plain, q_perm, scale, rowsum, (cudaStream_t)stream);
 }
 
 int nslq_bitlinear_create(const uint8_t *packed, int64_t N, int64_t K, float weight_scale,

@@ -126,6 +126,121 @@ act_quant_kernel(const T *__restrict__ x, int64_t K, int8_t *__restrict__ q_plai
     if (threadIdx.x == 0) scale_out[r] = scale;
 }
 
+static __device__ __forceinline__ double block_sum_f64(double v, double *smem)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) smem[w] = v;
+    __syncthreads();
+    double r = (l < AQ_THREADS / 32) ? smem[l] : 0.0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    return r;
+}
+
+// RMSNorm fused in front of the quantisation (the prologue NSL's BitNet kernel config names
+// `fused_rmsnorm` but never emits, crates/nsl-codegen/src/bitnet/config.rs:23-31): one CTA per row,
+//   rms = sqrt(sum_k x^2 / K + eps)                 in f64
+//   h   = (f32)(x / rms * weight)                   in f64, rounded once
+// exactly the arithmetic of nsl_tensor_rmsnorm (crates/nsl-runtime/src/tensor/mod.rs:3016-3035),
+// except that the sum of squares is a tree reduction instead of a sequential loop (it can differ
+// in the last bits of the f64); h never goes to memory unless h_out is given.  Then the row is
+// quantised from registers like act_quant_kernel.
+template <typename T, int XV>
+__global__ void __launch_bounds__(AQ_THREADS)
+rmsnorm_act_quant_kernel(const T *__restrict__ x, const float *__restrict__ weight, double eps, int64_t K,
+                         float *__restrict__ h_out, int8_t *__restrict__ q_plain, int8_t *__restrict__ q_perm,
+                         float *__restrict__ scale_out, int32_t *__restrict__ rowsum_out)
+{
+    __shared__ float smax[AQ_THREADS / 32];
+    __shared__ int ssum[AQ_THREADS / 32];
+    __shared__ double ssq[AQ_THREADS / 32];
+    const int64_t r = blockIdx.x;
+    const T *row = x + r * K;
+    pdl_wait();
+    const int nvec = (int)(K >> 2);
+    float4 xv[XV];
+    double sq = 0.0;
+#pragma unroll
+    for (int i = 0; i < XV; ++i) {
+        const int v = i * AQ_THREADS + threadIdx.x;
+        xv[i] = (v < nvec) ? Vec4<T>::load(row, v) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < XV; ++i)
+        sq += (double)xv[i].x * xv[i].x + (double)xv[i].y * xv[i].y + (double)xv[i].z * xv[i].z + (double)xv[i].w * xv[i].w;
+    const double rms = sqrt(block_sum_f64(sq, ssq) / (double)K + eps);
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < XV; ++i) {
+        const int v = i * AQ_THREADS + threadIdx.x;
+        if (v < nvec) {
+            const float4 w = reinterpret_cast<const float4 *>(weight)[v];
+            float4 h;
+            h.x = (float)((double)xv[i].x / rms * (double)w.x); h.y = (float)((double)xv[i].y / rms * (double)w.y);
+            h.z = (float)((double)xv[i].z / rms * (double)w.z); h.w = (float)((double)xv[i].w / rms * (double)w.w);
+            xv[i] = h;
+            if (h_out) reinterpret_cast<float4 *>(h_out + r * K)[v] = h;
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(h.x), fabsf(h.y)), fmaxf(fabsf(h.z), fabsf(h.w))));
+        }
+    }
+    const float scale = block_max(m, smax);
+    pdl_launch_dependents();
+    const float inv = __fdiv_rn(127.0f, scale);
+    int sum = 0;
+#pragma unroll
+    for (int i = 0; i < XV; ++i) {
+        const int v = i * AQ_THREADS + threadIdx.x;
+        const bool in = v < nvec;
+        const unsigned mask = __ballot_sync(0xffffffffu, in);          // whole quads: K % 16 == 0
+        if (in) {
+            const float4 f = xv[i];
+            const uint32_t w = pack4_i8(quant_one(f.x, inv), quant_one(f.y, inv), quant_one(f.z, inv), quant_one(f.w, inv));
+            sum = __dp4a((int)w, 0x01010101, sum);
+            if (q_plain) reinterpret_cast<uint32_t *>(q_plain + r * K)[v] = w;
+            if (q_perm) reinterpret_cast<uint32_t *>(q_perm + r * K)[v] = quad_transpose(w, mask);
+        }
+    }
+    if (rowsum_out) {
+        const int tot = block_sum(sum, ssum);
+        if (threadIdx.x == 0) rowsum_out[r] = tot;
+    }
+    if (threadIdx.x == 0) scale_out[r] = scale;
+}
+
+template <typename T>
+static int launch_rmsnorm_quant(const void *x, const float *weight, double eps, int64_t M, int64_t K, float *h_out,
+                                int8_t *q_plain, int8_t *q_perm, float *scale, int32_t *rowsum, cudaStream_t st)
+{
+    dim3 grid((unsigned)M), block(AQ_THREADS);
+    cudaError_t e;
+    if (K <= 4 * 4 * AQ_THREADS)
+        e = launch_kernel(rmsnorm_act_quant_kernel<T, 4>, grid, block, 0, st, (const T *)x, weight, eps, K, h_out, q_plain, q_perm, scale, rowsum);
+    else
+        e = launch_kernel(rmsnorm_act_quant_kernel<T, 12>, grid, block, 0, st, (const T *)x, weight, eps, K, h_out, q_plain, q_perm, scale, rowsum);
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "rmsnorm_act_quant_kernel: %s", cudaGetErrorString(e));
+    return check_launch("rmsnorm_act_quant_kernel");
+}
+
+int rmsnorm_act_quant_dispatch(const void *x, int x_dtype, const float *weight, double eps, int64_t M, int64_t K,
+                               float *h_out, int8_t *q_plain, int8_t *q_perm, float *scale, int32_t *rowsum, cudaStream_t st)
+{
+    if (!x || !weight || !scale) return fail(NSLQ_ERR_ARG, "nslq_rmsnorm_act_quant_i8: null x, weight or scale");
+    if (M < 0 || K <= 0 || M > 0x7fffffffLL) return fail(NSLQ_ERR_SHAPE, "nslq_rmsnorm_act_quant_i8: bad M=%lld K=%lld", (long long)M, (long long)K);
+    if (K % 16 != 0 || K > 12 * 4 * AQ_THREADS)
+        return fail(NSLQ_ERR_SHAPE, "nslq_rmsnorm_act_quant_i8: K=%lld must be a multiple of 16 and at most %d", (long long)K, 12 * 4 * AQ_THREADS);
+    if (!aligned16(x) || !aligned16(weight) || (h_out && !aligned16(h_out)) || (q_plain && !aligned16(q_plain)) || (q_perm && !aligned16(q_perm)))
+        return fail(NSLQ_ERR_ARG, "nslq_rmsnorm_act_quant_i8: buffers must be 16-byte aligned");
+    if (M == 0) return NSLQ_OK;
+    switch (x_dtype) {
+    case NSLQ_DTYPE_F32: return launch_rmsnorm_quant<float>(x, weight, eps, M, K, h_out, q_plain, q_perm, scale, rowsum, st);
+    case NSLQ_DTYPE_FP16: return launch_rmsnorm_quant<__half>(x, weight, eps, M, K, h_out, q_plain, q_perm, scale, rowsum, st);
+    case NSLQ_DTYPE_BF16: return launch_rmsnorm_quant<__nv_bfloat16>(x, weight, eps, M, K, h_out, q_plain, q_perm, scale, rowsum, st);
+    default: return fail(NSLQ_ERR_ARG, "nslq_rmsnorm_act_quant_i8: x_dtype %d not in {F32,FP16,BF16}", x_dtype);
+    }
+}
+
 template <typename T>
 static int launch_act_quant(const void *x, int64_t M, int64_t K, int8_t *q_plain, int8_t *q_perm,
                             float *scale, int32_t *rowsum, cudaStream_t st)

@@ -85,12 +85,15 @@ class BitNetDecoder:
         """fp32 output with the fp32 residual added in the epilogue."""
         return layer.forward(x2d, out_dtype=torch.float32, residual=residual)
 
-    def _lin_shared(self, layers, x2d):
-        """Several projections of one input: quantise once when the rows go down the two-kernel path."""
+    def _norm_lin_shared(self, layers, x2d, norm_w):
+        """RMSNorm, then several projections of the normalised rows.  More than four rows: one
+        launch normalises and quantises (the normalised rows never reach memory) and the
+        projections share the result; four or fewer: the decode kernel quantises for itself."""
         M = x2d.shape[0]
-        if M <= 4:          # decode kernel with the quantisation fused in: one launch per projection
-            return [l.forward(x2d, out_dtype=torch.bfloat16) for l in layers]
-        qa = ops.act_quant_i8(x2d, plain=False, perm=True)
+        if M <= 4:
+            hn = _rms_norm(x2d, norm_w, self.cfg.eps)
+            return [l.forward(hn, out_dtype=torch.bfloat16) for l in layers]
+        qa = ops.rmsnorm_act_quant_i8(x2d, norm_w, self.cfg.eps, plain=False, perm=True)
         return [l.forward_quantized(qa, out_dtype=torch.bfloat16) for l in layers]
 
     # ------------------------------------------------------------------ prefill
@@ -100,8 +103,7 @@ class BitNetDecoder:
         x = self.embed[ids].float().reshape(B * T, cfg.hidden)            # residual stream, fp32
         cos, sin = self.cos[:T], self.sin[:T]
         for li, L in enumerate(self.layers):
-            hn = _rms_norm(x, L["n1"], cfg.eps)
-            q, k, v = self._lin_shared([L["q"], L["k"], L["v"]], hn)
+            q, k, v = self._norm_lin_shared([L["q"], L["k"], L["v"]], x, L["n1"])
             q = _rope(q.view(B, T, cfg.heads, cfg.head_dim).transpose(1, 2), cos, sin)
             k = _rope(k.view(B, T, cfg.heads, cfg.head_dim).transpose(1, 2), cos, sin)
             v = v.view(B, T, cfg.heads, cfg.head_dim).transpose(1, 2)
@@ -110,8 +112,7 @@ class BitNetDecoder:
             a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
             a = a.transpose(1, 2).reshape(B * T, cfg.heads * cfg.head_dim)
             x = self._lin(L["o"], a, x)
-            hn = _rms_norm(x, L["n2"], cfg.eps)
-            g, u = self._lin_shared([L["gate"], L["up"]], hn)
+            g, u = self._norm_lin_shared([L["gate"], L["up"]], x, L["n2"])
             x = self._lin(L["down"], F.silu(g) * u, x)
         last = _rms_norm(x.view(B, T, cfg.hidden)[:, -1], self.final_norm, cfg.eps).to(torch.bfloat16)
         self.tokens.copy_((last @ self.lm_head.t()).argmax(-1))
@@ -124,8 +125,7 @@ class BitNetDecoder:
         cos, sin = self.cos[self.pos], self.sin[self.pos]                 # [1, D/2]
         mask = (self.key_index <= self.pos).view(1, 1, 1, self.max_ctx)   # keys 0..pos are visible
         for li, L in enumerate(self.layers):
-            hn = _rms_norm(x, L["n1"], cfg.eps)
-            q, k, v = self._lin_shared([L["q"], L["k"], L["v"]], hn)
+            q, k, v = self._norm_lin_shared([L["q"], L["k"], L["v"]], x, L["n1"])
             q = _rope(q.view(B, cfg.heads, 1, cfg.head_dim), cos, sin)
             k = _rope(k.view(B, cfg.heads, 1, cfg.head_dim), cos, sin)
             self.k_cache[li].index_copy_(2, self.pos, k)
@@ -135,8 +135,7 @@ class BitNetDecoder:
             pr = torch.softmax(sc.masked_fill(~mask, float("-inf")), -1).to(torch.bfloat16)
             a = torch.matmul(pr, self.v_cache[li])
             x = self._lin(L["o"], a.reshape(B, cfg.heads * cfg.head_dim), x)
-            hn = _rms_norm(x, L["n2"], cfg.eps)
-            g, u = self._lin_shared([L["gate"], L["up"]], hn)
+            g, u = self._norm_lin_shared([L["gate"], L["up"]], x, L["n2"])
             x = self._lin(L["down"], F.silu(g) * u, x)
         logits = _rms_norm(x, self.final_norm, cfg.eps).to(torch.bfloat16) @ self.lm_head.t()
         self.tokens.copy_(logits.argmax(-1))

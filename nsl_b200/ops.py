@@ -54,6 +54,27 @@ def act_quant_i8(x, plain=True, perm=True):
     return out
 
 
+def rmsnorm_act_quant_i8(x, weight, eps=1e-5, plain=False, perm=True, return_h=False):
+    """RMSNorm (NSL's f64 arithmetic, rounded once to f32) fused in front of act_quant_i8.
+    Returns the dict of act_quant_i8, plus "h" (the normalised rows, f32) when return_h."""
+    _cuda2d(x, "x")
+    M, K = x.shape
+    dev = x.device
+    if weight.dtype != torch.float32 or weight.numel() != K or not weight.is_cuda:
+        raise ValueError("weight must be a CUDA float32 tensor of K elements")
+    out = {
+        "scale": torch.empty(M, dtype=torch.float32, device=dev),
+        "rowsum": torch.empty(M, dtype=torch.int32, device=dev),
+        "q_plain": torch.empty(M, K, dtype=torch.int8, device=dev) if plain else None,
+        "q_perm": torch.empty(M, K, dtype=torch.int8, device=dev) if perm else None,
+        "h": torch.empty(M, K, dtype=torch.float32, device=dev) if return_h else None,
+    }
+    check(lib().nslq_rmsnorm_act_quant_i8(_ptr(x), _tag(x.dtype), _ptr(weight), float(eps), M, K, _ptr(out["h"]),
+                                          _ptr(out["q_plain"]), _ptr(out["q_perm"]), _ptr(out["scale"]),
+                                          _ptr(out["rowsum"]), _stream()))
+    return out
+
+
 class BitLinear:
     """A ternary weight in NSL's packed layout ([out_dim, hidden_dim/4] uint8) on the GPU."""
 

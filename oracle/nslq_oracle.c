@@ -104,6 +104,19 @@ void nslo_quantize_row_int8(const float *row, int64_t k, float scale, int8_t *q)
     }
 }
 
+/* crates/nsl-runtime/src/tensor/mod.rs:3016-3035  nsl_tensor_rmsnorm, f32 input, CPU arm:
+ * sequential f64 sum of squares, rms = sqrt(sum/n + eps), out = (f32)(x / rms * w). */
+void nslo_rmsnorm_f32(const float *x, const float *w, double eps, int64_t rows, int64_t n, float *out)
+{
+    for (int64_t r = 0; r < rows; ++r) {
+        const float *xr = x + r * n;
+        double sum_sq = 0.0;
+        for (int64_t j = 0; j < n; ++j) sum_sq += (double)xr[j] * (double)xr[j];
+        const double rms = sqrt(sum_sq / (double)n + eps);
+        for (int64_t j = 0; j < n; ++j) out[r * n + j] = (float)((double)xr[j] / rms * (double)w[j]);
+    }
+}
+
 /* crates/nsl-codegen/tests/bitnet_reference_impl.rs:77-95  ternary_gemm_element.
  * Returns the i32 accumulator through *acc_out as well (the bit-exact target). */
 float nslo_ternary_gemm_element(const int8_t *q, const int8_t *wcol, int64_t k,

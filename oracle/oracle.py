@@ -61,6 +61,17 @@ def max_threads():
     return int(lib().nslo_max_threads())
 
 
+# --------------------------------------------------------------------------- RMSNorm (prologue of the fused quantiser)
+def rmsnorm_f32(x, w, eps=1e-5):
+    """nsl_tensor_rmsnorm on f32 rows: sequential f64 sum of squares, one rounding to f32."""
+    x, w = _c(x, np.float32), _c(w, np.float32)
+    rows, n = x.shape
+    out = np.empty_like(x)
+    lib().nslo_rmsnorm_f32(_p(x, C.POINTER(C.c_float)), _p(w, C.POINTER(C.c_float)), C.c_double(eps),
+                           C.c_int64(rows), C.c_int64(n), _p(out, C.POINTER(C.c_float)))
+    return out
+
+
 # --------------------------------------------------------------------------- BitLinear
 def absmax_scale_row(row):
     row = _c(row, np.float32)

@@ -232,3 +232,24 @@ def test_qtensor_int4_group_axis1_is_the_w4a16_layout(oracle):
     want = x.astype(np.float64) @ deq.T
     assert np.allclose(got, want, rtol=1e-12, atol=1e-12)
     assert np.array_equal(got, oracle.w4a16_matmul_nk(x, d, s, z, n, k, gs, threads=3))
+
+
+def test_rmsnorm_restatement_known_answers(oracle):
+    """nsl_tensor_rmsnorm (crates/nsl-runtime/src/tensor/mod.rs:3016-3035) on rows whose result is
+    known in closed form: x = c * ones -> x / sqrt(c^2 + eps) * w; and against the same formula in
+    numpy f64 with a sequential sum."""
+    n = 8
+    w = np.arange(1, n + 1, dtype=np.float32)
+    x = np.full((1, n), 3.0, np.float32)
+    want = (3.0 / np.sqrt(9.0 + 1e-5) * w.astype(np.float64)).astype(np.float32)
+    assert np.array_equal(oracle.rmsnorm_f32(x, w, 1e-5)[0], want)
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((4, 100)).astype(np.float32)
+    w = rng.standard_normal(100).astype(np.float32)
+    got = oracle.rmsnorm_f32(x, w, 1e-5)
+    for r in range(4):
+        s = 0.0
+        for v in x[r].astype(np.float64):
+            s += v * v
+        rms = np.sqrt(s / 100 + 1e-5)
+        assert np.array_equal(got[r], (x[r].astype(np.float64) / rms * w.astype(np.float64)).astype(np.float32))
