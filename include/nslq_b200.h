@@ -102,6 +102,28 @@ int nslq_rmsnorm_act_quant_i8(const void *x, int x_dtype, const float *weight, d
                               int8_t *q_plain, int8_t *q_perm, float *scale, int32_t *rowsum,
                               void *stream);
 
+/*
+ * Decoder step between the q/k/v projections and the output projection, one launch: rotate-half
+ * RoPE of q and k at position *pos (stdlib/nsl/nn/rope.nsl:10-17: frequency table
+ * concat(freqs, freqs)), append of k and v to the KV cache, and causal single-query attention
+ * over keys 0..*pos with grouped heads (stdlib/nsl/nn/gqa.nsl:66-95).  No runtime entry point of
+ * NSL does this in one call; it stands in for rope.forward + scaled_dot_product_attention on the
+ * newest token.
+ *
+ *   q      bf16 [B,H,D]      k_new, v_new  bf16 [B,Hkv,D]      (projection outputs, before RoPE)
+ *   k_cache, v_cache  bf16 [B,Hkv,max_ctx,D]   row *pos is written, rows 0..*pos are read
+ *   cos_table, sin_table  f32 [max_ctx, D/2]
+ *   pos    device pointer to the int64 position (read by the kernel, so a CUDA graph can advance it)
+ *   out    bf16 [B,H,D]
+ * D % 4 == 0, D <= 128, H % Hkv == 0, max_ctx % 4 == 0.  fp32 arithmetic; a position outside
+ * [0, max_ctx) makes the kernel do nothing.
+ */
+int nslq_decode_attention(const void *q, const void *k_new, const void *v_new,
+                          void *k_cache, void *v_cache,
+                          const float *cos_table, const float *sin_table, const int64_t *pos,
+                          int64_t B, int64_t H, int64_t Hkv, int64_t D, int64_t max_ctx,
+                          float sm_scale, void *out, void *stream);
+
 /* ========================================================================== */
 /* BitLinear (ternary W1.58 A8)                                                */
 /* ========================================================================== */

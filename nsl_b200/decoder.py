@@ -1,10 +1,12 @@
 """Decoder harness for the model-shaped workloads of the benchmark (BitNet b1.58-3B shape).
 
 Everything that is NOT a quantized linear -- embedding, RMSNorm, RoPE, attention over the KV
-cache, greedy sampling, the bf16 lm_head -- is plain PyTorch, on purpose: those pieces are outside
+cache at prefill, greedy sampling, the bf16 lm_head -- is plain PyTorch, on purpose: those pieces are outside
 the quantized-linear path this library replaces (NSL has them in stdlib/nsl/nn/{norms,rope,gqa}.nsl
 and stdlib/nsl/inference/generate.nsl).  Every projection of every layer (q, k, v, o, gate, up,
-down) runs through nsl_b200.ops.BitLinear, i.e. the C ABI.  Weights are random ternary (no
+down) runs through nsl_b200.ops.BitLinear, i.e. the C ABI; in a decode step the RMSNorms in front of
+them and the attention of the new token (RoPE, cache append, softmax(qK)V) are library launches too
+(nslq_rmsnorm_act_quant_i8, nslq_decode_attention).  Weights are random ternary (no
 checkpoint is available offline), so the numbers are throughput numbers, not quality numbers.
 
 The residual stream is kept in fp32: the norms then need no casts, and the residual additions ride
@@ -53,6 +55,7 @@ class BitNetDecoder:
     """Random-init decoder of the given shape; act dtype bf16, KV cache bf16."""
 
     def __init__(self, cfg, batch, max_ctx, seed=0):
+        max_ctx = (max_ctx + 3) & ~3                                    # the attention kernel wants a multiple of 4
         self.cfg, self.B, self.max_ctx = cfg, batch, max_ctx
         gen = torch.Generator(device="cuda")
         gen.manual_seed(seed)
@@ -122,18 +125,11 @@ class BitNetDecoder:
     def _step(self):
         cfg, B = self.cfg, self.B
         x = self.embed[self.tokens].float()                               # [B, h] residual stream, fp32
-        cos, sin = self.cos[self.pos], self.sin[self.pos]                 # [1, D/2]
-        mask = (self.key_index <= self.pos).view(1, 1, 1, self.max_ctx)   # keys 0..pos are visible
         for li, L in enumerate(self.layers):
             q, k, v = self._norm_lin_shared([L["q"], L["k"], L["v"]], x, L["n1"])
-            q = _rope(q.view(B, cfg.heads, 1, cfg.head_dim), cos, sin)
-            k = _rope(k.view(B, cfg.heads, 1, cfg.head_dim), cos, sin)
-            self.k_cache[li].index_copy_(2, self.pos, k)
-            self.v_cache[li].index_copy_(2, self.pos, v.view(B, cfg.heads, 1, cfg.head_dim))
-            # single-query attention as two batched matmuls on the cache in place (no copies of K/V)
-            sc = torch.matmul(q, self.k_cache[li].transpose(-1, -2)).float() * self.sm_scale
-            pr = torch.softmax(sc.masked_fill(~mask, float("-inf")), -1).to(torch.bfloat16)
-            a = torch.matmul(pr, self.v_cache[li])
+            # RoPE, cache append and single-query attention: one launch of the library
+            a = ops.decode_attention(q, k, v, self.k_cache[li], self.v_cache[li], self.cos, self.sin, self.pos,
+                                     self.sm_scale)
             x = self._lin(L["o"], a.reshape(B, cfg.heads * cfg.head_dim), x)
             g, u = self._norm_lin_shared([L["gate"], L["up"]], x, L["n2"])
             x = self._lin(L["down"], F.silu(g) * u, x)

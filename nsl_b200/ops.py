@@ -75,6 +75,25 @@ def rmsnorm_act_quant_i8(x, weight, eps=1e-5, plain=False, perm=True, return_h=F
     return out
 
 
+def decode_attention(q, k_new, v_new, k_cache, v_cache, cos_table, sin_table, pos, sm_scale, out=None):
+    """RoPE at *pos, KV-cache append and causal single-query attention in one launch.
+    q [B,H,D] (or [B,H*D]), k_new/v_new [B,Hkv,D] bf16; caches [B,Hkv,max_ctx,D] bf16 (row pos is
+    written); cos/sin [max_ctx,D/2] f32; pos: int64 device tensor of one element.  Returns [B,H*D] bf16."""
+    B, Hkv, max_ctx, D = k_cache.shape
+    H = q.numel() // (B * D)
+    for t in (q, k_new, v_new, k_cache, v_cache):
+        if t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous():
+            raise ValueError("decode_attention: q, k, v and the caches must be contiguous CUDA bfloat16 tensors")
+    if pos.dtype != torch.int64 or pos.numel() != 1 or not pos.is_cuda:
+        raise ValueError("decode_attention: pos must be a one-element int64 CUDA tensor")
+    if out is None:
+        out = torch.empty(B, H * D, dtype=torch.bfloat16, device=q.device)
+    check(lib().nslq_decode_attention(_ptr(q), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), _ptr(cos_table),
+                                      _ptr(sin_table), _ptr(pos), B, H, Hkv, D, max_ctx, float(sm_scale), _ptr(out),
+                                      _stream()))
+    return out
+
+
 class BitLinear:
     """A ternary weight in NSL's packed layout ([out_dim, hidden_dim/4] uint8) on the GPU."""
 
