@@ -103,6 +103,19 @@ int nslq_rmsnorm_act_quant_i8(const void *x, int x_dtype, const float *weight, d
                               void *stream);
 
 /*
+ * SiLU(gate) * up fused in front of the quantisation of the down projection's input (SwiGLU FFN of
+ * the BitNet decoder, gate/up/down in stdlib-level model code; the survey of the reference lists it
+ * with the RMSNorm prologue as the linear's fused neighbours):
+ *   h[r,k] = (f32)( gate[r,k] / (1 + exp(-gate[r,k])) * up[r,k] )       fp32 arithmetic
+ *   then scale/q/rowsum of h exactly as nslq_act_quant_i8.
+ * gate, up: [M,K] of the same dtype in {F32, FP16, BF16}; h_out (f32 [M,K]) may be NULL.
+ * K % 16 == 0, K <= 12288, buffers 16-byte aligned.
+ */
+int nslq_swiglu_act_quant_i8(const void *gate, const void *up, int dtype, int64_t M, int64_t K,
+                             float *h_out, int8_t *q_plain, int8_t *q_perm, float *scale,
+                             int32_t *rowsum, void *stream);
+
+/*
  * Decoder step between the q/k/v projections and the output projection, one launch: rotate-half
  * RoPE of q and k at position *pos (stdlib/nsl/nn/rope.nsl:10-17: frequency table
  * concat(freqs, freqs)), append of k and v to the KV cache, and causal single-query attention

@@ -33,6 +33,8 @@ int check_launch(const char *what)
 int act_quant_dispatch(const void *, int, int64_t, int64_t, int8_t *, int8_t *, float *, int32_t *, cudaStream_t);
 int rmsnorm_act_quant_dispatch(const void *, int, const float *, double, int64_t, int64_t, float *, int8_t *, int8_t *,
                                float *, int32_t *, cudaStream_t);
+int swiglu_act_quant_dispatch(const void *, const void *, int, int64_t, int64_t, float *, int8_t *, int8_t *, float *,
+                              int32_t *, cudaStream_t);
 int decode_attention_dispatch(const void *, const void *, const void *, void *, void *, const float *, const float *,
                               const int64_t *, int64_t, int64_t, int64_t, int64_t, int64_t, float, void *, cudaStream_t);
 bool ternary_gemv_supported(const void *, const void *, int64_t);
@@ -201,6 +203,12 @@ int nslq_rmsnorm_act_quant_i8(const void *x, int x_dtype, const float *weight, d
                               float *h_out, int8_t *q_plain, int8_t *q_perm, float *scale, int32_t *rowsum, void *stream)
 {
     return rmsnorm_act_quant_dispatch(x, x_dtype, weight, eps, M, K, h_out, q_plain, q_perm, scale, rowsum, (cudaStream_t)stream);
+}
+
+int nslq_swiglu_act_quant_i8(const void *gate, const void *up, int dtype, int64_t M, int64_t K, float *h_out,
+                             int8_t *q_plain, int8_t *q_perm, float *scale, int32_t *rowsum, void *stream)
+{
+    return swiglu_act_quant_dispatch(gate, up, dtype, M, K, h_out, q_plain, q_perm, scale, rowsum, (cudaStream_t)stream);
 }
 
 int nslq_decode_attention(const void *q, const void *k_new, const void *v_new, void *k_cache, void *v_cache,

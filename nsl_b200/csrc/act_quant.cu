@@ -241,6 +241,93 @@ int rmsnorm_act_quant_dispatch(const void *x, int x_dtype, const float *weight, 
     }
 }
 
+// SiLU(gate) * up fused in front of the quantisation of the down projection's input (the other
+// "fused neighbour" of the linear: gate and up never make a round trip as an activation tensor):
+//   h = (f32)( g / (1 + exp(-g)) * u )    computed in fp32 from the f32/fp16/bf16 inputs,
+// then quantised from registers like act_quant_kernel.  One CTA per row.
+template <typename T, int XV>
+__global__ void __launch_bounds__(AQ_THREADS)
+swiglu_act_quant_kernel(const T *__restrict__ gate, const T *__restrict__ up, int64_t K, float *__restrict__ h_out,
+                        int8_t *__restrict__ q_plain, int8_t *__restrict__ q_perm, float *__restrict__ scale_out,
+                        int32_t *__restrict__ rowsum_out)
+{
+    __shared__ float smax[AQ_THREADS / 32];
+    __shared__ int ssum[AQ_THREADS / 32];
+    const int64_t r = blockIdx.x;
+    pdl_wait();
+    const int nvec = (int)(K >> 2);
+    float4 hv[XV];
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < XV; ++i) {
+        const int v = i * AQ_THREADS + threadIdx.x;
+        hv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (v < nvec) {
+            const float4 g = Vec4<T>::load(gate + r * K, v), u = Vec4<T>::load(up + r * K, v);
+            float4 h;
+            h.x = __fdiv_rn(g.x, 1.0f + expf(-g.x)) * u.x; h.y = __fdiv_rn(g.y, 1.0f + expf(-g.y)) * u.y;
+            h.z = __fdiv_rn(g.z, 1.0f + expf(-g.z)) * u.z; h.w = __fdiv_rn(g.w, 1.0f + expf(-g.w)) * u.w;
+            hv[i] = h;
+            if (h_out) reinterpret_cast<float4 *>(h_out + r * K)[v] = h;
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(h.x), fabsf(h.y)), fmaxf(fabsf(h.z), fabsf(h.w))));
+        }
+    }
+    const float scale = block_max(m, smax);
+    pdl_launch_dependents();
+    const float inv = __fdiv_rn(127.0f, scale);
+    int sum = 0;
+#pragma unroll
+    for (int i = 0; i < XV; ++i) {
+        const int v = i * AQ_THREADS + threadIdx.x;
+        const bool in = v < nvec;
+        const unsigned mask = __ballot_sync(0xffffffffu, in);          // whole quads: K % 16 == 0
+        if (in) {
+            const float4 f = hv[i];
+            const uint32_t w = pack4_i8(quant_one(f.x, inv), quant_one(f.y, inv), quant_one(f.z, inv), quant_one(f.w, inv));
+            sum = __dp4a((int)w, 0x01010101, sum);
+            if (q_plain) reinterpret_cast<uint32_t *>(q_plain + r * K)[v] = w;
+            if (q_perm) reinterpret_cast<uint32_t *>(q_perm + r * K)[v] = quad_transpose(w, mask);
+        }
+    }
+    if (rowsum_out) {
+        const int tot = block_sum(sum, ssum);
+        if (threadIdx.x == 0) rowsum_out[r] = tot;
+    }
+    if (threadIdx.x == 0) scale_out[r] = scale;
+}
+
+template <typename T>
+static int launch_swiglu_quant(const void *gate, const void *up, int64_t M, int64_t K, float *h_out, int8_t *q_plain,
+                               int8_t *q_perm, float *scale, int32_t *rowsum, cudaStream_t st)
+{
+    dim3 grid((unsigned)M), block(AQ_THREADS);
+    cudaError_t e;
+    if (K <= 4 * 4 * AQ_THREADS)
+        e = launch_kernel(swiglu_act_quant_kernel<T, 4>, grid, block, 0, st, (const T *)gate, (const T *)up, K, h_out, q_plain, q_perm, scale, rowsum);
+    else
+        e = launch_kernel(swiglu_act_quant_kernel<T, 12>, grid, block, 0, st, (const T *)gate, (const T *)up, K, h_out, q_plain, q_perm, scale, rowsum);
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "swiglu_act_quant_kernel: %s", cudaGetErrorString(e));
+    return check_launch("swiglu_act_quant_kernel");
+}
+
+int swiglu_act_quant_dispatch(const void *gate, const void *up, int dtype, int64_t M, int64_t K, float *h_out,
+                              int8_t *q_plain, int8_t *q_perm, float *scale, int32_t *rowsum, cudaStream_t st)
+{
+    if (!gate || !up || !scale) return fail(NSLQ_ERR_ARG, "nslq_swiglu_act_quant_i8: null gate, up or scale");
+    if (M < 0 || K <= 0 || M > 0x7fffffffLL) return fail(NSLQ_ERR_SHAPE, "nslq_swiglu_act_quant_i8: bad M=%lld K=%lld", (long long)M, (long long)K);
+    if (K % 16 != 0 || K > 12 * 4 * AQ_THREADS)
+        return fail(NSLQ_ERR_SHAPE, "nslq_swiglu_act_quant_i8: K=%lld must be a multiple of 16 and at most %d", (long long)K, 12 * 4 * AQ_THREADS);
+    if (!aligned16(gate) || !aligned16(up) || (h_out && !aligned16(h_out)) || (q_plain && !aligned16(q_plain)) || (q_perm && !aligned16(q_perm)))
+        return fail(NSLQ_ERR_ARG, "nslq_swiglu_act_quant_i8: buffers must be 16-byte aligned");
+    if (M == 0) return NSLQ_OK;
+    switch (dtype) {
+    case NSLQ_DTYPE_F32: return launch_swiglu_quant<float>(gate, up, M, K, h_out, q_plain, q_perm, scale, rowsum, st);
+    case NSLQ_DTYPE_FP16: return launch_swiglu_quant<__half>(gate, up, M, K, h_out, q_plain, q_perm, scale, rowsum, st);
+    case NSLQ_DTYPE_BF16: return launch_swiglu_quant<__nv_bfloat16>(gate, up, M, K, h_out, q_plain, q_perm, scale, rowsum, st);
+    default: return fail(NSLQ_ERR_ARG, "nslq_swiglu_act_quant_i8: dtype %d not in {F32,FP16,BF16}", dtype);
+    }
+}
+
 template <typename T>
 static int launch_act_quant(const void *x, int64_t M, int64_t K, int8_t *q_plain, int8_t *q_perm,
                             float *scale, int32_t *rowsum, cudaStream_t st)

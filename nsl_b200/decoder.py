@@ -88,6 +88,11 @@ class BitNetDecoder:
         """fp32 output with the fp32 residual added in the epilogue."""
         return layer.forward(x2d, out_dtype=torch.float32, residual=residual)
 
+    def _swiglu_down(self, layer, g, u, residual):
+        """down(silu(gate) * up) + residual: one launch forms and quantises the product, one multiplies."""
+        qa = ops.swiglu_act_quant_i8(g, u, plain=False, perm=True)
+        return layer.forward_quantized(qa, out_dtype=torch.float32, residual=residual)
+
     def _norm_lin_shared(self, layers, x2d, norm_w):
         """RMSNorm, then several projections of the normalised rows.  More than four rows: one
         launch normalises and quantises (the normalised rows never reach memory) and the
@@ -116,7 +121,7 @@ class BitNetDecoder:
             a = a.transpose(1, 2).reshape(B * T, cfg.heads * cfg.head_dim)
             x = self._lin(L["o"], a, x)
             g, u = self._norm_lin_shared([L["gate"], L["up"]], x, L["n2"])
-            x = self._lin(L["down"], F.silu(g) * u, x)
+            x = self._swiglu_down(L["down"], g, u, x)
         last = _rms_norm(x.view(B, T, cfg.hidden)[:, -1], self.final_norm, cfg.eps).to(torch.bfloat16)
         self.tokens.copy_((last @ self.lm_head.t()).argmax(-1))
         self.pos.fill_(T)
@@ -132,7 +137,7 @@ class BitNetDecoder:
                                      self.sm_scale)
             x = self._lin(L["o"], a.reshape(B, cfg.heads * cfg.head_dim), x)
             g, u = self._norm_lin_shared([L["gate"], L["up"]], x, L["n2"])
-            x = self._lin(L["down"], F.silu(g) * u, x)
+            x = self._swiglu_down(L["down"], g, u, x)
         logits = _rms_norm(x, self.final_norm, cfg.eps).to(torch.bfloat16) @ self.lm_head.t()
         self.tokens.copy_(logits.argmax(-1))
         self.pos.add_(1)

@@ -75,6 +75,26 @@ def rmsnorm_act_quant_i8(x, weight, eps=1e-5, plain=False, perm=True, return_h=F
     return out
 
 
+def swiglu_act_quant_i8(gate, up, plain=False, perm=True, return_h=False):
+    """SiLU(gate) * up (fp32 arithmetic) fused in front of act_quant_i8; gate, up [M,K] of one dtype."""
+    _cuda2d(gate, "gate")
+    _cuda2d(up, "up")
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise ValueError("gate and up must have the same shape and dtype")
+    M, K = gate.shape
+    dev = gate.device
+    out = {
+        "scale": torch.empty(M, dtype=torch.float32, device=dev),
+        "rowsum": torch.empty(M, dtype=torch.int32, device=dev),
+        "q_plain": torch.empty(M, K, dtype=torch.int8, device=dev) if plain else None,
+        "q_perm": torch.empty(M, K, dtype=torch.int8, device=dev) if perm else None,
+        "h": torch.empty(M, K, dtype=torch.float32, device=dev) if return_h else None,
+    }
+    check(lib().nslq_swiglu_act_quant_i8(_ptr(gate), _ptr(up), _tag(gate.dtype), M, K, _ptr(out["h"]), _ptr(out["q_plain"]),
+                                         _ptr(out["q_perm"]), _ptr(out["scale"]), _ptr(out["rowsum"]), _stream()))
+    return out
+
+
 def decode_attention(q, k_new, v_new, k_cache, v_cache, cos_table, sin_table, pos, sm_scale, out=None):
     """RoPE at *pos, KV-cache append and causal single-query attention in one launch.
     q [B,H,D] (or [B,H*D]), k_new/v_new [B,Hkv,D] bf16; caches [B,Hkv,max_ctx,D] bf16 (row pos is
