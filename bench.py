@@ -17,7 +17,7 @@ configurations):
   bitnet3b_b1 / _b8 / _b64
                 BitNet b1.58-3B-shaped decoder (26 layers, hidden 3200, FFN 8640, vocab 32002), random
                 ternary weights, 512-token prompt, 256 greedy decode steps in one CUDA graph; every
-                projection through the C ABI, the rest PyTorch; value in decode tok/s.
+                projection (and, per decode step, norms, attention and SwiGLU) through the C ABI; value in decode tok/s.
 One JSON line is printed by rank 0; at N=1 the default run appends the other workloads' figures
 under "also" and the decoder's under "decoder".  With --gpus N > 1 (launched by torchrun) the weights are column-sharded over the
 ranks, x is replicated and each output is all-gathered with NCCL: total work is fixed ("strong").
@@ -545,8 +545,9 @@ def run_decoder(torch, batch, peaks, prompt=512, steps=256, warm=8):
            "e2e_tok_s": round(batch * (steps) / e2e_s, 1),
            "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                         "frac": round(ach / peaks["hbm_gbs"], 4), "bytes_per_step": step_bytes,
-                        "note": "ternary weights + bf16 lm_head + KV read at mid-run context; attention, norms, "
-                                "RoPE and sampling are PyTorch"},
+                        "note": "ternary weights + bf16 lm_head + KV read at mid-run context; in a decode step the norms, "
+                                "RoPE + KV append + attention and SwiGLU are library launches; embedding, lm_head, sampling "
+                                "and the prefill glue are PyTorch"},
            "ceiling_tok_s": round(batch / (step_bytes / (peaks["hbm_gbs"] * 1e9)), 1)}
     del model
     torch.cuda.empty_cache()
