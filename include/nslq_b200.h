@@ -108,11 +108,13 @@ int nslq_rmsnorm_act_quant_i8(const void *x, int x_dtype, const float *weight, d
  * with the RMSNorm prologue as the linear's fused neighbours):
  *   h[r,k] = (f32)( gate[r,k] / (1 + exp(-gate[r,k])) * up[r,k] )       fp32 arithmetic
  *   then scale/q/rowsum of h exactly as nslq_act_quant_i8.
- * gate, up: [M,K] of the same dtype in {F32, FP16, BF16}; h_out (f32 [M,K]) may be NULL.
+ * gate, up: [M,K] of the same dtype in {F32, FP16, BF16} with row strides gate_ld, up_ld in elements
+ * (K when packed; larger when they are column slices of one fused gate|up projection output; rows
+ * must stay 16-byte aligned); h_out (f32 [M,K]) may be NULL.
  * K % 16 == 0, K <= 12288, buffers 16-byte aligned.
  */
 int nslq_swiglu_act_quant_i8(const void *gate, const void *up, int dtype, int64_t M, int64_t K,
-                             float *h_out, int8_t *q_plain, int8_t *q_perm, float *scale,
+                             int64_t gate_ld, int64_t up_ld, float *h_out, int8_t *q_plain, int8_t *q_perm, float *scale,
                              int32_t *rowsum, void *stream);
 
 /*
@@ -123,7 +125,9 @@ int nslq_swiglu_act_quant_i8(const void *gate, const void *up, int dtype, int64_
  * NSL does this in one call; it stands in for rope.forward + scaled_dot_product_attention on the
  * newest token.
  *
- *   q      bf16 [B,H,D]      k_new, v_new  bf16 [B,Hkv,D]      (projection outputs, before RoPE)
+ *   q      bf16 [B,H,D]      k_new, v_new  bf16 [B,Hkv,D]      (projection outputs, before RoPE);
+ *          *_batch_stride = elements between consecutive sequences (H*D resp. Hkv*D when packed;
+ *          larger when q, k, v are column slices of one fused projection output), multiples of 4
  *   k_cache, v_cache  bf16 [B,Hkv,max_ctx,D]   row *pos is written, rows 0..*pos are read
  *   cos_table, sin_table  f32 [max_ctx, D/2]
  *   pos    device pointer to the int64 position (read by the kernel, so a CUDA graph can advance it)
@@ -132,6 +136,7 @@ int nslq_swiglu_act_quant_i8(const void *gate, const void *up, int dtype, int64_
  * [0, max_ctx) makes the kernel do nothing.
  */
 int nslq_decode_attention(const void *q, const void *k_new, const void *v_new,
+                          int64_t q_batch_stride, int64_t k_batch_stride, int64_t v_batch_stride,
                           void *k_cache, void *v_cache,
                           const float *cos_table, const float *sin_table, const int64_t *pos,
                           int64_t B, int64_t H, int64_t Hkv, int64_t D, int64_t max_ctx,

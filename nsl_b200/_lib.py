@@ -18,8 +18,8 @@ SIGNATURES = {
     "nslq_set_dependent_launch": (None, [i32]),
     "nslq_device_status": (i32, [C.POINTER(i32)]),
     "nslq_act_quant_i8": (i32, [vp, i32, i64, i64, vp, vp, vp, vp, vp]),
-    "nslq_swiglu_act_quant_i8": (i32, [vp, vp, i32, i64, i64, vp, vp, vp, vp, vp, vp]),
-    "nslq_decode_attention": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, vp, vp]),
+    "nslq_swiglu_act_quant_i8": (i32, [vp, vp, i32, i64, i64, i64, i64, vp, vp, vp, vp, vp, vp]),
+    "nslq_decode_attention": (i32, [vp, vp, vp, i64, i64, i64, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, vp, vp]),
     "nslq_rmsnorm_act_quant_i8": (i32, [vp, i32, vp, f64, i64, i64, vp, vp, vp, vp, vp, vp]),
     "nslq_bitlinear_create": (i32, [vp, i64, i64, f32, C.POINTER(vp)]),
     "nslq_bitlinear_destroy": (None, [vp]),

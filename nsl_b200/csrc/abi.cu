@@ -33,9 +33,9 @@ int check_launch(const char *what)
 int act_quant_dispatch(const void *, int, int64_t, int64_t, int8_t *, int8_t *, float *, int32_t *, cudaStream_t);
 int rmsnorm_act_quant_dispatch(const void *, int, const float *, double, int64_t, int64_t, float *, int8_t *, int8_t *,
                                float *, int32_t *, cudaStream_t);
-int swiglu_act_quant_dispatch(const void *, const void *, int, int64_t, int64_t, float *, int8_t *, int8_t *, float *,
+int swiglu_act_quant_dispatch(const void *, const void *, int, int64_t, int64_t, int64_t, int64_t, float *, int8_t *, int8_t *, float *,
                               int32_t *, cudaStream_t);
-int decode_attention_dispatch(const void *, const void *, const void *, void *, void *, const float *, const float *,
+int decode_attention_dispatch(const void *, const void *, const void *, int64_t, int64_t, int64_t, void *, void *, const float *, const float *,
                               const int64_t *, int64_t, int64_t, int64_t, int64_t, int64_t, float, void *, cudaStream_t);
 bool ternary_gemv_supported(const void *, const void *, int64_t);
 int ternary_gemv_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int, int64_t, int64_t,
@@ -205,17 +205,19 @@ int nslq_rmsnorm_act_quant_i8(const void *x, int x_dtype, const float *weight, d
     return rmsnorm_act_quant_dispatch(x, x_dtype, weight, eps, M, K, h_out, q_plain, q_perm, scale, rowsum, (cudaStream_t)stream);
 }
 
-int nslq_swiglu_act_quant_i8(const void *gate, const void *up, int dtype, int64_t M, int64_t K, float *h_out,
+int nslq_swiglu_act_quant_i8(const void *gate, const void *up, int dtype, int64_t M, int64_t K, int64_t gate_ld,
+                             int64_t up_ld, float *h_out,
                              int8_t *q_plain, int8_t *q_perm, float *scale, int32_t *rowsum, void *stream)
 {
-    return swiglu_act_quant_dispatch(gate, up, dtype, M, K, h_out, q_plain, q_perm, scale, rowsum, (cudaStream_t)stream);
+    return swiglu_act_quant_dispatch(gate, up, dtype, M, K, gate_ld, up_ld, h_out, q_plain, q_perm, scale, rowsum, (cudaStream_t)stream);
 }
 
-int nslq_decode_attention(const void *q, const void *k_new, const void *v_new, void *k_cache, void *v_cache,
+int nslq_decode_attention(const void *q, const void *k_new, const void *v_new, int64_t q_batch_stride,
+                          int64_t k_batch_stride, int64_t v_batch_stride, void *k_cache, void *v_cache,
                           const float *cos_table, const float *sin_table, const int64_t *pos, int64_t B, int64_t H,
                           int64_t Hkv, int64_t D, int64_t max_ctx, float sm_scale, void *out, void *stream)
 {
-    return decode_attention_dispatch(q, k_new, v_new, k_cache, v_cache, cos_table, sin_table, pos, B, H, Hkv, D, max_ctx,
+    return decode_attention_dispatch(q, k_new, v_new, q_batch_stride, k_batch_stride, v_batch_stride, k_cache, v_cache, cos_table, sin_table, pos, B, H, Hkv, D, max_ctx,
                                      sm_scale, out, (cudaStream_t)stream);
 }
 

@@ -247,7 +247,8 @@ int rmsnorm_act_quant_dispatch(const void *x, int x_dtype, const float *weight, 
 // then quantised from registers like act_quant_kernel.  One CTA per row.
 template <typename T, int XV>
 __global__ void __launch_bounds__(AQ_THREADS)
-swiglu_act_quant_kernel(const T *__restrict__ gate, const T *__restrict__ up, int64_t K, float *__restrict__ h_out,
+swiglu_act_quant_kernel(const T *__restrict__ gate, const T *__restrict__ up, int64_t K, int64_t ld_g, int64_t ld_u,
+                        float *__restrict__ h_out,
                         int8_t *__restrict__ q_plain, int8_t *__restrict__ q_perm, float *__restrict__ scale_out,
                         int32_t *__restrict__ rowsum_out)
 {
@@ -263,7 +264,7 @@ swiglu_act_quant_kernel(const T *__restrict__ gate, const T *__restrict__ up, in
         const int v = i * AQ_THREADS + threadIdx.x;
         hv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (v < nvec) {
-            const float4 g = Vec4<T>::load(gate + r * K, v), u = Vec4<T>::load(up + r * K, v);
+            const float4 g = Vec4<T>::load(gate + r * ld_g, v), u = Vec4<T>::load(up + r * ld_u, v);
             float4 h;
             h.x = __fdiv_rn(g.x, 1.0f + expf(-g.x)) * u.x; h.y = __fdiv_rn(g.y, 1.0f + expf(-g.y)) * u.y;
             h.z = __fdiv_rn(g.z, 1.0f + expf(-g.z)) * u.z; h.w = __fdiv_rn(g.w, 1.0f + expf(-g.w)) * u.w;
@@ -297,20 +298,21 @@ swiglu_act_quant_kernel(const T *__restrict__ gate, const T *__restrict__ up, in
 }
 
 template <typename T>
-static int launch_swiglu_quant(const void *gate, const void *up, int64_t M, int64_t K, float *h_out, int8_t *q_plain,
+static int launch_swiglu_quant(const void *gate, const void *up, int64_t M, int64_t K, int64_t ld_g, int64_t ld_u, float *h_out, int8_t *q_plain,
                                int8_t *q_perm, float *scale, int32_t *rowsum, cudaStream_t st)
 {
     dim3 grid((unsigned)M), block(AQ_THREADS);
     cudaError_t e;
     if (K <= 4 * 4 * AQ_THREADS)
-        e = launch_kernel(swiglu_act_quant_kernel<T, 4>, grid, block, 0, st, (const T *)gate, (const T *)up, K, h_out, q_plain, q_perm, scale, rowsum);
+        e = launch_kernel(swiglu_act_quant_kernel<T, 4>, grid, block, 0, st, (const T *)gate, (const T *)up, K, ld_g, ld_u, h_out, q_plain, q_perm, scale, rowsum);
     else
-        e = launch_kernel(swiglu_act_quant_kernel<T, 12>, grid, block, 0, st, (const T *)gate, (const T *)up, K, h_out, q_plain, q_perm, scale, rowsum);
+        e = launch_kernel(swiglu_act_quant_kernel<T, 12>, grid, block, 0, st, (const T *)gate, (const T *)up, K, ld_g, ld_u, h_out, q_plain, q_perm, scale, rowsum);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "swiglu_act_quant_kernel: %s", cudaGetErrorString(e));
     return check_launch("swiglu_act_quant_kernel");
 }
 
-int swiglu_act_quant_dispatch(const void *gate, const void *up, int dtype, int64_t M, int64_t K, float *h_out,
+int swiglu_act_quant_dispatch(const void *gate, const void *up, int dtype, int64_t M, int64_t K, int64_t ld_g, int64_t ld_u,
+                              float *h_out,
                               int8_t *q_plain, int8_t *q_perm, float *scale, int32_t *rowsum, cudaStream_t st)
 {
     if (!gate || !up || !scale) return fail(NSLQ_ERR_ARG, "nslq_swiglu_act_quant_i8: null gate, up or scale");
@@ -319,11 +321,14 @@ int swiglu_act_quant_dispatch(const void *gate, const void *up, int dtype, int64
         return fail(NSLQ_ERR_SHAPE, "nslq_swiglu_act_quant_i8: K=%lld must be a multiple of 16 and at most %d", (long long)K, 12 * 4 * AQ_THREADS);
     if (!aligned16(gate) || !aligned16(up) || (h_out && !aligned16(h_out)) || (q_plain && !aligned16(q_plain)) || (q_perm && !aligned16(q_perm)))
         return fail(NSLQ_ERR_ARG, "nslq_swiglu_act_quant_i8: buffers must be 16-byte aligned");
+    const int64_t es = dtype == NSLQ_DTYPE_F32 ? 4 : 2;
+    if (ld_g < K || ld_u < K || (ld_g * es) % 16 != 0 || (ld_u * es) % 16 != 0)
+        return fail(NSLQ_ERR_SHAPE, "nslq_swiglu_act_quant_i8: row strides must be at least K and keep rows 16-byte aligned");
     if (M == 0) return NSLQ_OK;
     switch (dtype) {
-    case NSLQ_DTYPE_F32: return launch_swiglu_quant<float>(gate, up, M, K, h_out, q_plain, q_perm, scale, rowsum, st);
-    case NSLQ_DTYPE_FP16: return launch_swiglu_quant<__half>(gate, up, M, K, h_out, q_plain, q_perm, scale, rowsum, st);
-    case NSLQ_DTYPE_BF16: return launch_swiglu_quant<__nv_bfloat16>(gate, up, M, K, h_out, q_plain, q_perm, scale, rowsum, st);
+    case NSLQ_DTYPE_F32: return launch_swiglu_quant<float>(gate, up, M, K, ld_g, ld_u, h_out, q_plain, q_perm, scale, rowsum, st);
+    case NSLQ_DTYPE_FP16: return launch_swiglu_quant<__half>(gate, up, M, K, ld_g, ld_u, h_out, q_plain, q_perm, scale, rowsum, st);
+    case NSLQ_DTYPE_BF16: return launch_swiglu_quant<__nv_bfloat16>(gate, up, M, K, ld_g, ld_u, h_out, q_plain, q_perm, scale, rowsum, st);
     default: return fail(NSLQ_ERR_ARG, "nslq_swiglu_act_quant_i8: dtype %d not in {F32,FP16,BF16}", dtype);
     }
 }

@@ -41,7 +41,8 @@ static __device__ __forceinline__ float warp_sum(float v)
 }
 
 struct AttnParams {
-    const __nv_bfloat16 *q, *k_new, *v_new;   // [B,H,D], [B,Hkv,D], [B,Hkv,D]
+    const __nv_bfloat16 *q, *k_new, *v_new;   // [B,H,D], [B,Hkv,D], [B,Hkv,D]; rows of a sequence contiguous
+    int64_t q_bs, k_bs, v_bs;                 // elements between consecutive sequences of q, k_new, v_new
     __nv_bfloat16 *k_cache, *v_cache;         // [B,Hkv,max_ctx,D]
     const float *cos_t, *sin_t;               // [max_ctx, D/2]
     const int64_t *pos;                       // device scalar: index the new token is written at
@@ -66,9 +67,9 @@ decode_attention_kernel(const AttnParams p)
     const int pos = (int)*p.pos;
     if (pos < 0 || pos >= p.max_ctx) return;              // nothing sensible to do; the host checks the range it can see
     const int half = p.D >> 1, nl = p.D >> 2;             // lanes that hold four dimensions each
-    const __nv_bfloat16 *qg = p.q + ((int64_t)b * p.H + h) * p.D;
-    const __nv_bfloat16 *kg = p.k_new + ((int64_t)b * p.Hkv + hk) * p.D;
-    const __nv_bfloat16 *vg = p.v_new + ((int64_t)b * p.Hkv + hk) * p.D;
+    const __nv_bfloat16 *qg = p.q + (int64_t)b * p.q_bs + (int64_t)h * p.D;
+    const __nv_bfloat16 *kg = p.k_new + (int64_t)b * p.k_bs + (int64_t)hk * p.D;
+    const __nv_bfloat16 *vg = p.v_new + (int64_t)b * p.v_bs + (int64_t)hk * p.D;
     __nv_bfloat16 *kc = p.k_cache + ((int64_t)b * p.Hkv + hk) * p.max_ctx * p.D;
     __nv_bfloat16 *vc = p.v_cache + ((int64_t)b * p.Hkv + hk) * p.max_ctx * p.D;
 
@@ -161,7 +162,8 @@ decode_attention_kernel(const AttnParams p)
     }
 }
 
-int decode_attention_dispatch(const void *q, const void *k_new, const void *v_new, void *k_cache, void *v_cache,
+int decode_attention_dispatch(const void *q, const void *k_new, const void *v_new, int64_t q_bs, int64_t k_bs, int64_t v_bs,
+                              void *k_cache, void *v_cache,
                               const float *cos_t, const float *sin_t, const int64_t *pos, int64_t B, int64_t H, int64_t Hkv,
                               int64_t D, int64_t max_ctx, float sm_scale, void *out, cudaStream_t st)
 {
@@ -182,7 +184,9 @@ int decode_attention_dispatch(const void *q, const void *k_new, const void *v_ne
                         cudaGetErrorString(cudaGetLastError()));
         reserved = smem;
     }
-    AttnParams p{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_new, (const __nv_bfloat16 *)v_new,
+    if (q_bs % 4 != 0 || k_bs % 4 != 0 || v_bs % 4 != 0 || q_bs < H * D || k_bs < Hkv * D || v_bs < Hkv * D)
+        return fail(NSLQ_ERR_SHAPE, "nslq_decode_attention: batch strides must be multiples of 4 elements and cover a sequence's rows");
+    AttnParams p{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_new, (const __nv_bfloat16 *)v_new, q_bs, k_bs, v_bs,
                  (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, cos_t, sin_t, pos, (__nv_bfloat16 *)out,
                  (int)H, (int)Hkv, (int)D, (int)max_ctx, sm_scale};
     cudaError_t e = wide ? launch_kernel(decode_attention_kernel<512>, dim3((unsigned)(B * H)), dim3(512), smem, st, p)

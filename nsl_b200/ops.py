@@ -77,8 +77,9 @@ def rmsnorm_act_quant_i8(x, weight, eps=1e-5, plain=False, perm=True, return_h=F
 
 def swiglu_act_quant_i8(gate, up, plain=False, perm=True, return_h=False):
     """SiLU(gate) * up (fp32 arithmetic) fused in front of act_quant_i8; gate, up [M,K] of one dtype."""
-    _cuda2d(gate, "gate")
-    _cuda2d(up, "up")
+    for t, name in ((gate, "gate"), (up, "up")):      # rows may be column slices of a wider tensor
+        if not (t.is_cuda and t.dim() == 2 and t.stride(1) == 1):
+            raise ValueError("%s must be a 2-D CUDA tensor with contiguous rows" % name)
     if gate.shape != up.shape or gate.dtype != up.dtype:
         raise ValueError("gate and up must have the same shape and dtype")
     M, K = gate.shape
@@ -90,7 +91,8 @@ def swiglu_act_quant_i8(gate, up, plain=False, perm=True, return_h=False):
         "q_perm": torch.empty(M, K, dtype=torch.int8, device=dev) if perm else None,
         "h": torch.empty(M, K, dtype=torch.float32, device=dev) if return_h else None,
     }
-    check(lib().nslq_swiglu_act_quant_i8(_ptr(gate), _ptr(up), _tag(gate.dtype), M, K, _ptr(out["h"]), _ptr(out["q_plain"]),
+    check(lib().nslq_swiglu_act_quant_i8(_ptr(gate), _ptr(up), _tag(gate.dtype), M, K, gate.stride(0), up.stride(0),
+                                         _ptr(out["h"]), _ptr(out["q_plain"]),
                                          _ptr(out["q_perm"]), _ptr(out["scale"]), _ptr(out["rowsum"]), _stream()))
     return out
 
@@ -100,15 +102,21 @@ def decode_attention(q, k_new, v_new, k_cache, v_cache, cos_table, sin_table, po
     q [B,H,D] (or [B,H*D]), k_new/v_new [B,Hkv,D] bf16; caches [B,Hkv,max_ctx,D] bf16 (row pos is
     written); cos/sin [max_ctx,D/2] f32; pos: int64 device tensor of one element.  Returns [B,H*D] bf16."""
     B, Hkv, max_ctx, D = k_cache.shape
-    H = q.numel() // (B * D)
-    for t in (q, k_new, v_new, k_cache, v_cache):
+    q, k_new, v_new = q.reshape(B, -1) if q.dim() != 2 else q, k_new.reshape(B, -1) if k_new.dim() != 2 else k_new, \
+        v_new.reshape(B, -1) if v_new.dim() != 2 else v_new
+    H = q.shape[1] // D
+    for t in (q, k_new, v_new):                      # [B, heads*D] rows, possibly column slices of a fused projection
+        if t.dtype != torch.bfloat16 or not t.is_cuda or t.stride(1) != 1:
+            raise ValueError("decode_attention: q, k, v must be CUDA bfloat16 with contiguous rows")
+    for t in (k_cache, v_cache):
         if t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous():
-            raise ValueError("decode_attention: q, k, v and the caches must be contiguous CUDA bfloat16 tensors")
+            raise ValueError("decode_attention: the caches must be contiguous CUDA bfloat16 tensors")
     if pos.dtype != torch.int64 or pos.numel() != 1 or not pos.is_cuda:
         raise ValueError("decode_attention: pos must be a one-element int64 CUDA tensor")
     if out is None:
         out = torch.empty(B, H * D, dtype=torch.bfloat16, device=q.device)
-    check(lib().nslq_decode_attention(_ptr(q), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), _ptr(cos_table),
+    check(lib().nslq_decode_attention(_ptr(q), _ptr(k_new), _ptr(v_new), q.stride(0), k_new.stride(0), v_new.stride(0),
+                                      _ptr(k_cache), _ptr(v_cache), _ptr(cos_table),
                                       _ptr(sin_table), _ptr(pos), B, H, Hkv, D, max_ctx, float(sm_scale), _ptr(out),
                                       _stream()))
     return out

@@ -67,3 +67,23 @@ def test_against_float64(ops, B, H, Hkv, D, max_ctx, pos):
     # rows other than pos untouched
     if pos > 0:
         assert np.array_equal(kct.float().cpu().numpy()[:, :, :pos], kc[:, :, :pos])
+
+
+def test_column_slices_of_a_fused_projection(ops):
+    """q, k, v handed over as column slices of one [B, 3*H*D] tensor give the same bytes as packed inputs."""
+    B, H, D, max_ctx, pos = 3, 8, 100, 64, 20
+    g = torch.Generator(device="cuda"); g.manual_seed(3)
+    qkv = torch.randn(B, 3 * H * D, device="cuda", generator=g).to(torch.bfloat16)
+    kc = torch.randn(B, H, max_ctx, D, device="cuda", generator=g).to(torch.bfloat16)
+    vc = torch.randn(B, H, max_ctx, D, device="cuda", generator=g).to(torch.bfloat16)
+    half = D // 2
+    ang = torch.arange(max_ctx, device="cuda").float()[:, None] / (10000.0 ** (torch.arange(half, device="cuda").float() / half))[None, :]
+    cos, sin = ang.cos(), ang.sin()
+    pos_t = torch.tensor([pos], dtype=torch.int64, device="cuda")
+    hd = H * D
+    kc1, vc1, kc2, vc2 = kc.clone(), vc.clone(), kc.clone(), vc.clone()
+    a = ops.decode_attention(qkv[:, :hd], qkv[:, hd:2 * hd], qkv[:, 2 * hd:], kc1, vc1, cos, sin, pos_t, 0.1)
+    b = ops.decode_attention(qkv[:, :hd].contiguous(), qkv[:, hd:2 * hd].contiguous(), qkv[:, 2 * hd:].contiguous(), kc2, vc2,
+                             cos, sin, pos_t, 0.1)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b) and torch.equal(kc1, kc2) and torch.equal(vc1, vc2)

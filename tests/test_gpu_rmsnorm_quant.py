@@ -92,3 +92,15 @@ def test_swiglu_then_quant(ops, oracle, M, K, dt):
     q_ref = np.stack([oracle.quantize_row_int8(w32[r], oracle.absmax_scale_row(w32[r])) for r in range(M)])
     d = np.abs(q.astype(np.int32) - q_ref.astype(np.int32))
     assert d.max() <= 1 and (d != 0).mean() <= 1e-3
+
+
+def test_swiglu_on_column_slices(ops):
+    """gate and up as the two halves of one fused projection output (row stride 2K)."""
+    M, K = 5, 8640
+    g = torch.Generator(device="cuda"); g.manual_seed(11)
+    gu = torch.randn(M, 2 * K, device="cuda", generator=g).to(torch.bfloat16)
+    a = ops.swiglu_act_quant_i8(gu[:, :K], gu[:, K:], plain=True, return_h=True)
+    b = ops.swiglu_act_quant_i8(gu[:, :K].contiguous(), gu[:, K:].contiguous(), plain=True, return_h=True)
+    torch.cuda.synchronize()
+    for key in ("h", "q_plain", "q_perm", "scale", "rowsum"):
+        assert torch.equal(a[key], b[key]), key
