@@ -1,9 +1,10 @@
 // Stage 1: per-token absmax int8 activation quantisation.
 //
-// One CTA per token row.  The row is read once into registers; max|x| is reduced
-// with warp shuffles (then across warps through shared memory); the row is then
-// quantised from registers with the reference's exact arithmetic and written in the
-// natural order and/or the order the matmul kernels consume, plus scale and sum.
+// One CTA per token row.  The row is read once into registers, each thread holding whole
+// groups of 16 consecutive elements; max|x| is reduced with warp shuffles (then across warps
+// through shared memory); the row is then quantised from registers with the reference's exact
+// arithmetic and written in the natural order and/or the order the matmul kernels consume
+// (16-byte stores assembled in registers), plus scale and sum.
 //
 // Arithmetic follows crates/nsl-codegen/tests/bitnet_reference_impl.rs:46-70 of
 // NSL: inv = 127/scale (IEEE divide), v = x*inv, clamp to [-127,127], round half
@@ -41,9 +42,106 @@ static __device__ __forceinline__ int block_sum(int v, int *smem)
     return r;
 }
 
-// VEC = true: K % 16 == 0 and 16-byte aligned rows; four elements per thread per
-// iteration, quads of lanes cover one group of 16 k (needed for q_perm).
-template <typename T, bool VEC, int XV>
+// Sixteen consecutive elements of a row as fp32: four 16-byte loads for fp32, two for the 16-bit types.
+template <typename T> struct Group16;
+template <> struct Group16<float> {
+    static __device__ __forceinline__ void load(const float *row, int g, float (&f)[16]) {
+        const float4 *p = reinterpret_cast<const float4 *>(row) + 4 * (int64_t)g;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float4 v = p[j]; f[4 * j] = v.x; f[4 * j + 1] = v.y; f[4 * j + 2] = v.z; f[4 * j + 3] = v.w; }
+    }
+};
+template <> struct Group16<__half> {
+    static __device__ __forceinline__ void load(const __half *row, int g, float (&f)[16]) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(row) + 2 * (int64_t)g;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint4 v = p[j];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&w[e]));
+                f[8 * j + 2 * e] = a.x; f[8 * j + 2 * e + 1] = a.y;
+            }
+        }
+    }
+};
+template <> struct Group16<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16 *row, int g, float (&f)[16]) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(row) + 2 * (int64_t)g;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint4 v = p[j];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { f[8 * j + 2 * e] = __uint_as_float(w[e] << 16); f[8 * j + 2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u); }
+        }
+    }
+};
+
+// Four int32 in [-128, 127] -> one word, q0 in the low byte (two saturating pack instructions).
+static __device__ __forceinline__ uint32_t pack4_sat(int q0, int q1, int q2, int q3)
+{
+    uint32_t hi, w;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(q3), "r"(q2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(q1), "r"(q0), "r"(hi));
+    return w;
+}
+
+// One group of 16 quantised and stored: natural order and/or the order the matmul kernels consume
+// (position 4i+j of the group holds k = 4j+i), one 16-byte store each; returns the sum of the 16.
+// FAST: inv is finite, so |x*inv| <= 127*(1+2^-23) for every element of the row and
+//   trunc(s + copysign(0.49999997, s)) == round-half-away(s)
+// holds for every float |s| <= 200 (checked over all of them on the CPU): below 0.5 the sum stays
+// below 1, at a tie k+0.5 it rounds up to k+1 exactly, elsewhere it stays inside [k, k+1).  Four
+// instructions per element, no compare, no clamp.  The other rows (scale 0, or so small that
+// 127/scale overflows) take quant_one, which saturates and maps NaN to 0 like the reference.
+template <bool FAST>
+static __device__ __forceinline__ int quant_group(const float (&f)[16], float inv, int8_t *q_plain_row, int8_t *q_perm_row, int g)
+{
+    int q[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        if (FAST) {
+            const float s = __fmul_rn(f[e], inv);
+            const float h = __int_as_float((__float_as_int(s) & 0x80000000) | 0x3effffff);
+            q[e] = __float2int_rz(__fadd_rn(s, h));
+        } else {
+            q[e] = quant_one(f[e], inv);
+        }
+    }
+    uint4 pw;
+    pw.x = pack4_sat(q[0], q[4], q[8], q[12]);
+    pw.y = pack4_sat(q[1], q[5], q[9], q[13]);
+    pw.z = pack4_sat(q[2], q[6], q[10], q[14]);
+    pw.w = pack4_sat(q[3], q[7], q[11], q[15]);
+    if (q_perm_row) reinterpret_cast<uint4 *>(q_perm_row)[g] = pw;
+    if (q_plain_row) {
+        uint4 nw;
+        nw.x = pack4_sat(q[0], q[1], q[2], q[3]);
+        nw.y = pack4_sat(q[4], q[5], q[6], q[7]);
+        nw.z = pack4_sat(q[8], q[9], q[10], q[11]);
+        nw.w = pack4_sat(q[12], q[13], q[14], q[15]);
+        reinterpret_cast<uint4 *>(q_plain_row)[g] = nw;
+    }
+    int sum = __dp4a((int)pw.x, 0x01010101, 0);
+    sum = __dp4a((int)pw.y, 0x01010101, sum);
+    sum = __dp4a((int)pw.z, 0x01010101, sum);
+    return __dp4a((int)pw.w, 0x01010101, sum);
+}
+
+static __device__ __forceinline__ float absmax16(const float (&f)[16], float m)
+{
+#pragma unroll
+    for (int e = 0; e < 16; ++e) m = fmaxf(m, fabsf(f[e]));
+    return m;
+}
+
+// VEC = true: K % 16 == 0 and 16-byte aligned rows; a thread owns whole groups of 16 consecutive
+// elements, so both output orders are assembled in registers and stored 16 bytes at a time: no
+// shuffles, no lane masks.  (The kernel is bound by issued instructions, not by HBM, as long as it
+// spends more than about eight per element.)
+template <typename T, bool VEC, int XG>
 __global__ void __launch_bounds__(AQ_THREADS)
 act_quant_kernel(const T *__restrict__ x, int64_t K, int8_t *__restrict__ q_plain,
                  int8_t *__restrict__ q_perm, float *__restrict__ scale_out,
@@ -55,25 +153,28 @@ act_quant_kernel(const T *__restrict__ x, int64_t K, int8_t *__restrict__ q_plai
     const T *row = x + r * K;
     pdl_wait();
 
-    // VEC path: the thread's share of the row stays in registers between the absmax pass and
-    // the rounding pass (XV float4 per thread: K <= XV*4*AQ_THREADS; longer rows re-read the
-    // tail, which is still in L1/L2).  XV is 4 or 12: short rows keep registers low so that more
-    // rows are in flight per SM.
-    const int nvec = VEC ? (int)(K >> 2) : 0;
-    float4 xv[VEC ? XV : 1];
+    // VEC path: the thread's groups stay in registers between the absmax pass and the rounding pass
+    // (XG groups per thread: K <= XG*16*AQ_THREADS; longer rows re-read the tail, which is still in
+    // L1/L2).  XG is 1 or 3: short rows keep registers low so that more rows are in flight per SM.
+    const int ngrp = VEC ? (int)(K >> 4) : 0;
+    float xv[VEC ? XG : 1][16];
     float m = 0.0f;
     if (VEC) {
 #pragma unroll
-        for (int i = 0; i < XV; ++i) {
-            const int v = i * AQ_THREADS + threadIdx.x;
-            xv[i] = (v < nvec) ? Vec4<T>::load(row, v) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < XG; ++i) {
+            const int g = i * AQ_THREADS + threadIdx.x;
+            if (g < ngrp) Group16<T>::load(row, g, xv[i]);
+            else {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) xv[i][e] = 0.0f;
+            }
         }
 #pragma unroll
-        for (int i = 0; i < XV; ++i)
-            m = fmaxf(m, fmaxf(fmaxf(fabsf(xv[i].x), fabsf(xv[i].y)), fmaxf(fabsf(xv[i].z), fabsf(xv[i].w))));
-        for (int v = XV * AQ_THREADS + threadIdx.x; v < nvec; v += AQ_THREADS) {
-            const float4 f = Vec4<T>::load(row, v);
-            m = fmaxf(m, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+        for (int i = 0; i < XG; ++i) m = absmax16(xv[i], m);
+        for (int g = XG * AQ_THREADS + threadIdx.x; g < ngrp; g += AQ_THREADS) {
+            float f[16];
+            Group16<T>::load(row, g, f);
+            m = absmax16(f, m);
         }
     } else {
         for (int64_t k = threadIdx.x; k < K; k += AQ_THREADS) m = fmaxf(m, fabsf(Elem<T>::to_f32(row[k])));
@@ -85,32 +186,24 @@ act_quant_kernel(const T *__restrict__ x, int64_t K, int8_t *__restrict__ q_plai
 
     int sum = 0;
     if (VEC) {
-        // K/4 is a multiple of 4 and AQ_THREADS is a multiple of 4, so the four lanes of a quad
-        // are always inside the row together; `mask` names exactly the lanes inside.
-        auto quant_store = [&](const float4 &f, int v, unsigned mask) {
-            // An all-zero row has scale 0 and inv = +inf: 0 * inf and NaN * inf are NaN, which
-            // quant_one maps to 0 like the reference, so the row needs no special case here.  (The
-            // kernel is bound by issued instructions -- about 25 per element at 1.4 IPC -- not by
-            // HBM, so the selects and the four adds of the row sum are worth removing.)
-            const int q0 = quant_one(f.x, inv), q1 = quant_one(f.y, inv);
-            const int q2 = quant_one(f.z, inv), q3 = quant_one(f.w, inv);
-            const uint32_t w = pack4_i8(q0, q1, q2, q3);
-            sum = __dp4a((int)w, 0x01010101, sum);
-            if (q_plain) reinterpret_cast<uint32_t *>(q_plain + r * K)[v] = w;
-            if (q_perm) reinterpret_cast<uint32_t *>(q_perm + r * K)[v] = quad_transpose(w, mask);
-        };
+        int8_t *pl = q_plain ? q_plain + r * K : nullptr, *pp = q_perm ? q_perm + r * K : nullptr;
+        if (inv < INFINITY) {                              // CTA-uniform; false for inf and NaN
 #pragma unroll
-        for (int i = 0; i < XV; ++i) {
-            const int v = i * AQ_THREADS + threadIdx.x;
-            const bool in = v < nvec;
-            const unsigned mask = __ballot_sync(0xffffffffu, in);
-            if (in) quant_store(xv[i], v, mask);
-        }
-        for (int base = XV * AQ_THREADS; base < nvec; base += AQ_THREADS) {
-            const int v = base + threadIdx.x;
-            const bool in = v < nvec;
-            const unsigned mask = __ballot_sync(0xffffffffu, in);
-            if (in) quant_store(Vec4<T>::load(row, v), v, mask);
+            for (int i = 0; i < XG; ++i) {
+                const int g = i * AQ_THREADS + threadIdx.x;
+                if (g < ngrp) sum += quant_group<true>(xv[i], inv, pl, pp, g);
+            }
+            for (int g = XG * AQ_THREADS + threadIdx.x; g < ngrp; g += AQ_THREADS) {
+                float f[16];
+                Group16<T>::load(row, g, f);
+                sum += quant_group<true>(f, inv, pl, pp, g);
+            }
+        } else {
+            for (int g = threadIdx.x; g < ngrp; g += AQ_THREADS) {
+                float f[16];
+                Group16<T>::load(row, g, f);
+                sum += quant_group<false>(f, inv, pl, pp, g);
+            }
         }
     } else {
         for (int64_t k = threadIdx.x; k < K; k += AQ_THREADS) {
@@ -345,8 +438,8 @@ static int launch_act_quant(const void *x, int64_t M, int64_t K, int8_t *q_plain
     dim3 grid((unsigned)M), block(AQ_THREADS);
     cudaError_t e;
     if (!vec) e = launch_kernel(act_quant_kernel<T, false, 1>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
-    else if (K <= 4 * 4 * AQ_THREADS) e = launch_kernel(act_quant_kernel<T, true, 4>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
-    else e = launch_kernel(act_quant_kernel<T, true, 12>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
+    else if (K <= 16 * AQ_THREADS) e = launch_kernel(act_quant_kernel<T, true, 1>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
+    else e = launch_kernel(act_quant_kernel<T, true, 3>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "act_quant_kernel: %s", cudaGetErrorString(e));
     return check_launch("act_quant_kernel");
 }

@@ -10,24 +10,19 @@
 // per layer of the decoder harness; the position is read from device memory so that a CUDA graph
 // of the step can advance it itself.
 //
-// HBM-bound on the cache reads: one CTA per (b, h), sixteen warps, a warp per key, lanes 0..D/4-1 each holding
-// four head dimensions, so a key or value row is one coalesced read of 2*D bytes; scores live in
-// shared memory (ctx floats); fp32 arithmetic throughout, bf16 in and out.
+// HBM-bound on the cache reads: one CTA per (b, h).  q.K runs on the tensor pipe (mma.sync m16n8k16,
+// the query as row 0 of A, eight keys per MMA column set, fp32 accumulation); P@V is fp32 FMAs with a
+// warp per value row, lanes 0..D/4-1 each holding four head dimensions.  Scores live in shared memory
+// (ctx floats); bf16 in and out.
 #include "common.cuh"
 
 namespace nslq {
 
 // CTA width: 16 warps when there are few (b, h) pairs (batch 1 has only H CTAs, so each must be wide),
-// 4 warps when there are enough CTAs to fill the machine several times over.
-constexpr int DA_UNROLL = 8;               // key / value rows in flight per warp
+// 8 while two CTAs per SM still hold every pair, 4 warps beyond that.
+constexpr int DA_UNROLL = 16;              // value rows in flight per warp
+constexpr int DA_KU = 2;                   // groups of eight key rows in flight per warp
 
-static __device__ __forceinline__ float4 ld_bf16x4(const __nv_bfloat16 *p)
-{
-    const uint2 r = *reinterpret_cast<const uint2 *>(p);
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&r.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&r.y));
-    return make_float4(a.x, a.y, b.x, b.y);
-}
 static __device__ __forceinline__ void st_bf16x4(__nv_bfloat16 *p, float4 v)
 {
     __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
@@ -57,8 +52,8 @@ decode_attention_kernel(const AttnParams p)
 {
     constexpr int DA_WARPS = DA_THREADS / 32;
     extern __shared__ __align__(16) float sm[];
-    float *scores = sm;                                   // [max_ctx]
-    float *xrow = sm + p.max_ctx;                         // [2][D]: q then k_new before rotation
+    float *scores = sm;                                   // [max_ctx + DA_UNROLL]
+    float *xrow = sm + p.max_ctx + DA_UNROLL;                         // [2][D]: q then k_new before rotation
     float *part = xrow + 2 * p.D;                         // [DA_WARPS][D] partial outputs, then reductions
     __shared__ float red[DA_WARPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -99,23 +94,68 @@ decode_attention_kernel(const AttnParams p)
     }
     __syncthreads();                                      // the new row is in the cache for this CTA's own reads
 
-    // ---- scores: a warp per key, DA_UNROLL keys in flight
+    // ---- scores on the tensor pipe: mma.sync.m16n8k16 with the query as row 0 of A (the other fifteen
+    // rows are zero) and eight keys as the columns of B, read straight from the cache: lane (g, t)
+    // loads dims 2t, 2t+1 and 2t+8, 2t+9 of key j0+g for every 16 dims.  About 2.6 issued
+    // instructions per key instead of 17 for a per-key shuffle reduction; the kernel was bound by
+    // issued instructions, not by HBM.
     const int n = pos + 1;
+    const int g = lane >> 2, t = lane & 3;
+    constexpr int KSTEPS = 8;                              // 16 dims each: D <= 128
+    uint32_t qa0[KSTEPS], qa2[KSTEPS];                     // A fragment registers of row 0 (zero elsewhere)
+    {
+        // the rotated query goes through shared memory once, as bf16 pairs
+        __nv_bfloat16 *qs = reinterpret_cast<__nv_bfloat16 *>(xrow);          // [D], reuses the staging rows (all reads of them are behind the barrier above)
+        if (warp == 0 && lane < nl) st_bf16x4(qs + 4 * lane, qv);
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const int d0 = 16 * ks + 2 * t, d2 = d0 + 8;
+            qa0[ks] = (g == 0 && d0 < p.D) ? *reinterpret_cast<const uint32_t *>(qs + d0) : 0u;
+            qa2[ks] = (g == 0 && d2 < p.D) ? *reinterpret_cast<const uint32_t *>(qs + d2) : 0u;
+        }
+    }
+    const int ksteps = (p.D + 15) >> 4;
+    // Loads carry no predicates: a dimension past D reads dimension D-2 instead (its query register is
+    // zero) and a key past the end reads key n-1 (its score is never stored), so every address is
+    // inside initialised cache rows and a warp keeps DA_KU * 8 key rows in flight per iteration.
+    // Only the last 16 dimensions can reach past D.
+    const int last0 = min(16 * (ksteps - 1) + 2 * t, p.D - 2) - 2 * t, last2 = min(16 * (ksteps - 1) + 2 * t + 8, p.D - 2) - 2 * t;
     float mx = -INFINITY;
-    for (int j0 = warp * DA_UNROLL; j0 < n; j0 += DA_WARPS * DA_UNROLL) {
-        float4 kv[DA_UNROLL];
+    for (int j0 = warp * (8 * DA_KU); j0 < n; j0 += DA_WARPS * (8 * DA_KU)) {
+        uint32_t b0[DA_KU][KSTEPS], b1[DA_KU][KSTEPS];
 #pragma unroll
-        for (int u = 0; u < DA_UNROLL; ++u)
-            kv[u] = (lane < nl && j0 + u < n) ? ld_bf16x4(kc + (int64_t)(j0 + u) * p.D + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int u = 0; u < DA_KU; ++u) {
+            const __nv_bfloat16 *krow = kc + (int64_t)min(j0 + 8 * u + g, n - 1) * p.D + 2 * t;
 #pragma unroll
-        for (int u = 0; u < DA_UNROLL; ++u) {
-            const float s = warp_sum(qv.x * kv[u].x + qv.y * kv[u].y + qv.z * kv[u].z + qv.w * kv[u].w) * p.sm_scale;
-            if (j0 + u < n) {
-                if (lane == 0) scores[j0 + u] = s;
-                mx = fmaxf(mx, s);
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                if (ks < ksteps - 1) {                     // warp-uniform
+                    b0[u][ks] = *reinterpret_cast<const uint32_t *>(krow + 16 * ks);
+                    b1[u][ks] = *reinterpret_cast<const uint32_t *>(krow + 16 * ks + 8);
+                } else if (ks == ksteps - 1) {
+                    b0[u][ks] = *reinterpret_cast<const uint32_t *>(krow + last0);
+                    b1[u][ks] = *reinterpret_cast<const uint32_t *>(krow + last2);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < DA_KU; ++u) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks)
+                if (ks < ksteps)
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                                 : "r"(qa0[ks]), "r"(0u), "r"(qa2[ks]), "r"(0u), "r"(b0[u][ks]), "r"(b1[u][ks]));
+            if (g == 0) {                                  // row 0 of C: keys j, j + 1
+                const int j = j0 + 8 * u + 2 * t;
+                if (j < n) { const float sv = c[0] * p.sm_scale; scores[j] = sv; mx = fmaxf(mx, sv); }
+                if (j + 1 < n) { const float sv = c[1] * p.sm_scale; scores[j + 1] = sv; mx = fmaxf(mx, sv); }
             }
         }
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if (lane == 0) red[warp] = mx;
     __syncthreads();
     mx = red[0];
@@ -127,6 +167,7 @@ decode_attention_kernel(const AttnParams p)
         scores[j] = e;
         sum += e;
     }
+    for (int j = n + threadIdx.x; j < n + DA_UNROLL; j += DA_THREADS) scores[j] = 0.0f;     // the array has DA_UNROLL spare floats
     sum = warp_sum(sum);
     __syncthreads();
     if (lane == 0) red[warp] = sum;
@@ -137,16 +178,25 @@ decode_attention_kernel(const AttnParams p)
     const float inv = 1.0f / tot;
 
     // ---- out = P @ V: a warp per value row, lanes over the head dimensions
+    // Probabilities past the end are zero (written above the last key by the softmax loop), rows past
+    // the end read row n-1 and lanes past D/4 read the row's last four dimensions: no predicates.
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int voff = 4 * min(lane, nl - 1);
     for (int j0 = warp * DA_UNROLL; j0 < n; j0 += DA_WARPS * DA_UNROLL) {
-        float4 vv[DA_UNROLL];
+        uint2 vv[DA_UNROLL];
 #pragma unroll
         for (int u = 0; u < DA_UNROLL; ++u)
-            vv[u] = (lane < nl && j0 + u < n) ? ld_bf16x4(vc + (int64_t)(j0 + u) * p.D + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+            vv[u] = *reinterpret_cast<const uint2 *>(vc + (int64_t)min(j0 + u, n - 1) * p.D + voff);
 #pragma unroll
-        for (int u = 0; u < DA_UNROLL; ++u) {
-            const float pj = j0 + u < n ? scores[j0 + u] : 0.0f;
-            acc.x += pj * vv[u].x; acc.y += pj * vv[u].y; acc.z += pj * vv[u].z; acc.w += pj * vv[u].w;
+        for (int u = 0; u < DA_UNROLL; u += 4) {
+            const float4 pj = *reinterpret_cast<const float4 *>(scores + j0 + u);   // j0 is a multiple of 4
+            const float pp[4] = {pj.x, pj.y, pj.z, pj.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint2 r = vv[u + e];
+                acc.x += pp[e] * __uint_as_float(r.x << 16); acc.y += pp[e] * __uint_as_float(r.x & 0xffff0000u);
+                acc.z += pp[e] * __uint_as_float(r.y << 16); acc.w += pp[e] * __uint_as_float(r.y & 0xffff0000u);
+            }
         }
     }
     if (lane < nl) *reinterpret_cast<float4 *>(part + warp * p.D + 4 * lane) = acc;
@@ -172,13 +222,16 @@ int decode_attention_dispatch(const void *q, const void *k_new, const void *v_ne
     if (B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || D > 128 || D % 4 != 0 || max_ctx <= 0 || max_ctx % 4 != 0 || B * H > 0x7fffffffLL)
         return fail(NSLQ_ERR_SHAPE, "nslq_decode_attention: B=%lld H=%lld Hkv=%lld D=%lld (D %% 4 == 0, D <= 128) max_ctx=%lld (a multiple of 4)",
                     (long long)B, (long long)H, (long long)Hkv, (long long)D, (long long)max_ctx);
-    const bool wide = B * H < 1024;
-    const int warps = wide ? 16 : 4;
-    const size_t smem = (size_t)(max_ctx + 2 * D + warps * D) * sizeof(float);
+    // About 640 threads fit an SM at this kernel's register count: the widest CTA that still leaves every
+    // (b, h) pair resident at once.
+    const int threads = B * H <= 148 ? 512 : (B * H <= 296 ? 256 : 128);
+    const int warps = threads / 32;
+    const size_t smem = (size_t)(max_ctx + DA_UNROLL + 2 * D + warps * D) * sizeof(float);
     if (smem > 200 * 1024) return fail(NSLQ_ERR_UNSUPPORTED, "nslq_decode_attention: max_ctx=%lld does not fit shared memory", (long long)max_ctx);
     static size_t reserved = 48 * 1024;
     if (smem > reserved) {
         if (cudaFuncSetAttribute(decode_attention_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+            cudaFuncSetAttribute(decode_attention_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
             cudaFuncSetAttribute(decode_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return fail(NSLQ_ERR_CUDA, "decode_attention_kernel: cannot reserve %zu bytes of shared memory: %s", smem,
                         cudaGetErrorString(cudaGetLastError()));
@@ -189,8 +242,10 @@ int decode_attention_dispatch(const void *q, const void *k_new, const void *v_ne
     AttnParams p{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_new, (const __nv_bfloat16 *)v_new, q_bs, k_bs, v_bs,
                  (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, cos_t, sin_t, pos, (__nv_bfloat16 *)out,
                  (int)H, (int)Hkv, (int)D, (int)max_ctx, sm_scale};
-    cudaError_t e = wide ? launch_kernel(decode_attention_kernel<512>, dim3((unsigned)(B * H)), dim3(512), smem, st, p)
-                         : launch_kernel(decode_attention_kernel<128>, dim3((unsigned)(B * H)), dim3(128), smem, st, p);
+    const dim3 grid((unsigned)(B * H));
+    cudaError_t e = threads == 512 ? launch_kernel(decode_attention_kernel<512>, grid, dim3(512), smem, st, p)
+                  : threads == 256 ? launch_kernel(decode_attention_kernel<256>, grid, dim3(256), smem, st, p)
+                                   : launch_kernel(decode_attention_kernel<128>, grid, dim3(128), smem, st, p);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "decode_attention_kernel: %s", cudaGetErrorString(e));
     return check_launch("decode_attention_kernel");
 }
