@@ -54,7 +54,7 @@ def _rope(x, cos, sin):
 class BitNetDecoder:
     """Random-init decoder of the given shape; act dtype bf16, KV cache bf16."""
 
-    def __init__(self, cfg, batch, max_ctx, seed=0):
+    def __init__(self, cfg, batch, max_ctx, seed=0, side_streams=True):
         max_ctx = (max_ctx + 3) & ~3                                    # the attention kernel wants a multiple of 4
         self.cfg, self.B, self.max_ctx = cfg, batch, max_ctx
         gen = torch.Generator(device="cuda")
@@ -82,6 +82,30 @@ class BitNetDecoder:
         self.key_index = torch.arange(max_ctx, device="cuda")
         self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
         self.graph = None
+        # Sibling projections (q/k/v, gate/up) of a decode step run on side streams: at a few dozen rows
+        # one projection occupies 25 to 68 of the 148 SMs, so three of them fit side by side.
+        self.side = [torch.cuda.Stream(), torch.cuda.Stream()] if side_streams else []
+        self.fork = False                                                # set while a decode step is issued
+
+    def _siblings(self, fns):
+        """Run independent launches; in a decode step the second and later ones go to side streams."""
+        if not self.fork or len(fns) == 1 or not self.side:
+            return [f() for f in fns]
+        cur = torch.cuda.current_stream()
+        start = torch.cuda.Event()
+        start.record(cur)
+        outs, joins = [None] * len(fns), []
+        for i, (f, st) in enumerate(zip(fns[1:], self.side), start=1):
+            st.wait_event(start)
+            with torch.cuda.stream(st):
+                outs[i] = f()
+            done = torch.cuda.Event()
+            done.record(st)
+            joins.append(done)
+        outs[0] = fns[0]()
+        for done in joins:
+            cur.wait_event(done)
+        return outs
 
     # ------------------------------------------------------------------ linears through the C ABI
     def _lin(self, layer, x2d, residual):
@@ -100,9 +124,9 @@ class BitNetDecoder:
         M = x2d.shape[0]
         if M <= 4:
             hn = _rms_norm(x2d, norm_w, self.cfg.eps)
-            return [l.forward(hn, out_dtype=torch.bfloat16) for l in layers]
+            return self._siblings([lambda l=l: l.forward(hn, out_dtype=torch.bfloat16) for l in layers])
         qa = ops.rmsnorm_act_quant_i8(x2d, norm_w, self.cfg.eps, plain=False, perm=True)
-        return [l.forward_quantized(qa, out_dtype=torch.bfloat16) for l in layers]
+        return self._siblings([lambda l=l: l.forward_quantized(qa, out_dtype=torch.bfloat16) for l in layers])
 
     # ------------------------------------------------------------------ prefill
     def prefill(self, ids):
@@ -129,6 +153,7 @@ class BitNetDecoder:
     # ------------------------------------------------------------------ one decode step (graph-capturable)
     def _step(self):
         cfg, B = self.cfg, self.B
+        self.fork = bool(self.side)
         x = self.embed[self.tokens].float()                               # [B, h] residual stream, fp32
         for li, L in enumerate(self.layers):
             q, k, v = self._norm_lin_shared([L["q"], L["k"], L["v"]], x, L["n1"])
@@ -141,6 +166,7 @@ class BitNetDecoder:
         logits = _rms_norm(x, self.final_norm, cfg.eps).to(torch.bfloat16) @ self.lm_head.t()
         self.tokens.copy_(logits.argmax(-1))
         self.pos.add_(1)
+        self.fork = False
 
     def capture(self):
         s = torch.cuda.Stream()
