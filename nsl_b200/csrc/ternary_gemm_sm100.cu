@@ -52,17 +52,17 @@ constexpr int BK = 128;                  // bytes of int8 along K per k-block = 
 constexpr int THREADS = 640;            // 20 warps: 0 TMA, 1 MMA, 4-7 and 16-19 epilogue, 8-15 unpack
 
 template <int BT> struct Cfg {
-    static_assert(BT == 128 || BT == 192, "token tile");
+    static_assert(BT == 64 || BT == 128 || BT == 192, "token tile");
     // k-blocks (128 k) per pipeline step.  One step costs the MMA warp one barrier round trip and
     // two commits whatever its size, and with one k-block per step that overhead, not the tensor
     // pipe, set the pace; the wide tile has TMEM columns for single k-block stages only.
-    static constexpr int KS = (BT == 128) ? 2 : 1;
+    static constexpr int KS = (BT == 192) ? 1 : 2;
     static constexpr int X_SUB = BT * BK;                             // one 128-byte-swizzled activation sub-tile
     static constexpr int X_BYTES = KS * X_SUB;
     static constexpr int PK_ROW = KS * (BK / 4);                      // packed bytes per weight row and step
     static constexpr int P_BYTES = BW * PK_ROW;                       // packed 2-bit weight tile as it sits in global memory
     static constexpr int T_BYTES = X_BYTES + P_BYTES;                 // one copy stage, multiple of 1024
-    static constexpr int TS = (BT == 192) ? 6 : 5;                    // copy stages in flight
+    static constexpr int TS = (BT == 192) ? 6 : (BT == 128 ? 5 : 7);  // copy stages in flight
     static constexpr int A_COLS = 32 * KS;                            // TMEM columns per operand stage
     static constexpr int AS = (512 - 2 * BT) / A_COLS;                // TMEM operand stages: 4
     static constexpr int HALF_T = BT / 2;                             // tokens per epilogue warp
@@ -74,13 +74,13 @@ template <int BT> struct Cfg {
                                       | (0u << 7)      // A format: unsigned 8-bit (codes)
                                       | (1u << 10)     // B format: signed 8-bit (activations)
                                       | ((uint32_t)(BT >> 3) << 17) | ((uint32_t)(BW >> 4) << 24);
-    // TMEM columns (512 allocated).  BT = 128: accumulators at 0 and 128, operand stages from 256.
+    // TMEM columns (512 allocated).  BT = 64, 128: accumulators at 0 and BT, operand stages from 2 BT.
     // BT = 192: accumulators at 0 and 256 (kept on 256-column boundaries), operand stages in the
     // two 64-column gaps behind them.
-    static __device__ __forceinline__ uint32_t acc_col(uint32_t buf) { return BT == 128 ? buf * 128u : buf * 256u; }
+    static __device__ __forceinline__ uint32_t acc_col(uint32_t buf) { return BT == 192 ? buf * 256u : buf * (uint32_t)BT; }
     static __device__ __forceinline__ uint32_t a_col(uint32_t a)
     {
-        return BT == 128 ? 256u + (uint32_t)A_COLS * a : 192u + 32u * (a & 1u) + 256u * (a >> 1);
+        return BT == 192 ? 192u + 32u * (a & 1u) + 256u * (a >> 1) : 2u * BT + (uint32_t)A_COLS * a;
     }
 };
 
@@ -417,6 +417,9 @@ static int gemm_one_launch(const uint8_t *w, const int8_t *q_perm, const float *
         const int64_t rounds = (tiles + sms - 1) / sms;
         return (double)rounds * bt;
     };
+    // Up to 64 rows: a 64-token tile halves the MMA work of every step (one tile per CTA, the launch is
+    // a latency chain of prologue, K / 256 steps and epilogue).
+    if (M <= 64) return launch_gemm<64>(q_perm, p, st);
     if (rounds_cost(192) <= rounds_cost(128)) return launch_gemm<192>(q_perm, p, st);
     return launch_gemm<128>(q_perm, p, st);
 }

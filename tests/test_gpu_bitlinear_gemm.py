@@ -24,6 +24,7 @@ def case(rng, M, N, K):
 @pytest.mark.parametrize("M,N,K", [
     (17, 192, 128), (64, 256, 64), (128, 192, 256), (129, 200, 320), (300, 448, 1088),
     (128, 8, 128), (40, 260, 192), (257, 1000, 3200), (130, 3200, 8640),
+    (64, 3200, 8640), (33, 19200, 640), (50, 8640, 3200),     # the 64-token tile: long K, two tiles per CTA
 ])
 def test_gemm_shapes(ops, oracle, M, N, K):
     rng = np.random.default_rng(M * 1009 + N * 17 + K)
