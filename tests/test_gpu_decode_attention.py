@@ -25,7 +25,11 @@ def rope64(x, cos, sin):
 
 
 @pytest.mark.parametrize("B,H,Hkv,D,max_ctx,pos", [(1, 32, 32, 100, 776, 0), (2, 32, 32, 100, 776, 517), (3, 8, 2, 128, 64, 63),
-                                                   (4, 4, 4, 64, 40, 7), (64, 32, 32, 100, 776, 640)])
+                                                   (4, 4, 4, 64, 40, 7), (64, 32, 32, 100, 776, 640),
+                                                   # clusters of 8 / 4 / 2 CTAs per (b, h): empty slices, ragged last slice, slice boundaries
+                                                   (1, 32, 32, 100, 776, 640), (1, 8, 8, 128, 260, 15), (1, 8, 8, 128, 260, 16), (1, 8, 8, 128, 260, 127),
+                                                   (1, 8, 8, 128, 260, 128), (2, 32, 8, 64, 520, 300), (4, 32, 32, 100, 776, 333),
+                                                   (8, 32, 32, 100, 776, 641)])
 def test_against_float64(ops, B, H, Hkv, D, max_ctx, pos):
     rng = np.random.default_rng(B * 7 + pos)
     half = D // 2
