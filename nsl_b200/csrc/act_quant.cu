@@ -9,9 +9,13 @@
 // Arithmetic follows crates/nsl-codegen/tests/bitnet_reference_impl.rs:46-70 of
 // NSL: inv = 127/scale (IEEE divide), v = x*inv, clamp to [-127,127], round half
 // away from zero, NaN -> 0.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace nslq {
+
+namespace cg = cooperative_groups;
 
 constexpr int AQ_THREADS = 256;
 
@@ -390,12 +394,100 @@ swiglu_act_quant_kernel(const T *__restrict__ gate, const T *__restrict__ up, in
     if (threadIdx.x == 0) scale_out[r] = scale;
 }
 
+// A handful of rows (decode): one CTA per row is a long serial chain (K exp/divide pairs on 256 threads)
+// on one of 148 SMs.  Here a cluster of CL CTAs shares a row: every CTA forms and keeps K/CL products
+// (at most one group of 16 per thread), the row maximum is exchanged through the cluster's shared
+// memory, and rank 0 adds up the partial row sums.  Same arithmetic, same bits as the kernel above.
+constexpr int SQC_THREADS = 128;
+template <typename T, int CL>
+__global__ void __launch_bounds__(SQC_THREADS)
+swiglu_act_quant_cluster_kernel(const T *__restrict__ gate, const T *__restrict__ up, int64_t K, int64_t ld_g, int64_t ld_u,
+                                float *__restrict__ h_out, int8_t *__restrict__ q_plain, int8_t *__restrict__ q_perm,
+                                float *__restrict__ scale_out, int32_t *__restrict__ rowsum_out)
+{
+    __shared__ float wmax[SQC_THREADS / 32];
+    __shared__ int wsum[SQC_THREADS / 32];
+    __shared__ float cmax;                // this CTA's maximum, read by its peers
+    __shared__ int csum[CL];              // rank 0's copy collects every CTA's partial row sum
+    cg::cluster_group cl = cg::this_cluster();
+    const int64_t r = blockIdx.x / CL;
+    const int rank = blockIdx.x % CL, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();
+    const int ngrp = (int)(K >> 4), per = (ngrp + CL - 1) / CL;          // per <= SQC_THREADS (checked by the host)
+    const int g = rank * per + (int)threadIdx.x;
+    const bool active = (int)threadIdx.x < per && g < ngrp;
+    float h[16];
+    float m = 0.0f;
+    if (active) {
+        float gv[16], uv[16];
+        Group16<T>::load(gate + r * ld_g, g, gv);
+        Group16<T>::load(up + r * ld_u, g, uv);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) h[e] = __fdiv_rn(gv[e], 1.0f + expf(-gv[e])) * uv[e];
+        if (h_out) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                reinterpret_cast<float4 *>(h_out + r * K)[4 * g + j] = make_float4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+        }
+        m = absmax16(h, m);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) wmax[warp] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) cmax = fmaxf(fmaxf(wmax[0], wmax[1]), fmaxf(wmax[2], wmax[3]));
+    cl.sync();                            // every CTA's maximum is published (and every CTA is running)
+    float scale = 0.0f;
+#pragma unroll
+    for (int c = 0; c < CL; ++c) scale = fmaxf(scale, *cl.map_shared_rank(&cmax, c));
+    pdl_launch_dependents();
+    const float inv = __fdiv_rn(127.0f, scale);
+    int sum = 0;
+    if (active) {
+        int8_t *pl = q_plain ? q_plain + r * K : nullptr, *pp = q_perm ? q_perm + r * K : nullptr;
+        sum = inv < INFINITY ? quant_group<true>(h, inv, pl, pp, g) : quant_group<false>(h, inv, pl, pp, g);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) wsum[warp] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) *cl.map_shared_rank(&csum[rank], 0) = wsum[0] + wsum[1] + wsum[2] + wsum[3];
+    cl.sync();                            // peers stay alive until every remote read of cmax is done; partial sums have landed
+    if (rank == 0 && threadIdx.x == 0) {
+        int tot = 0;
+#pragma unroll
+        for (int c = 0; c < CL; ++c) tot += csum[c];
+        if (rowsum_out) rowsum_out[r] = tot;
+        scale_out[r] = scale;
+    }
+}
+
 template <typename T>
 static int launch_swiglu_quant(const void *gate, const void *up, int64_t M, int64_t K, int64_t ld_g, int64_t ld_u, float *h_out, int8_t *q_plain,
                                int8_t *q_perm, float *scale, int32_t *rowsum, cudaStream_t st)
 {
     dim3 grid((unsigned)M), block(AQ_THREADS);
     cudaError_t e;
+    constexpr int CL = 8;
+    if (M <= 16 && K <= (int64_t)16 * SQC_THREADS * CL) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(M * CL));
+        cfg.blockDim = dim3(SQC_THREADS);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = CL;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = g_use_pdl ? 2 : 1;
+        e = cudaLaunchKernelEx(&cfg, swiglu_act_quant_cluster_kernel<T, CL>, (const T *)gate, (const T *)up, K, ld_g, ld_u, h_out, q_plain,
+                               q_perm, scale, rowsum);
+        if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "swiglu_act_quant_cluster_kernel: %s", cudaGetErrorString(e));
+        return check_launch("swiglu_act_quant_cluster_kernel");
+    }
     if (K <= 4 * 4 * AQ_THREADS)
         e = launch_kernel(swiglu_act_quant_kernel<T, 4>, grid, block, 0, st, (const T *)gate, (const T *)up, K, ld_g, ld_u, h_out, q_plain, q_perm, scale, rowsum);
     else
