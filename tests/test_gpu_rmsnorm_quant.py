@@ -65,7 +65,7 @@ def test_feeds_bitlinear(ops, oracle):
     assert np.array_equal(host(acc), host(acc2)) and np.array_equal(host(y), host(y2))
 
 
-@pytest.mark.parametrize("M,K", [(1, 8640), (9, 8640), (130, 1024), (2, 64)])
+@pytest.mark.parametrize("M,K", [(1, 8640), (9, 8640), (64, 8640), (65, 3200), (130, 1024), (2, 64), (3, 12288), (2, 9600)])
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
 def test_swiglu_then_quant(ops, oracle, M, K, dt):
     """h = silu(gate) * up in fp32 against float64 (rel 1e-6 + a floor for the tiny outputs), the
@@ -104,3 +104,17 @@ def test_swiglu_on_column_slices(ops):
     torch.cuda.synchronize()
     for key in ("h", "q_plain", "q_perm", "scale", "rowsum"):
         assert torch.equal(a[key], b[key]), key
+
+
+def test_swiglu_cluster_rows_equal_single_cta_rows(ops):
+    """Up to 64 rows a cluster of CTAs shares a row, beyond that one CTA takes it: same bits either way."""
+    g_ = torch.Generator(device="cuda")
+    g_.manual_seed(5)
+    M, K = 70, 8640
+    g = (torch.randn(M, K, device="cuda", generator=g_) * 3).to(torch.bfloat16)
+    u = torch.randn(M, K, device="cuda", generator=g_).to(torch.bfloat16)
+    big = ops.swiglu_act_quant_i8(g, u, plain=True, perm=True, return_h=True)
+    small = ops.swiglu_act_quant_i8(g[:7].contiguous(), u[:7].contiguous(), plain=True, perm=True, return_h=True)
+    torch.cuda.synchronize()
+    for key in ("h", "q_plain", "q_perm", "scale", "rowsum"):
+        assert torch.equal(big[key][:7], small[key]), key
