@@ -281,6 +281,17 @@ rmsnorm_act_quant_kernel(const T *__restrict__ x, const float *__restrict__ weig
         const int v = i * AQ_THREADS + threadIdx.x;
         xv[i] = (v < nvec) ? Vec4<T>::load(row, v) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    // Short rows: the norm weights are fetched now, not behind the reduction (a second memory round trip
+    // in a kernel that is one latency chain).  Long rows have no registers to spare for that.
+    constexpr bool WPRE = XV <= 4;
+    float4 wv[WPRE ? XV : 1];
+    if (WPRE) {
+#pragma unroll
+        for (int i = 0; i < XV; ++i) {
+            const int v = i * AQ_THREADS + threadIdx.x;
+            wv[i] = (v < nvec) ? __ldg(reinterpret_cast<const float4 *>(weight) + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
 #pragma unroll
     for (int i = 0; i < XV; ++i)
         sq += (double)xv[i].x * xv[i].x + (double)xv[i].y * xv[i].y + (double)xv[i].z * xv[i].z + (double)xv[i].w * xv[i].w;
@@ -291,7 +302,7 @@ rmsnorm_act_quant_kernel(const T *__restrict__ x, const float *__restrict__ weig
     for (int i = 0; i < XV; ++i) {
         const int v = i * AQ_THREADS + threadIdx.x;
         if (v < nvec) {
-            const float4 w = reinterpret_cast<const float4 *>(weight)[v];
+            const float4 w = WPRE ? wv[WPRE ? i : 0] : reinterpret_cast<const float4 *>(weight)[v];
             float4 h;
             h.x = norm_one(xv[i].x, rms, rinv, w.x); h.y = norm_one(xv[i].y, rms, rinv, w.y);
             h.z = norm_one(xv[i].z, rms, rinv, w.z); h.w = norm_one(xv[i].w, rms, rinv, w.w);
