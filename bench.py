@@ -210,6 +210,7 @@ class PrefillGemm(Workload):
         self.ws = torch.empty(int(ops.lib().nslq_bitlinear_workspace_bytes(self.M, self.F)), dtype=torch.uint8,
                               device="cuda")
         self.y_host = torch.empty(self.M * self.F, dtype=torch.float32).pin_memory()
+        self.comm = torch.cuda.Stream() if world > 1 else None
         self.kernel_launches = 2                               # per kernel_only() pass
         self.launches_per_step = 4                             # 2 x (act quant + GEMM)
         self.h2d = self.d2h = self.M * (self.H + self.F) * 4
@@ -228,8 +229,24 @@ class PrefillGemm(Workload):
         self.gather(self.ys[i], self.ygs[i])
 
     def step(self):
+        if self.world == 1:
+            for i in range(2):
+                self.one_call(i, self.xs[i])
+            return
+        # The two projections are independent calls: the all-gather of the first one's output shards runs
+        # on a second stream under the second one's quantisation and GEMM (both captured in the graph).
+        torch = self.torch
+        cur = torch.cuda.current_stream()
         for i in range(2):
-            self.one_call(i, self.xs[i])
+            self.layers[i].forward(self.xs[i], out=self.ys[i], workspace=self.ws)
+            ready = torch.cuda.Event()
+            ready.record(cur)
+            self.comm.wait_event(ready)
+            with torch.cuda.stream(self.comm):
+                self.gather(self.ys[i], self.ygs[i])
+        done = torch.cuda.Event()
+        done.record(self.comm)
+        cur.wait_event(done)
 
     def kernel_only(self):
         for i in range(2):
@@ -628,7 +645,7 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seed 0)",
             "config": {"workload": wl.name, "cuda_graph": m["graph"], "dependent_launch": not args.no_pdl,
                        "streams": getattr(wl, "streams", 1), "l2": wl.l2_note,
-                       "parallelism": ("column-sharded x%d + NCCL all-gather" % world) if world > 1 else "single GPU"},
+                       "parallelism": ("column-sharded x%d + NCCL all-gather (the first projection's gather overlaps the second projection)" % world) if world > 1 else "single GPU"},
             "e2e": {"value": round(m["e2e"], 3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
                     "d2h_bytes_per_step": wl.d2h},
             "gpu_launches": wl.launches_per_step * args.steps,
