@@ -223,6 +223,10 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     const uint32_t tmem_base = *slot_ptr;
 
     pdl_wait();   // activations, scales and row sums come from the preceding kernel
+    // The next kernel of the stream may be scheduled from here on: it takes the SMs this grid leaves idle
+    // (fewer tiles than SMs, the last partial round) for its own prologue and waits for this grid's
+    // completion before it touches memory.
+    pdl_launch_dependents();
 
     if (warp == 0) {
         // ---------------- TMA producer (activation tile + packed weight tile)
@@ -360,7 +364,6 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
     }
     // ---------------- teardown: every thread arrives here, on success and after an expired wait
-    pdl_launch_dependents();
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -400,7 +403,8 @@ static int launch_gemm(const void *q_perm, gemm::Params &p, cudaStream_t st)
     p.tiles_w = (int)((p.N + gemm::BW - 1) / gemm::BW);
     const int tiles = p.tiles_t * p.tiles_w;
     const int grid = tiles < sm100::sm_count() ? tiles : sm100::sm_count();
-    gemm::ternary_gemm_kernel<BT><<<grid, gemm::THREADS, C::SMEM, st>>>(tmap_x, tmap_w, p);
+    cudaError_t e = launch_kernel(gemm::ternary_gemm_kernel<BT>, dim3(grid), dim3(gemm::THREADS), (size_t)C::SMEM, st, tmap_x, tmap_w, p);
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "ternary_gemm_kernel: %s", cudaGetErrorString(e));
     return check_launch("ternary_gemm_kernel");
 }
 
