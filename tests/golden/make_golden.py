@@ -19,7 +19,9 @@ def flatten(rows):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit(__doc__)
+    ref = sys.argv[1]
     src = os.path.join(ref, "crates/nsl-codegen/tests/fixtures/bitnet_reference_outputs.json")
     with open(src) as f:
         doc = json.load(f)
