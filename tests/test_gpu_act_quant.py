@@ -65,6 +65,17 @@ def test_adversarial_rows(ops, oracle):
     check(ops, oracle, np.stack(rows))
 
 
+def test_every_tie_and_its_neighbours(ops, oracle):
+    """Scale 127 makes x*inv = x: every k + 0.5 and the floats on either side of it, both signs."""
+    k = np.arange(0, 127, dtype=np.float32) + np.float32(0.5)
+    below, above = np.nextafter(k, np.float32(-1e9)), np.nextafter(k, np.float32(1e9))
+    vals = np.concatenate([k, below, above])
+    row = np.concatenate([vals, -vals, [np.float32(127.0)]]).astype(np.float32)
+    row = np.concatenate([row, np.zeros((-len(row)) % 16, np.float32)])
+    q = check(ops, oracle, np.stack([row, row[::-1].copy()]))
+    assert q[0, 0] == 1 and q[0, 127] == 0 and q[0, 254] == 1          # 0.5, just below, just above
+
+
 @pytest.mark.parametrize("dt", ["float16", "bfloat16"])
 def test_half_inputs(ops, oracle, dt):
     rng = np.random.default_rng(5)
