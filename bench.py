@@ -211,6 +211,7 @@ class PrefillGemm(Workload):
                               device="cuda")
         self.y_host = torch.empty(self.M * self.F, dtype=torch.float32).pin_memory()
         self.comm = torch.cuda.Stream() if world > 1 else None
+        self.e2e_streams = None
         self.kernel_launches = 2                               # per kernel_only() pass
         self.launches_per_step = 4                             # 2 x (act quant + GEMM)
         self.h2d = self.d2h = self.M * (self.H + self.F) * 4
@@ -253,11 +254,39 @@ class PrefillGemm(Workload):
             self.layers[i].forward_quantized(self.qas[i], out=self.ys[i])
 
     def e2e_step(self, it):
+        """Pinned host x -> device -> quantise + GEMM -> pinned host y, both projections.  The copies in
+        and out run on their own streams, so the 71 MB result of the first projection leaves while the
+        71 MB input of the second arrives (PCIe is full duplex); every buffer is single and guarded by
+        events, and the step ends only when its last result is on the host."""
+        torch = self.torch
+        cur = torch.cuda.current_stream()
+        if self.e2e_streams is None:
+            self.e2e_streams = (torch.cuda.Stream(), torch.cuda.Stream())
+            self.e2e_consumed = [None, None]                 # x staging buffer i read by its projection
+            self.e2e_out_done = [None, None]                 # y buffer i copied to the host
+        s_in, s_out = self.e2e_streams
         for i in range(2):
-            self.xst[i].copy_(self.xh[i], non_blocking=True)
+            if self.e2e_consumed[i] is not None:
+                s_in.wait_event(self.e2e_consumed[i])
+            with torch.cuda.stream(s_in):
+                self.xst[i].copy_(self.xh[i], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(s_in)
+            cur.wait_event(arrived)
+            if self.e2e_out_done[i] is not None:
+                cur.wait_event(self.e2e_out_done[i])
             self.one_call(i, self.xst[i])
+            computed = torch.cuda.Event()
+            computed.record(cur)
+            self.e2e_consumed[i] = computed
+            s_out.wait_event(computed)
             out = self.ygs[i] if self.world > 1 else self.ys[i]
-            self.y_host[:out.numel()].copy_(out.view(-1), non_blocking=True)
+            with torch.cuda.stream(s_out):
+                self.y_host[:out.numel()].copy_(out.view(-1), non_blocking=True)
+                left = torch.cuda.Event()
+                left.record(s_out)
+            self.e2e_out_done[i] = left
+        cur.wait_event(self.e2e_out_done[1])                  # the timed stream sees the last byte reach the host
 
     @classmethod
     def cpu_baseline(cls, threads, budget_s=15.0):
