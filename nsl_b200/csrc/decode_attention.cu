@@ -68,6 +68,16 @@ decode_attention_kernel(const AttnParams p)
     const int bh = blockIdx.x / SPLIT, rank = blockIdx.x % SPLIT;     // the cluster spans SPLIT consecutive CTAs
     const int b = bh / p.H, h = bh % p.H, hk = h / (p.H / p.Hkv);
     pdl_wait();
+    // q and k_new do not depend on the position: their loads go out before the position is read, not
+    // behind the branch on it (2 D <= 256 values, at most two per thread).
+    const __nv_bfloat16 *qg = p.q + (int64_t)b * p.q_bs + (int64_t)h * p.D;
+    const __nv_bfloat16 *kg = p.k_new + (int64_t)b * p.k_bs + (int64_t)hk * p.D;
+    float xin[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int d = (int)threadIdx.x + u * DA_THREADS;
+        xin[u] = d < 2 * p.D ? __bfloat162float(d < p.D ? qg[d] : kg[d - p.D]) : 0.0f;
+    }
     const int pos = (int)*p.pos;
     if (pos < 0 || pos >= p.max_ctx) return;              // nothing sensible to do; the host checks the range it can see (every CTA of a cluster takes this exit together)
     if (SPLIT > 1) cg::this_cluster().sync();             // every CTA of the cluster runs before anyone writes into rank 0's shared memory
@@ -77,15 +87,16 @@ decode_attention_kernel(const AttnParams p)
     const int chunk = SPLIT > 1 ? (((n + SPLIT - 1) / SPLIT + 15) & ~15) : n;
     const int jb = rank * chunk, je = min(n, jb + chunk);
     const bool owns_new = SPLIT == 1 || (jb <= pos && pos < je);         // the slice that holds the new row writes it
-    const __nv_bfloat16 *qg = p.q + (int64_t)b * p.q_bs + (int64_t)h * p.D;
-    const __nv_bfloat16 *kg = p.k_new + (int64_t)b * p.k_bs + (int64_t)hk * p.D;
     const __nv_bfloat16 *vg = p.v_new + (int64_t)b * p.v_bs + (int64_t)hk * p.D;
     __nv_bfloat16 *kc = p.k_cache + ((int64_t)b * p.Hkv + hk) * p.max_ctx * p.D;
     __nv_bfloat16 *vc = p.v_cache + ((int64_t)b * p.Hkv + hk) * p.max_ctx * p.D;
 
     // ---- RoPE of q and k_new; append k, v (every head of a KV group writes the same bytes)
-    for (int d = threadIdx.x; d < 2 * p.D; d += DA_THREADS)
-        xrow[d] = __bfloat162float(d < p.D ? qg[d] : kg[d - p.D]);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int d = (int)threadIdx.x + u * DA_THREADS;
+        if (d < 2 * p.D) xrow[d] = xin[u];
+    }
     __syncthreads();
     float4 qv = make_float4(0.f, 0.f, 0.f, 0.f);         // this lane's four dimensions of the rotated, scaled query
     if (lane < nl) {
