@@ -431,7 +431,7 @@ class W4A16(Workload):
         self.name = "w4a16_m%d_n11008_k4096_g128" % M
         gemm = M > 16
         self.bound, self.unit = ("tensor", "TFLOPS") if gemm else ("hbm", "GB/s")
-        self.kernel_name = "w4a16_gemm_kernel" if gemm else ("w4a16_decode_kernel" if M > 8 else "w4a16_gemv_persistent_kernel")
+        self.kernel_name = "w4a16_gemm_kernel" if gemm else ("w4a16_decode_kernel" if M >= 4 else "w4a16_gemv_persistent_kernel")
         self.LAYERS = 8 if gemm else 24
         gen = torch.Generator(device="cuda")
         gen.manual_seed(0)

@@ -88,9 +88,10 @@ static inline bool decode_pays(int64_t M, int64_t N, int64_t K)
 }
 
 // W4A16, M <= 16: the tensor-memory kernel (w4a16_decode_kernel) against the mma.sync kernel
-// (w4a16_gemv_persistent_kernel).  Measured on [11008, 4096], group 128: 15.7 vs 13.1 us at M = 1,
-// 23.3 vs 35 us at M = 16 -- the new kernel's cost barely depends on M, the old one's grows with it.
-static inline bool w4_decode_pays(int64_t M, int64_t, int64_t) { return M > 8; }
+// (w4a16_gemv_persistent_kernel).  Measured on [11008, 4096], group 128: 14.8 vs 13.1 us at M = 1,
+// 15.1 vs 16.7 at M = 4, 16.9 vs 22.7 at M = 8, 19.2 vs 35 at M = 16 -- the new kernel's cost barely
+// depends on M, the old one's grows with it.
+static inline bool w4_decode_pays(int64_t M, int64_t, int64_t) { return M >= 4; }
 
 static inline int out_elem_size(int dt)
 {

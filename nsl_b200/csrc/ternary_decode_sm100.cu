@@ -174,9 +174,11 @@ ternary_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p
                 // q holds, per group of 16 k, four words: word i = class i of the group's four bytes
                 const int groups16 = (int)(p.K >> 4), all = groups16 * p.M;
                 const uint4 *src = reinterpret_cast<const uint4 *>(p.q);
+                // (token, group) of this thread's element, advanced by SW per element: no division in the loop
+                int m = tq / groups16, gg = tq - m * groups16;
+                const int adv_m = SW / groups16, adv_g = SW - adv_m * groups16;
 #pragma unroll 4
                 for (int e = tq; e < all; e += SW) {
-                    const int m = e / groups16, gg = e - m * groups16;
                     const int kb = gg >> 3, g = gg & 7;
                     const uint4 v = __ldg(src + e);
                     uint8_t *blk = base_ptr + (size_t)kb * XB_BYTES;
@@ -184,6 +186,9 @@ ternary_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p
                     *reinterpret_cast<uint32_t *>(blk + xs_off(m, 32 + 4 * g)) = v.y;
                     *reinterpret_cast<uint32_t *>(blk + xs_off(m, 64 + 4 * g)) = v.z;
                     *reinterpret_cast<uint32_t *>(blk + xs_off(m, 96 + 4 * g)) = v.w;
+                    m += adv_m;
+                    gg += adv_g;
+                    if (gg >= groups16) { gg -= groups16; ++m; }
                 }
                 if (tq < p.M) { scale_s[tq] = p.scale[tq]; rowsum_s[tq] = p.rowsum[tq]; }
             } else {

@@ -169,19 +169,29 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
             const int chunks_row = (int)(p.K >> 3), all = p.nkb * 16 * p.M;      // padded to whole 128-k blocks
             const uint4 *src = reinterpret_cast<const uint4 *>(p.x);
             constexpr int UL = 8;                                  // loads in flight per thread
+            // (token, chunk in the padded row) of this thread's element, advanced by SW per element: one
+            // division per thread instead of four per element (they made this stage ten microseconds
+            // long at sixteen tokens).
+            const int row_chunks = p.nkb * 16;
+            int m_next = tq / row_chunks, cc_next = tq - m_next * row_chunks;
+            const int adv_m = SW / row_chunks, adv_c = SW - adv_m * row_chunks;
             for (int e0 = 0; e0 < all; e0 += UL * SW) {
                 uint4 vv[UL];
+                int mm[UL], cq[UL];
 #pragma unroll
                 for (int u = 0; u < UL; ++u) {
                     const int e = e0 + u * SW + tq;
-                    const int m = e < all ? e / (p.nkb * 16) : 0, cc = e < all ? e - m * (p.nkb * 16) : 0;
-                    vv[u] = (e < all && cc < chunks_row) ? __ldg(src + (int64_t)m * chunks_row + cc) : make_uint4(0, 0, 0, 0);
+                    mm[u] = m_next; cq[u] = cc_next;
+                    m_next += adv_m;
+                    cc_next += adv_c;
+                    if (cc_next >= row_chunks) { cc_next -= row_chunks; ++m_next; }
+                    vv[u] = (e < all && cq[u] < chunks_row) ? __ldg(src + (int64_t)mm[u] * chunks_row + cq[u]) : make_uint4(0, 0, 0, 0);
                 }
 #pragma unroll
                 for (int u = 0; u < UL; ++u) {
                     const int e = e0 + u * SW + tq;
                     const bool in = e < all;
-                    const int m = in ? e / (p.nkb * 16) : 0, cc = in ? e - m * (p.nkb * 16) : 0;   // chunk index in the padded row
+                    const int m = in ? mm[u] : 0, cc = in ? cq[u] : 0;   // chunk index in the padded row
                     const uint4 v = vv[u];
                     // (e0..e7) -> positions (e0,e4,e1,e5,e2,e6,e3,e7)
                     uint4 o;
@@ -309,6 +319,21 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
                 asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
                 for (int st = 0; st < p.nsteps && ok; ++st, ++it) {
                     const uint32_t sb = it % NB;
+                    // The step's group constants and token sums do not depend on the MMAs: they are read
+                    // before the wait, so their latency hides behind it (this warp is alone on its
+                    // scheduler for most of the tile and nothing else would cover it).
+                    float sc[KS], cm[KS];
+                    float4 xs[KS][NTOK / 4];
+#pragma unroll
+                    for (int ks = 0; ks < KS; ++ks) {
+                        const int kb = st * KS + ks, kbc = min(kb, p.nkb - 1);
+                        const int g = (int)(((uint32_t)kbc * (uint32_t)p.gmul) >> 16);   // kb / (128-k blocks per group), no divide
+                        sc[ks] = kb < p.nkb ? tab_s[g * BW] : 0.0f;
+                        cm[ks] = -(MAGIC + tab_z[g * BW]);
+                        const float4 *xs4 = reinterpret_cast<const float4 *>(xsum + kbc * NTOK);
+#pragma unroll
+                        for (int t4 = 0; t4 < NTOK / 4; ++t4) xs[ks][t4] = xs4[t4];
+                    }
                     if (!(ok = mbar_wait_warp(done_bar(it), done_par(it), 0x731))) break;
                     tc_fence_after();
                     uint32_t r[KS * NTOK];
@@ -316,21 +341,16 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
                     tc_fence_before();
                     mbar_arrive(acce_bar(sb));
 #pragma unroll
-                    for (int ks = 0; ks < KS; ++ks) {
-                        const int kb = st * KS + ks;
-                        if (kb < p.nkb) {                                    // warp-uniform
-                            const int g = (int)(((uint32_t)kb * (uint32_t)p.gmul) >> 16);   // kb / (128-k blocks per group), no divide
-                            const float sc = tab_s[g * BW], c = MAGIC + tab_z[g * BW];
-                            const float4 *xs4 = reinterpret_cast<const float4 *>(xsum + kb * NTOK);
+                    for (int t4 = 0; t4 < NTOK / 4; ++t4) {
+                        if (4 * t4 >= p.M) continue;                         // warp-uniform: only the tokens that exist
 #pragma unroll
-                            for (int t4 = 0; t4 < NTOK / 4; ++t4) {
-                                const float4 xs = xs4[t4];
-                                const float xe[4] = {xs.x, xs.y, xs.z, xs.w};
+                        for (int ks = 0; ks < KS; ++ks) {
+                            if (st * KS + ks >= p.nkb) continue;             // warp-uniform: its accumulator was never written
+                            const float xe[4] = {xs[ks][t4].x, xs[ks][t4].y, xs[ks][t4].z, xs[ks][t4].w};
 #pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const int t = 4 * t4 + e;
-                                    yacc[t] = fmaf(sc, fmaf(-c, xe[e], __uint_as_float(r[ks * NTOK + t])), yacc[t]);
-                                }
+                            for (int e = 0; e < 4; ++e) {
+                                const int t = 4 * t4 + e;
+                                yacc[t] = fmaf(sc[ks], fmaf(cm[ks], xe[e], __uint_as_float(r[ks * NTOK + t])), yacc[t]);
                             }
                         }
                     }
