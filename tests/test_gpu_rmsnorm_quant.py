@@ -118,3 +118,22 @@ def test_swiglu_cluster_rows_equal_single_cta_rows(ops):
     torch.cuda.synchronize()
     for key in ("h", "q_plain", "q_perm", "scale", "rowsum"):
         assert torch.equal(big[key][:7], small[key]), key
+
+
+def test_rmsnorm_bits_when_the_sum_of_squares_is_exact(ops, oracle):
+    """Power-of-two magnitudes make the f64 sum of squares independent of the summation order, so every
+    normalised value must equal the oracle's bit for bit -- including the elements that leave the fast
+    path of the kernel's arithmetic (zeros, results below the normal float range)."""
+    rng = np.random.default_rng(77)
+    M, K = 6, 256
+    x = (np.exp2(rng.integers(-12, 13, size=(M, K))) * rng.choice([-1.0, 1.0], size=(M, K))).astype(np.float32)
+    x[:, 5] = 0.0
+    x[:, 9] = -0.0
+    x[:, 17] = np.float32(1.2e-38)
+    x[:, 33] = np.float32(-3e-41)            # denormal input
+    w = rng.uniform(0.5, 1.5, size=K).astype(np.float32)
+    w[40] = np.float32(1e-30)                # pushes one product below the normal range
+    out = ops.rmsnorm_act_quant_i8(dev(x), dev(w), 1e-5, plain=True, perm=True, return_h=True)
+    torch.cuda.synchronize()
+    h, h_ref = host(out["h"]), oracle.rmsnorm_f32(x, w, 1e-5)
+    assert np.array_equal(h.view(np.uint32), h_ref.view(np.uint32))
