@@ -62,7 +62,7 @@ template <int BT> struct Cfg {
     static constexpr int PK_ROW = KS * (BK / 4);                      // packed bytes per weight row and step
     static constexpr int P_BYTES = BW * PK_ROW;                       // packed 2-bit weight tile as it sits in global memory
     static constexpr int T_BYTES = X_BYTES + P_BYTES;                 // one copy stage, multiple of 1024
-    static constexpr int TS = (BT == 192) ? 6 : (BT == 128 ? 5 : 7);  // copy stages in flight
+    static constexpr int TS = (BT == 128) ? 5 : 7;                      // copy stages in flight
     static constexpr int A_COLS = 32 * KS;                            // TMEM columns per operand stage
     static constexpr int AS = (512 - 2 * BT) / A_COLS;                // TMEM operand stages: 4
     static constexpr int HALF_T = BT / 2;                             // tokens per epilogue warp
