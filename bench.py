@@ -21,6 +21,8 @@ configurations):
 One JSON line is printed by rank 0; at N=1 the default run appends the other workloads' figures
 under "also" and the decoder's under "decoder".  With --gpus N > 1 (launched by torchrun) the weights are column-sharded over the
 ranks, x is replicated and each output is all-gathered with NCCL: total work is fixed ("strong").
+"e2e" is the same step fed from pinned host memory and read back to pinned host memory inside the
+timed region; the prefill step keeps the copies in and out on streams of their own (PCIe is full duplex).
 
 --impl reference times the reference's CPU arithmetic for the same workload (the C restatement
 under oracle/, all host threads) on a bounded sample and prints the same line with
