@@ -162,10 +162,11 @@ class Workload:
     key = name = unit = dtype = kernel_name = ""
     bound = "hbm"
 
+    comm = None
+
     def gather(self, y_local, gathered):
         if self.world > 1:
-            from nsl_b200 import sharding
-            sharding.all_gather_columns(y_local, gathered)
+            self.comm.allgather_cols(y_local, gathered=gathered)     # ncclAllGather, called by the library
 
     def roofline(self, peaks, kernel_ms):
         per_launch = self.kernel_work()                      # this rank's shard, one launch
@@ -185,7 +186,18 @@ class Workload:
 
 
 class PrefillGemm(Workload):
-    """BitLinear prefill GEMM (configs[1]): up/gate then down projection, M=2048."""
+    """BitLinear prefill GEMM (configs[1]): up/gate then down projection, M=2048.
+
+    x is fp32 as the configuration states; y is bf16, the output type of the reference's own GPU
+    kernel (crates/nsl-codegen/src/bitnet/mod.rs:133-307 emits f16/bf16 stores) -- the fp32 values
+    are bit-equal to the CPU path and rounded once (out_dtype="f32" runs the fp32-output variant).
+
+    N > 1: the weight rows are sharded over the ranks and x is replicated.  gather="peer" (default):
+    the GEMM epilogue stores every finished tile into all ranks' copies of the [M, N] result over
+    NVLink (nslq_bitlinear_forward_gathered), the two projections run on two streams, and a flag
+    barrier closes the step.  gather="nccl": each rank writes its [M, N/G] block and the library
+    calls ncclAllGather (nslq_allgather_cols), the first projection's gather overlapping the second
+    projection."""
     key, name = "prefill_gemm", "bitlinear_prefill_gemm_m2048_up8640x3200_down3200x8640"
     unit, dtype, bound, int8 = "TOPS", "int8 x int2 -> int32", "tensor", True
     kernel_name = "ternary_gemm_kernel"
@@ -193,31 +205,44 @@ class PrefillGemm(Workload):
     SHAPES = [(8640, 3200), (3200, 8640)]                      # (N, K): up/gate, down
     OPS_PER_PROJ = 2 * 2048 * 3200 * 8640
 
-    def __init__(self, torch, ops, rank, world, **_):
+    def __init__(self, torch, ops, rank, world, comm=None, gather="peer", out_dtype="bf16", **_):
         self.torch, self.ops, self.rank, self.world = torch, ops, rank, world
+        self.comm, self.mode = comm, (gather if world > 1 else "none")
+        self.ydt = torch.bfloat16 if out_dtype == "bf16" else torch.float32
+        self.out_dtype = out_dtype
+        es = 2 if out_dtype == "bf16" else 4
         gen = torch.Generator(device="cuda")
         gen.manual_seed(0)
-        self.layers, self.xs, self.ys, self.ygs, self.qas, self.xh, self.xst = [], [], [], [], [], [], []
+        self.layers, self.xs, self.ys, self.ygs, self.qas, self.xh, self.xst, self.wss = [], [], [], [], [], [], [], []
+        self.full_w = []
         for n, k in self.SHAPES:
             r0, rows = ops.shard_rows(n, world, rank)
             full = device_ternary(torch, n, k, gen)            # same bytes on every rank (seed 0)
             self.layers.append(ops.BitLinear(full[r0:r0 + rows].contiguous(), 0.02))
+            self.full_w.append(full if (world > 1 and rank == 0) else None)
             x = torch.randn(self.M, k, device="cuda", generator=gen)
             self.xs.append(x)
             self.xh.append(x.cpu().pin_memory())
             self.xst.append(torch.empty_like(x))
-            self.ys.append(torch.empty(self.M, rows, device="cuda"))
-            self.ygs.append(torch.empty(world, self.M, rows, device="cuda") if world > 1 else None)
+            self.ys.append(torch.empty(self.M, rows, device="cuda", dtype=self.ydt))
+            if world > 1 and self.mode == "peer":
+                self.ygs.append(comm.symm_empty((self.M, n), self.ydt))        # [M, N], every rank stores into it
+            elif world > 1:
+                self.ygs.append(torch.empty(world, self.M, rows, device="cuda", dtype=self.ydt))
+            else:
+                self.ygs.append(None)
             self.qas.append(ops.act_quant_i8(x, plain=False, perm=True))
-        self.ws = torch.empty(int(ops.lib().nslq_bitlinear_workspace_bytes(self.M, self.F)), dtype=torch.uint8,
-                              device="cuda")
-        self.y_host = torch.empty(self.M * self.F, dtype=torch.float32).pin_memory()
-        self.comm = torch.cuda.Stream() if world > 1 else None
+            self.wss.append(torch.empty(int(ops.lib().nslq_bitlinear_workspace_bytes(self.M, k)), dtype=torch.uint8,
+                                        device="cuda"))
+        self.y_host = torch.empty(self.M * self.F, dtype=self.ydt).pin_memory()
+        self.side = torch.cuda.Stream() if world > 1 else None
         self.e2e_streams = None
         self.kernel_launches = 2                               # per kernel_only() pass
-        self.launches_per_step = 4                             # 2 x (act quant + GEMM)
-        self.h2d = self.d2h = self.M * (self.H + self.F) * 4
-        self.l2_note = "inputs larger than L2 (26+71 MB of x, 14 MB of W, 97 MB of y per step)"
+        # 2 x (act quant + GEMM); sharded: + 2 flag barriers (peer) or 2 NCCL all-gathers, not counted as ours
+        self.launches_per_step = 4 + (2 if self.mode == "peer" else 0)
+        self.h2d = self.M * (self.H + self.F) * 4
+        self.d2h = self.M * (self.H + self.F) * es
+        self.l2_note = "inputs larger than L2 (26+71 MB of x, 14 MB of W, %d MB of y per step)" % (self.d2h // 1000000)
 
     def units_per_step(self):
         return 2 * self.OPS_PER_PROJ / 1e12
@@ -228,40 +253,89 @@ class PrefillGemm(Workload):
         return self.OPS_PER_PROJ / self.world
 
     def one_call(self, i, x):
-        self.layers[i].forward(x, out=self.ys[i], workspace=self.ws)
-        self.gather(self.ys[i], self.ygs[i])
+        if self.mode == "peer":
+            self.layers[i].forward_gathered(self.comm, x, self.ygs[i], workspace=self.wss[i])
+        else:
+            self.layers[i].forward(x, out=self.ys[i], workspace=self.wss[i])
+            if self.mode == "nccl":
+                self.comm.allgather_cols(self.ys[i], gathered=self.ygs[i])
 
-    def step(self):
+    def step(self, xs=None):
+        xs = xs or self.xs
         if self.world == 1:
             for i in range(2):
-                self.one_call(i, self.xs[i])
+                self.one_call(i, xs[i])
             return
-        # The two projections are independent calls: the all-gather of the first one's output shards runs
-        # on a second stream under the second one's quantisation and GEMM (both captured in the graph).
         torch = self.torch
         cur = torch.cuda.current_stream()
+        if self.mode == "peer":
+            # The peers may still be reading the previous step's result: nobody stores before everybody
+            # has arrived.  Then the two projections (independent calls) run side by side on two streams,
+            # their tiles going out over NVLink as they finish, and a second barrier says "all landed".
+            self.comm.barrier()
+            fork = torch.cuda.Event()
+            fork.record(cur)
+            self.side.wait_event(fork)
+            with torch.cuda.stream(self.side):
+                self.one_call(1, xs[1])
+                join = torch.cuda.Event()
+                join.record(self.side)
+            self.one_call(0, xs[0])
+            cur.wait_event(join)
+            self.comm.barrier()
+            return
+        # NCCL plane: the all-gather of the first projection's shards runs on a second stream under the
+        # second projection's quantisation and GEMM (both captured in the graph).
         for i in range(2):
-            self.layers[i].forward(self.xs[i], out=self.ys[i], workspace=self.ws)
+            self.layers[i].forward(xs[i], out=self.ys[i], workspace=self.wss[i])
             ready = torch.cuda.Event()
             ready.record(cur)
-            self.comm.wait_event(ready)
-            with torch.cuda.stream(self.comm):
-                self.gather(self.ys[i], self.ygs[i])
+            self.side.wait_event(ready)
+            with torch.cuda.stream(self.side):
+                self.comm.allgather_cols(self.ys[i], gathered=self.ygs[i])
         done = torch.cuda.Event()
-        done.record(self.comm)
+        done.record(self.side)
         cur.wait_event(done)
 
     def kernel_only(self):
         for i in range(2):
-            self.layers[i].forward_quantized(self.qas[i], out=self.ys[i])
+            if self.mode == "peer":
+                self.layers[i].forward_quantized_gathered(self.comm, self.qas[i], self.ygs[i])
+            else:
+                self.layers[i].forward_quantized(self.qas[i], out=self.ys[i])
+
+    def gather_check(self):
+        """Rank 0: the gathered [M, N] of both projections against the unsharded kernel on a row sample
+        (the unsharded kernel is what the parity tests hold against the CPU path)."""
+        if self.world == 1 or self.rank != 0:
+            return None
+        torch, ok = self.torch, True
+        rows = torch.arange(0, self.M, 16, device="cuda")
+        for i, (n, k) in enumerate(self.SHAPES):
+            ref = self.ops.BitLinear(self.full_w[i], 0.02).forward(self.xs[i][rows].contiguous(), out_dtype=self.ydt)
+            got = self.ygs[i] if self.mode == "peer" else self.ygs[i].permute(1, 0, 2).reshape(self.M, n)
+            ok = ok and bool(torch.equal(got[rows], ref))
+        return "gathered [M,N] of both projections bit-equal to the unsharded kernel on %d sampled rows: %s" % (
+            rows.numel(), "yes" if ok else "NO")
 
     def e2e_step(self, it):
-        """Pinned host x -> device -> quantise + GEMM -> pinned host y, both projections.  The copies in
-        and out run on their own streams, so the 71 MB result of the first projection leaves while the
-        71 MB input of the second arrives (PCIe is full duplex); every buffer is single and guarded by
-        events, and the step ends only when its last result is on the host."""
+        """Pinned host x -> device -> quantise + GEMM -> pinned host y, both projections.  Single GPU: the
+        copies in and out run on their own streams, so the result of the first projection leaves while the
+        input of the second arrives (PCIe is full duplex); every buffer is single and guarded by events, and
+        the step ends only when its last result is on the host.  Sharded: both inputs arrive, the sharded
+        step runs, both gathered results leave."""
         torch = self.torch
         cur = torch.cuda.current_stream()
+        if self.world > 1:
+            for i in range(2):
+                self.xst[i].copy_(self.xh[i], non_blocking=True)
+            self.step(self.xst)
+            off = 0
+            for i in range(2):
+                out = self.ygs[i]
+                self.y_host[off:off + out.numel()].copy_(out.view(-1), non_blocking=True)
+                off = 0                                          # the host buffer holds one result at a time
+            return
         if self.e2e_streams is None:
             self.e2e_streams = (torch.cuda.Stream(), torch.cuda.Stream())
             self.e2e_consumed = [None, None]                 # x staging buffer i read by its projection
@@ -282,7 +356,7 @@ class PrefillGemm(Workload):
             computed.record(cur)
             self.e2e_consumed[i] = computed
             s_out.wait_event(computed)
-            out = self.ygs[i] if self.world > 1 else self.ys[i]
+            out = self.ys[i]
             with torch.cuda.stream(s_out):
                 self.y_host[:out.numel()].copy_(out.view(-1), non_blocking=True)
                 left = torch.cuda.Event()
@@ -319,8 +393,8 @@ class DecodeGemv(Workload):
     N, K, M, LAYERS = 8640, 3200, 1, 64
     BYTES_PER_CALL = 8640 * 3200 // 4 + 3200 * 4 + 8640 * 4    # packed W + x fp32 + y fp32
 
-    def __init__(self, torch, ops, rank, world, streams=1, **_):
-        self.torch, self.ops, self.rank, self.world = torch, ops, rank, world
+    def __init__(self, torch, ops, rank, world, streams=1, comm=None, **_):
+        self.torch, self.ops, self.rank, self.world, self.comm = torch, ops, rank, world, comm
         self.streams = max(1, streams) if world == 1 else 1
         self.side = [torch.cuda.Stream() for _ in range(self.streams)] if self.streams > 1 else []
         gen = torch.Generator(device="cuda")
@@ -427,8 +501,8 @@ class W4A16(Workload):
     N, K, GS = 11008, 4096, 128
     dtype, int8 = "bf16 x uint4 -> fp32", False
 
-    def __init__(self, torch, ops, rank, world, M=1, **_):
-        self.torch, self.ops, self.rank, self.world, self.M = torch, ops, rank, world, M
+    def __init__(self, torch, ops, rank, world, M=1, comm=None, **_):
+        self.torch, self.ops, self.rank, self.world, self.M, self.comm = torch, ops, rank, world, M, comm
         self.key = "w4a16_m%d" % M
         self.name = "w4a16_m%d_n11008_k4096_g128" % M
         gemm = M > 16
@@ -520,13 +594,13 @@ class W4A16(Workload):
                 "sample": "%d of %d token rows, extrapolated linearly (%.2f s per call)" % (rows, M, dt)}, dt
 
 
-def make_workload(key, torch, ops, rank, world, streams=1):
+def make_workload(key, torch, ops, rank, world, streams=1, comm=None, gather="peer", out_dtype="bf16"):
     if key == "prefill_gemm":
-        return PrefillGemm(torch, ops, rank, world)
+        return PrefillGemm(torch, ops, rank, world, comm=comm, gather=gather, out_dtype=out_dtype)
     if key in DECODE_CLASSES:
-        return DECODE_CLASSES[key](torch, ops, rank, world, streams=streams)
+        return DECODE_CLASSES[key](torch, ops, rank, world, streams=streams, comm=comm)
     if key.startswith("w4a16_m"):
-        return W4A16(torch, ops, rank, world, M=int(key[7:]))
+        return W4A16(torch, ops, rank, world, M=int(key[7:]), comm=comm)
     raise SystemExit("unknown workload %s" % key)
 
 
@@ -652,6 +726,10 @@ def run_ours(args):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     from nsl_b200 import lib, ops
+    comm = None
+    if world > 1:
+        from nsl_b200 import sharding
+        comm = sharding.Comm.from_torch()          # the library's own communicator (NCCL + peer memory)
     if args.no_pdl:
         lib().nslq_set_dependent_launch(0)
     peaks = load_peaks()
@@ -663,10 +741,19 @@ def run_ours(args):
                     "higher_is_better": True, "data": "synthetic (seed 0)", "dtype": "int8 x int2 -> int32"})
         print(json.dumps(out))
         return
-    wl = make_workload(args.workload, torch, ops, rank, world, streams=args.streams)
+    wl = make_workload(args.workload, torch, ops, rank, world, streams=args.streams, comm=comm, gather=args.gather,
+                       out_dtype=args.out_dtype)
     sampler = ClockSampler(local) if rank == 0 else None
     m = measure(torch, wl, args.steps, args.warmup, use_graph, dist, sampler)
     roof = wl.roofline(peaks, m["kernel_ms"])
+    check = wl.gather_check() if hasattr(wl, "gather_check") else None
+    if world == 1:
+        par = "single GPU"
+    elif getattr(wl, "mode", "nccl") == "peer":
+        par = ("weight rows sharded x%d, x replicated; all-gather fused into the GEMM epilogue (tiles stored into every "
+               "rank's copy over NVLink), two projections on two streams, flag barriers before and after" % world)
+    else:
+        par = "weight rows sharded x%d, x replicated; ncclAllGather of the output shards called by the library" % world
     line = None
     if rank == 0:
         cpu, _ = cpu_arm(args.workload, 1, 12.0)
@@ -676,13 +763,17 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seed 0)",
             "config": {"workload": wl.name, "cuda_graph": m["graph"], "dependent_launch": not args.no_pdl,
                        "streams": getattr(wl, "streams", 1), "l2": wl.l2_note,
-                       "parallelism": ("column-sharded x%d + NCCL all-gather (the first projection's gather overlaps the second projection)" % world) if world > 1 else "single GPU"},
+                       "x_dtype": "f32", "y_dtype": getattr(wl, "out_dtype", "f32"), "parallelism": par},
             "e2e": {"value": round(m["e2e"], 3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
                     "d2h_bytes_per_step": wl.d2h},
             "gpu_launches": wl.launches_per_step * args.steps,
             "roofline": roof, "cpu_baseline": cpu, "clocks": m["clocks"],
         }
+        if check:
+            line["gather_check"] = check
     status = ops.device_status()
+    if comm is not None:
+        status = status or comm.status()
     del wl
     torch.cuda.empty_cache()
 
@@ -707,6 +798,8 @@ def run_ours(args):
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()
+        if comm is not None:
+            comm.close()
         dist.destroy_process_group()
 
 
@@ -747,6 +840,9 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=WORKLOAD_KEYS)
     ap.add_argument("--streams", type=int, default=1,
                     help="decode_gemv: issue the independent calls of a step round-robin on this many streams")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="N > 1, prefill: shards stored into every rank's copy by the GEMM epilogue, or ncclAllGather")
+    ap.add_argument("--out-dtype", default="bf16", choices=["bf16", "f32"], help="prefill: dtype of y")
     ap.add_argument("--no-graph", action="store_true", help="issue launches directly instead of replaying a CUDA graph")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels without the programmatic-dependent-launch attribute")
     ap.add_argument("--no-also", action="store_true", help="skip the secondary workloads of the default run")

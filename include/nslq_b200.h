@@ -32,6 +32,8 @@ extern "C" {
 #define NSLQ_ERR_CUDA         -3 /* a CUDA runtime call or launch failed            */
 #define NSLQ_ERR_UNSUPPORTED  -4 /* valid request with no kernel for it             */
 #define NSLQ_ERR_WORKSPACE    -5 /* workspace missing or too small                  */
+#define NSLQ_ERR_COMM         -6 /* NCCL missing or a collective failed             */
+#define NSLQ_ERR_TIMEOUT      -7 /* a bounded wait on a collective reached its deadline */
 
 /* ---- dtype tags: NSL's NslTensor.dtype wire tags -------------------------
  * crates/nsl-runtime/src/tensor/mod.rs:246-256 */
@@ -310,6 +312,111 @@ int nslq_awq_quantize_kn(const void *w, int w_dtype, int64_t K, int64_t N, int64
  * NSLQ_ERR_SHAPE, as in the reference.
  */
 int nslq_shard_rows(int64_t N, int world, int rank, int64_t *row0, int64_t *rows);
+
+/*
+ * The communicator of a column-sharded run: one process per GPU on one node.  Follows NSL's
+ * NCCL backend (crates/nsl-runtime/src/tensor_parallel/collective.rs:854-1130): rank 0 mints
+ * a unique id (nslq_shard_unique_id, NSLQ_UNIQUE_ID_BYTES bytes of host memory), the host
+ * hands it to every rank by its own means (NSL: a shared-memory broadcast), and every rank
+ * calls nslq_shard_init with the device it will use current.  The join runs under a watchdog:
+ * if the clique is not complete after NSL_NCCL_TIMEOUT_SECS (default 300) the process is
+ * aborted with a message, as the reference does, because a peer that died before joining would
+ * otherwise leave the others waiting for ever.  NCCL is loaded with dlopen at the first use (a
+ * NCCL already in the process is reused), so the library itself loads without it; world == 1
+ * needs no NCCL and no id.  At most NSLQ_MAX_RANKS ranks.
+ */
+#define NSLQ_MAX_RANKS        8
+#define NSLQ_UNIQUE_ID_BYTES  128
+typedef struct nslq_comm nslq_comm_t;
+int  nslq_shard_unique_id(void *id_out);
+int  nslq_shard_init(const void *unique_id, int rank, int world, nslq_comm_t **out);
+void nslq_shard_destroy(nslq_comm_t *c);
+int  nslq_shard_info(const nslq_comm_t *c, int *rank, int *world);
+
+/*
+ * The one exchange step of the column-parallel layout, by NCCL: all-gather of the [M, N_local]
+ * output shards (ncclAllGather on `stream`; crates/nsl-runtime/src/tensor_parallel/
+ * collective.rs:1061-1087).  `gathered` receives the shards rank after rank, [world][M][N_local]
+ * -- for M == 1 that already is y[N].  When y_full is not NULL a second small kernel lays the
+ * result out as [M][world*N_local] there (y_full must not alias gathered unless M == 1).
+ * dtype: any NSLQ_DTYPE_* tag (bytes are moved, not interpreted).  The call only enqueues;
+ * nslq_shard_wait is the bounded way to wait for it.
+ */
+int nslq_allgather_cols(nslq_comm_t *c, const void *y_local, int dtype, int64_t M, int64_t N_local,
+                        void *gathered, void *y_full, void *stream);
+
+/*
+ * Waits until `stream` has drained, polling instead of blocking: an asynchronous NCCL error or
+ * the deadline (timeout_ms; <= 0 = NSL_NCCL_TIMEOUT_SECS) ends the wait with NSLQ_ERR_COMM /
+ * NSLQ_ERR_TIMEOUT after the communicator has been aborted (it is unusable afterwards; destroy
+ * it).  The reference aborts the process at this point (collective.rs:975-1010); a library
+ * leaves that decision to its host.  Not for use during stream capture.
+ */
+int nslq_shard_wait(nslq_comm_t *c, void *stream, int64_t timeout_ms);
+
+/*
+ * Peer memory.  nslq_symm_alloc is collective (every rank calls it, same size, same order): each
+ * rank allocates `bytes` of device memory, the ranks exchange CUDA IPC handles over the
+ * communicator and map one another's buffers; *local_ptr is this rank's own buffer, zero-filled.
+ * The library's kernels reach the peers' copies with plain loads and stores only.  No counterpart
+ * in NSL (its NCCL backend has no peer-memory path).
+ */
+int nslq_symm_alloc(nslq_comm_t *c, int64_t bytes, void **local_ptr);
+int nslq_symm_free(nslq_comm_t *c, void *local_ptr);
+
+/*
+ * Flag barrier over peer memory, one small kernel on `stream`: every rank announces that the
+ * work in front of the barrier on its stream is complete (its stores into peers' buffers
+ * included) and waits until every other rank has announced the same.  The wait is bounded
+ * (2 s): a rank that never arrives makes the kernel record 0x501 (nslq_shard_status) and
+ * return; the context stays usable.  Graph-capturable (the epoch lives in device memory).
+ */
+int nslq_peer_barrier(nslq_comm_t *c, void *stream);
+int nslq_shard_status(nslq_comm_t *c, int *status);
+
+/*
+ * All-gather by peer stores: this rank's [M, N_local] block goes to columns
+ * [rank*N_local, (rank+1)*N_local) of the [M][world*N_local] result y_full in EVERY rank's copy.
+ * y_full must lie inside a buffer of nslq_symm_alloc, at the same offset on every rank; rows of
+ * the block must be multiples of 16 bytes.  Completion on the peers is what nslq_peer_barrier
+ * announces.
+ */
+int nslq_peer_allgather_cols(nslq_comm_t *c, const void *y_local, int dtype, int64_t M, int64_t N_local,
+                             void *y_full, void *stream);
+
+/*
+ * BitLinear on this rank's row shard of W with the all-gather fused in: y_full is the whole
+ * [M][world*N_shard] result, inside a buffer of nslq_symm_alloc.  For M > 16 the tensor-core
+ * GEMM's epilogue stores each finished tile into this rank's copy and into every peer's copy
+ * (the transfer overlaps the remaining tiles); for M <= 16 the decode kernel writes the local
+ * block and one kernel pushes it.  x (and so its quantisation) is replicated on every rank,
+ * hence the accumulators equal the unsharded ones bit for bit.  The caller brackets a group of
+ * these calls with nslq_peer_barrier: one before the first store into a buffer the peers may
+ * still be reading, one after the last call, before anyone reads y_full.
+ * bias: this rank's N_shard entries or NULL.  Workspace as nslq_bitlinear_forward, sized by
+ * nslq_bitlinear_gathered_workspace_bytes(M, K, N_shard).  Requires K % 64 == 0.
+ * The _quantized form takes activations already quantised by nslq_act_quant_i8; its scratch
+ * (M <= 16 only) is M*N_shard*4 bytes rounded up to 256.
+ */
+int64_t nslq_bitlinear_gathered_workspace_bytes(int64_t M, int64_t K, int64_t N_shard);
+/*
+ * The kernel capability the gathered calls are built on, usable without a communicator: the
+ * [M, N] result is written as columns [col0, col0+N) of rows of `ldy` elements into n_copies
+ * (1..8) arrays at once -- y_copies is a HOST array of device pointers to the [M][ldy] arrays.
+ * E.g. q, k and v projections writing the column blocks of one fused [M, 3*hidden] buffer, or a
+ * test standing in for two ranks on one GPU.  y_scratch as above (M <= 16 only).
+ */
+int nslq_bitlinear_forward_quantized_cols(const nslq_bitlinear_t *w, const int8_t *q_perm, const float *scale,
+                                          const int32_t *rowsum, int64_t M, void *const *y_copies, int n_copies,
+                                          int64_t ldy, int64_t col0, int y_dtype, const float *bias,
+                                          void *y_scratch, int64_t y_scratch_bytes, void *stream);
+int nslq_bitlinear_forward_gathered(nslq_comm_t *c, const nslq_bitlinear_t *w_shard, const void *x, int x_dtype,
+                                    int64_t M, void *y_full, int y_dtype, const float *bias,
+                                    void *workspace, int64_t workspace_bytes, void *stream);
+int nslq_bitlinear_forward_quantized_gathered(nslq_comm_t *c, const nslq_bitlinear_t *w_shard, const int8_t *q_perm,
+                                              const float *scale, const int32_t *rowsum, int64_t M,
+                                              void *y_full, int y_dtype, const float *bias,
+                                              void *y_scratch, int64_t y_scratch_bytes, void *stream);
 
 #ifdef __cplusplus
 }

@@ -6,8 +6,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# NSLQ_LIB points at another build of the same library (kernel experiments); default: the in-tree build
-LIB_PATH = os.environ.get("NSLQ_LIB") or os.path.join(_HERE, "libnslq_b200.so")
+LIB_PATH = os.path.join(_HERE, "libnslq_b200.so")
 
 vp, i64, i32, f32, f64 = C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_double
 
@@ -36,6 +35,21 @@ SIGNATURES = {
     "nslq_int4_quantize_nk": (i32, [vp, i32, i64, i64, i64, vp, vp, vp, vp]),
     "nslq_awq_quantize_kn": (i32, [vp, i32, i64, i64, i64, vp, vp, vp, vp]),
     "nslq_shard_rows": (i32, [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]),
+    "nslq_shard_unique_id": (i32, [vp]),
+    "nslq_shard_init": (i32, [vp, i32, i32, C.POINTER(vp)]),
+    "nslq_shard_destroy": (None, [vp]),
+    "nslq_shard_info": (i32, [vp, C.POINTER(i32), C.POINTER(i32)]),
+    "nslq_allgather_cols": (i32, [vp, vp, i32, i64, i64, vp, vp, vp]),
+    "nslq_shard_wait": (i32, [vp, vp, i64]),
+    "nslq_symm_alloc": (i32, [vp, i64, C.POINTER(vp)]),
+    "nslq_symm_free": (i32, [vp, vp]),
+    "nslq_peer_barrier": (i32, [vp, vp]),
+    "nslq_shard_status": (i32, [vp, C.POINTER(i32)]),
+    "nslq_peer_allgather_cols": (i32, [vp, vp, i32, i64, i64, vp, vp]),
+    "nslq_bitlinear_gathered_workspace_bytes": (i64, [i64, i64, i64]),
+    "nslq_bitlinear_forward_quantized_cols": (i32, [vp, vp, vp, vp, i64, C.POINTER(vp), i32, i64, i64, i32, vp, vp, i64, vp]),
+    "nslq_bitlinear_forward_gathered": (i32, [vp, vp, vp, i32, i64, vp, i32, vp, vp, i64, vp]),
+    "nslq_bitlinear_forward_quantized_gathered": (i32, [vp, vp, vp, vp, vp, i64, vp, i32, vp, vp, i64, vp]),
 }
 
 # Entry points with NSL's own calling convention (include/nsl_shims.h): i64 handles in, i64 out.

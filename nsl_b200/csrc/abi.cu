@@ -54,7 +54,7 @@ int ternary_decode_fused_dispatch(const uint8_t *, const void *, int, int, int64
 int ternary_decode_status(int *);
 bool ternary_gemm_supported(const void *, const void *, int64_t, int64_t, int64_t);
 int ternary_gemm_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int64_t, int64_t,
-                          int64_t, float, void *, int, int32_t *, const float *, const float *, cudaStream_t);
+                          int64_t, float, void *, int, int32_t *, const float *, const float *, const OutSpec *, cudaStream_t);
 int ternary_gemm_status(int *);
 int w4a16_gemm_status(int *);
 bool w4a16_gemv_supported(const void *, const void *, int, int64_t, int64_t);
@@ -255,7 +255,7 @@ int nslq_bitlinear_forward_quantized(const nslq_bitlinear_t *w, const int8_t *q_
     cudaStream_t st = (cudaStream_t)stream;
     if (M > 16 && ternary_gemm_supported(w->packed, q_perm, M, w->N, w->K))
         return ternary_gemm_dispatch(w->packed, q_perm, scale, rowsum, M, w->N, w->K, w->weight_scale, y, y_dtype,
-                                     acc_out, bias, residual, st);
+                                     acc_out, bias, residual, nullptr, st);
     if (!ternary_gemv_supported(w->packed, q_perm, w->K))
         return fail(NSLQ_ERR_UNSUPPORTED, "nslq_bitlinear_forward_quantized: needs K %% 64 == 0 and 16-byte aligned buffers (K=%lld)",
                     (long long)w->K);

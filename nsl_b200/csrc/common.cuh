@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/nslq_b200.h"
 
 // The object behind nslq_bitlinear_t: a borrowed packed weight and its shape.
@@ -16,12 +18,56 @@ struct nslq_bitlinear {
 
 namespace nslq {
 
+// Where a linear's output goes when it is not a plain [M][N] array: the row stride of y
+// (a column block of a wider [M][ldy] result) and, in a column-sharded run, the address of
+// the same block in the other ranks' copies of that result, which receive the same stores.
+struct OutSpec {
+    int64_t ldy;
+    int npeer;
+    void *peer[NSLQ_MAX_RANKS - 1];
+};
+
 // Records the calling thread's last error text and returns `code`.
 int fail(int code, const char *fmt, ...);
 // Checks cudaGetLastError() after a launch.
 int check_launch(const char *what);
 
 static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// One-time CUDA state is per device (a function attribute set on device 0 says nothing about
+// device 1), so launchers keep it in tables indexed by the current device.
+constexpr int kMaxDevices = 64;
+static inline int device_index()
+{
+    int d = 0;
+    cudaGetDevice(&d);
+    return (d >= 0 && d < kMaxDevices) ? d : 0;
+}
+// Makes sure `kernel` may use `smem` bytes of dynamic shared memory on the current device.
+// `table` is the launcher's own static table (zero-initialised); safe from several host threads.
+template <typename K>
+static inline cudaError_t reserve_smem(K kernel, std::atomic<size_t> (&table)[kMaxDevices], size_t smem)
+{
+    std::atomic<size_t> &slot = table[device_index()];
+    if (smem <= 48 * 1024 || smem <= slot.load(std::memory_order_acquire)) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) {
+        size_t seen = slot.load(std::memory_order_relaxed);
+        while (seen < smem && !slot.compare_exchange_weak(seen, smem, std::memory_order_release)) {}
+    }
+    return e;
+}
+static inline int sm_count_current()
+{
+    static std::atomic<int> n[kMaxDevices];
+    const int d = device_index();
+    int v = n[d].load(std::memory_order_relaxed);
+    if (!v) {
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, d);
+        n[d].store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
 
 template <typename T> struct Elem;
 template <> struct Elem<float> {

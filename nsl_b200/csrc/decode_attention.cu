@@ -310,17 +310,14 @@ int decode_attention_dispatch(const void *q, const void *k_new, const void *v_ne
     const int warps = threads / 32;
     const size_t smem = (size_t)(max_ctx + DA_UNROLL + 2 * D + warps * D) * sizeof(float);
     if (smem > 200 * 1024) return fail(NSLQ_ERR_UNSUPPORTED, "nslq_decode_attention: max_ctx=%lld does not fit shared memory", (long long)max_ctx);
-    static size_t reserved = 48 * 1024;
-    if (smem > reserved) {
-        if (cudaFuncSetAttribute(decode_attention_kernel<256, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-            cudaFuncSetAttribute(decode_attention_kernel<256, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-            cudaFuncSetAttribute(decode_attention_kernel<256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-            cudaFuncSetAttribute(decode_attention_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-            cudaFuncSetAttribute(decode_attention_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return fail(NSLQ_ERR_CUDA, "decode_attention_kernel: cannot reserve %zu bytes of shared memory: %s", smem,
-                        cudaGetErrorString(cudaGetLastError()));
-        reserved = smem;
-    }
+    static std::atomic<size_t> r8[kMaxDevices], r4[kMaxDevices], r2[kMaxDevices], r1[kMaxDevices], r0[kMaxDevices];
+    if (reserve_smem(decode_attention_kernel<256, 8>, r8, smem) != cudaSuccess ||
+        reserve_smem(decode_attention_kernel<256, 4>, r4, smem) != cudaSuccess ||
+        reserve_smem(decode_attention_kernel<256, 2>, r2, smem) != cudaSuccess ||
+        reserve_smem(decode_attention_kernel<256, 1>, r1, smem) != cudaSuccess ||
+        reserve_smem(decode_attention_kernel<128, 1>, r0, smem) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "decode_attention_kernel: cannot reserve %zu bytes of shared memory: %s", smem,
+                    cudaGetErrorString(cudaGetLastError()));
     if (q_bs % 4 != 0 || k_bs % 4 != 0 || v_bs % 4 != 0 || q_bs < H * D || k_bs < Hkv * D || v_bs < Hkv * D)
         return fail(NSLQ_ERR_SHAPE, "nslq_decode_attention: batch strides must be multiples of 4 elements and cover a sequence's rows");
     AttnParams p{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_new, (const __nv_bfloat16 *)v_new, q_bs, k_bs, v_bs,

@@ -35,8 +35,15 @@ static __device__ __forceinline__ unsigned long long globaltimer_ns()
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait: true when the phase completed, false after WAIT_NS (status word set).
-static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int site)
+// Bounded wait: true when the phase completed, false once it has given up (status word set).
+// It gives up only when BOTH two seconds of wall clock have passed AND the thread has polled
+// MIN_POLLS times itself: %globaltimer keeps running while the context is switched out for
+// another tenant of the GPU, the poll count does not, so a pre-empted kernel is not mistaken for
+// a stuck one.  `abort` (optional, shared memory, zeroed by the kernel) is a CTA-wide flag: the
+// role whose wait expires raises it and every other role's wait leaves at its next check, so
+// the whole CTA reaches its teardown together instead of each role serving its own two seconds.
+constexpr uint32_t MIN_POLLS = 1u << 20;
+static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int site, volatile int *abort = nullptr)
 {
     long long t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
@@ -48,11 +55,16 @@ static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, 
             : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
         if ((spin & 63u) == 63u) {
+            if (abort && *abort) return false;
             // signed difference: should %globaltimer ever step backwards between two reads, an
             // unsigned difference would read as an instant timeout
             const long long now = (long long)globaltimer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > (long long)WAIT_NS) { atomicCAS(&g_wait_status, 0, site); return false; }
+            else if (now - t0 > (long long)WAIT_NS && spin >= MIN_POLLS) {
+                atomicCAS(&g_wait_status, 0, site);
+                if (abort) *abort = 1;
+                return false;
+            }
         }
     }
 }
@@ -72,9 +84,9 @@ static __device__ __forceinline__ bool elect_one()
 // the warp converged, so it is re-formed here and the outcome made uniform.  (A version of
 // mbar_wait that slept between polls let the lanes drift apart and, without this, ended in rare
 // launch failures in millisecond-long launches.)
-static __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int site)
+static __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int site, volatile int *abort = nullptr)
 {
-    const bool ok = mbar_wait(bar, parity, site);
+    const bool ok = mbar_wait(bar, parity, site, abort);
     return __all_sync(0xffffffffu, ok) != 0;
 }
 static __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tmap, int x, int y, uint32_t bar)
@@ -171,16 +183,7 @@ static inline EncodeTiledFn encode_tiled()
     return fn;
 }
 
-static inline int sm_count()
-{
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    }
-    return n;
-}
+static inline int sm_count() { return sm_count_current(); }
 
 static inline int make_map_2d(CUtensorMap *m, const void *ptr, uint64_t inner_bytes, uint64_t rows, uint32_t box_inner,
                        uint32_t box_rows, CUtensorMapSwizzle swz)

@@ -456,13 +456,10 @@ static int launch_decode(dec::Params &p, cudaStream_t st)
     int smem = 0, grid = 0;
     if (!dec_plan(p, &smem, &grid))
         return fail(NSLQ_ERR_UNSUPPORTED, "ternary_decode_kernel: K=%lld does not fit shared memory", (long long)p.K);
-    static int reserved = 0;
-    if (smem > reserved) {
-        if (cudaFuncSetAttribute(dec::ternary_decode_kernel<XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-            return fail(NSLQ_ERR_CUDA, "ternary_decode_kernel: cannot reserve %d bytes of shared memory: %s", smem,
-                        cudaGetErrorString(cudaGetLastError()));
-        reserved = smem;
-    }
+    static std::atomic<size_t> reserved[kMaxDevices];
+    if (reserve_smem(dec::ternary_decode_kernel<XT>, reserved, (size_t)smem) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "ternary_decode_kernel: cannot reserve %d bytes of shared memory: %s", smem,
+                    cudaGetErrorString(cudaGetLastError()));
     CUtensorMap tmap_w;
     int rc = sm100::make_map_2d(&tmap_w, p.w, (uint64_t)(p.K / 4), (uint64_t)p.N, dec::PK_ROW, dec::BW, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;

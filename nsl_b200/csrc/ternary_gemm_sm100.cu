@@ -96,6 +96,9 @@ struct Params {
     int y_dtype;
     float weight_scale;
     int tiles_t, tiles_w;    // token tiles, weight-row tiles
+    int64_t ldy;             // elements between consecutive token rows of y (N when y is [M][N])
+    int npeer;               // copies of y in other GPUs' memory that receive the same stores
+    void *y_peer[NSLQ_MAX_RANKS - 1];
 };
 
 template <typename T> struct OutStore;
@@ -138,8 +141,11 @@ static __device__ __forceinline__ void store_group(const Params &p, const uint32
 #pragma unroll
         for (int j = 0; j < EG; ++j) v[j] = __fadd_rn(v[j], bias);
     }
-    if (!n_ok) return;
+    // no early return for lanes past N: the caller's next instruction is a warp-wide
+    // tcgen05.ld, which every lane must reach together
+    if (n_ok) {
     const int64_t o = mt * p.N + n;
+    const int64_t oy = mt * p.ldy + n;
     const int64_t left = p.M - mt;
     if (left >= EG) {
         if (p.acc_out) {
@@ -154,7 +160,14 @@ static __device__ __forceinline__ void store_group(const Params &p, const uint32
             for (int j = 0; j < EG; ++j) v[j] = __fadd_rn(v[j], res[j]);
         }
 #pragma unroll
-        for (int j = 0; j < EG; ++j) OutStore<T>::put(p.y, o + j * p.N, v[j]);
+        for (int j = 0; j < EG; ++j) OutStore<T>::put(p.y, oy + j * p.ldy, v[j]);
+        // column-sharded run: the same tile goes straight into every other rank's copy of the
+        // gathered output (plain stores over NVLink; the all-gather rides in the epilogue)
+        for (int pi = 0; pi < p.npeer; ++pi) {
+            void *yp = p.y_peer[pi];
+#pragma unroll
+            for (int j = 0; j < EG; ++j) OutStore<T>::put(yp, oy + j * p.ldy, v[j]);
+        }
     } else {
 #pragma unroll
         for (int j = 0; j < EG; ++j) {
@@ -163,9 +176,11 @@ static __device__ __forceinline__ void store_group(const Params &p, const uint32
                 if (p.acc_out) p.acc_out[oj] = acc[j];
                 float vj = v[j];
                 if (p.residual) vj = __fadd_rn(vj, p.residual[oj]);
-                OutStore<T>::put(p.y, oj, vj);
+                OutStore<T>::put(p.y, oy + j * p.ldy, vj);
+                for (int pi = 0; pi < p.npeer; ++pi) OutStore<T>::put(p.y_peer[pi], oy + j * p.ldy, vj);
             }
         }
+    }
     }
 }
 
@@ -189,28 +204,33 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     // waits for and the ring has 8 > TS entries, so the phase it tests cannot have been overtaken.
     constexpr int ND = 8;
     static_assert(C::TS < ND && C::AS < ND, "done ring too short");
-    constexpr int NBAR = 2 * C::TS + C::AS + ND + 4;
-    static_assert(NBAR * 8 + 8 <= C::BAR_BYTES, "barrier area");
+    constexpr int NBAR = 2 * C::TS + C::AS + ND + 5;
+    static_assert(NBAR * 8 + 16 <= C::BAR_BYTES, "barrier area");
     auto raw_bar = [&](int t) { return bars + 8u * t; };
     auto pfree_bar = [&](int t) { return bars + 8u * (C::TS + t); };
     auto afull_bar = [&](int a) { return bars + 8u * (2 * C::TS + a); };
     auto done_bar = [&](uint32_t i) { return bars + 8u * (2 * C::TS + C::AS + (i & (ND - 1))); };
     auto accf_bar = [&](int b) { return bars + 8u * (2 * C::TS + C::AS + ND + b); };
     auto acce_bar = [&](int b) { return bars + 8u * (2 * C::TS + C::AS + ND + 2 + b); };
+    const uint32_t drain_bar = bars + 8u * (2 * C::TS + C::AS + ND + 4);   // used only when a wait gave up
     // parity of the phase of done[i mod 8] that step i completes
     auto done_par = [&](uint32_t i) { return (i / ND) & 1u; };
     const uint32_t slot = bars + 8u * NBAR;
     volatile uint32_t *slot_ptr = reinterpret_cast<volatile uint32_t *>(base_ptr + C::TS * C::T_BYTES + C::SCALE_BYTES + 8 * NBAR);
+    // CTA-wide "a wait gave up" flag: raised by the role whose wait expired, seen by every other wait
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + C::TS * C::T_BYTES + C::SCALE_BYTES + 8 * NBAR + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nkb = (int)((p.K + BK * C::KS - 1) / (BK * C::KS));   // pipeline steps per tile
     const int ntiles = p.tiles_t * p.tiles_w;
 
     if (threadIdx.x == 0) {
+        *abort_flag = 0;
         for (int t = 0; t < C::TS; ++t) { mbar_init(raw_bar(t), 1); mbar_init(pfree_bar(t), 4); }
         for (int a = 0; a < C::AS; ++a) mbar_init(afull_bar(a), 4);
         for (int i = 0; i < ND; ++i) mbar_init(done_bar(i), 1);
         for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 256); }
+        mbar_init(drain_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -238,8 +258,8 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 const int m0 = (tile % p.tiles_t) * BT, n0 = (tile / p.tiles_t) * BW;
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     if (it >= (uint32_t)C::TS) {       // the stage's previous user: step it - TS
-                        if (!(ok = mbar_wait(done_bar(it - C::TS), done_par(it - C::TS), 0x101))) break;
-                        if (!(ok = mbar_wait(pfree_bar(s), ph ^ 1u, 0x102))) break;
+                        if (!(ok = mbar_wait(done_bar(it - C::TS), done_par(it - C::TS), 0x101, abort_flag))) break;
+                        if (!(ok = mbar_wait(pfree_bar(s), ph ^ 1u, 0x102, abort_flag))) break;
                     }
                     const uint32_t st = base + s * C::T_BYTES;
                     mbar_arrive_expect_tx(raw_bar(s), C::T_BYTES);
@@ -249,6 +269,14 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     tma_load_2d(st + C::X_BYTES, &tmap_w, kb * C::PK_ROW, n0, raw_bar(s));
                     if (++s == C::TS) { s = 0; ph ^= 1u; }
                 }
+            }
+            if (*abort_flag) {
+                // A wait gave up somewhere in this CTA.  Copies this thread issued may still be on
+                // their way into shared memory; the CTA must not end under them.  Wait (bounded, and
+                // without looking at the flag) for the last TS stages it armed.
+                const uint32_t first = it > (uint32_t)C::TS ? it - C::TS : 0u;
+                for (uint32_t j = first; j < it; ++j)
+                    mbar_wait(raw_bar((int)(j % C::TS)), (j / C::TS) & 1u, 0x103);
             }
         }
     } else if (warp == 1) {
@@ -261,11 +289,11 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         bool ok = true;
         for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
             const uint32_t buf = t & 1u, cph = (t >> 1) & 1u;
-            if (!(ok = mbar_wait_warp(acce_bar(buf), cph ^ 1u, 0x201))) break;
+            if (!(ok = mbar_wait_warp(acce_bar(buf), cph ^ 1u, 0x201, abort_flag))) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + C::acc_col(buf);
             for (int kb = 0; kb < nkb; ++kb, ++it) {
-                if (!(ok = mbar_wait_warp(afull_bar(a), aph, 0x203))) break;    // codes stored (and the copy stage landed)
+                if (!(ok = mbar_wait_warp(afull_bar(a), aph, 0x203, abort_flag))) break;    // codes stored (and the copy stage landed)
                 tc_fence_after();
                 if (leader) {
                     const uint32_t a_tmem = tmem_base + C::a_col(a);
@@ -284,6 +312,13 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             }
             if (ok && leader) umma_commit(accf_bar(buf));
         }
+        if (__any_sync(0xffffffffu, *abort_flag != 0)) {
+            // Leaving early: tensor memory is freed in the teardown, so every MMA issued so far must
+            // have retired first.  One more commit tracks them all; wait for it (bounded).
+            if (leader) umma_commit(drain_bar);
+            __syncwarp();
+            mbar_wait_warp(drain_bar, 0, 0x204);
+        }
     } else if (warp >= 8 && warp < 16) {
         // ---------------- unpack warps (packed row -> u8 codes in this thread's TMEM lane)
         const int q = warp & 3;                      // TMEM lane quadrant of this warp
@@ -294,12 +329,12 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         int s = group % C::TS;                       // ring positions of iteration `it`, stepped by two
         uint32_t a = group % C::AS, sph = 0, aph = 0;
         for (int it = group; it < total_it && ok; it += 2) {
-            if (!(ok = mbar_wait_warp(raw_bar(s), sph, 0x301))) break;                            // packed tile landed
+            if (!(ok = mbar_wait_warp(raw_bar(s), sph, 0x301, abort_flag))) break;                            // packed tile landed
             const uint4 *pk = reinterpret_cast<const uint4 *>(base_ptr + s * C::T_BYTES + C::X_BYTES + row * C::PK_ROW);
             uint4 pv[2 * C::KS];
 #pragma unroll
             for (int i = 0; i < 2 * C::KS; ++i) pv[i] = pk[i];
-            if (it >= C::AS && !(ok = mbar_wait_warp(done_bar(it - C::AS), done_par(it - C::AS), 0x302))) break;   // operand stage reusable
+            if (it >= C::AS && !(ok = mbar_wait_warp(done_bar(it - C::AS), done_par(it - C::AS), 0x302, abort_flag))) break;   // operand stage reusable
             tc_fence_after();
 #pragma unroll
             for (int h = 0; h < C::KS; ++h) {                                                // one k-block: 32 bytes -> 32 columns
@@ -344,12 +379,13 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 rs[i] = m < p.M ? p.rowsum[m] : 0;
             }
             __syncwarp();
-            if (!(ok = mbar_wait_warp(accf_bar(buf), cph, 0x401))) break;
+            if (!(ok = mbar_wait_warp(accf_bar(buf), cph, 0x401, abort_flag))) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + C::acc_col(buf) + half * C::HALF_T;
 #pragma unroll 1
             for (int g = 0; g < C::HALF_T / EG; ++g) {
                 uint32_t r[EG];
+                __syncwarp();                         // tcgen05.ld is warp-wide: re-form the warp after the guarded stores
                 tmem_ld16(taddr + g * EG, r);
                 if (g == C::HALF_T / EG - 1) {       // this thread's last read of the accumulator: hand it back
                     tc_fence_before();
@@ -387,13 +423,10 @@ template <int BT>
 static int launch_gemm(const void *q_perm, gemm::Params &p, cudaStream_t st)
 {
     using C = gemm::Cfg<BT>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(gemm::ternary_gemm_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
-            return fail(NSLQ_ERR_CUDA, "ternary_gemm_kernel: cannot reserve %d bytes of shared memory: %s", C::SMEM,
-                        cudaGetErrorString(cudaGetLastError()));
-        attr_set = true;
-    }
+    static std::atomic<size_t> reserved[kMaxDevices];
+    if (reserve_smem(gemm::ternary_gemm_kernel<BT>, reserved, (size_t)C::SMEM) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "ternary_gemm_kernel: cannot reserve %d bytes of shared memory: %s", C::SMEM,
+                    cudaGetErrorString(cudaGetLastError()));
     CUtensorMap tmap_x, tmap_w;
     int rc = sm100::make_map_2d(&tmap_x, q_perm, (uint64_t)p.K, (uint64_t)p.M, gemm::BK, BT, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
@@ -410,9 +443,15 @@ static int launch_gemm(const void *q_perm, gemm::Params &p, cudaStream_t st)
 
 static int gemm_one_launch(const uint8_t *w, const int8_t *q_perm, const float *scale, const int32_t *rowsum, int64_t M,
                            int64_t N, int64_t K, float weight_scale, void *y, int y_dtype, int32_t *acc_out,
-                           const float *bias, const float *residual, cudaStream_t st)
+                           const float *bias, const float *residual, const OutSpec *os, int64_t row_off, cudaStream_t st)
 {
-    gemm::Params p{w, scale, rowsum, y, acc_out, bias, residual, M, N, K, y_dtype, weight_scale, 0, 0};
+    gemm::Params p{w, scale, rowsum, y, acc_out, bias, residual, M, N, K, y_dtype, weight_scale, 0, 0, N, 0, {}};
+    if (os) {
+        const int es = y_dtype == NSLQ_DTYPE_F32 ? 4 : 2;
+        p.ldy = os->ldy;
+        p.npeer = os->npeer;
+        for (int i = 0; i < os->npeer; ++i) p.y_peer[i] = (char *)os->peer[i] + row_off * os->ldy * es;
+    }
     // Token-tile width: the one that wastes fewer SM-rounds on this shape (ties go to the wider
     // tile, which moves fewer shared-memory bytes per MAC).
     const int sms = sm100::sm_count();
@@ -439,14 +478,15 @@ constexpr int64_t GEMM_MAX_ROWS = 4096;
 
 int ternary_gemm_dispatch(const uint8_t *w, const int8_t *q_perm, const float *scale, const int32_t *rowsum, int64_t M,
                           int64_t N, int64_t K, float weight_scale, void *y, int y_dtype, int32_t *acc_out,
-                          const float *bias, const float *residual, cudaStream_t st)
+                          const float *bias, const float *residual, const OutSpec *os, cudaStream_t st)
 {
     const int es = y_dtype == NSLQ_DTYPE_F32 ? 4 : 2;
+    const int64_t ldy = os ? os->ldy : N;
     for (int64_t m0 = 0; m0 < M; m0 += GEMM_MAX_ROWS) {
         const int64_t mc = (M - m0) < GEMM_MAX_ROWS ? (M - m0) : GEMM_MAX_ROWS;
         int rc = gemm_one_launch(w, q_perm + m0 * K, scale + m0, rowsum + m0, mc, N, K, weight_scale,
-                                 (char *)y + m0 * N * es, y_dtype, acc_out ? acc_out + m0 * N : nullptr, bias,
-                                 residual ? residual + m0 * N : nullptr, st);
+                                 (char *)y + m0 * ldy * es, y_dtype, acc_out ? acc_out + m0 * N : nullptr, bias,
+                                 residual ? residual + m0 * N : nullptr, os, m0, st);
         if (rc) return rc;
     }
     return NSLQ_OK;

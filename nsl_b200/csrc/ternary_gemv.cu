@@ -358,12 +358,9 @@ static int launch_fused(const FusedParams &p, cudaStream_t st)
 {
     constexpr int NW = KW * TPC;
     const size_t smem = (((size_t)p.M * p.K + 15) & ~(size_t)15) + (size_t)NW * 32 * 4 * 4 + (size_t)NW * FUSED_MAX_M * 8 + FUSED_MAX_M * 8 + 64;
-    static size_t reserved = 0;
-    if (smem > 48 * 1024 && smem > reserved) {
-        if (cudaFuncSetAttribute(ternary_gemv_fused_kernel<T, KW, TPC, UNROLL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return fail(NSLQ_ERR_CUDA, "ternary_gemv_fused_kernel: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(cudaGetLastError()));
-        reserved = smem;
-    }
+    static std::atomic<size_t> reserved[kMaxDevices];
+    if (reserve_smem(ternary_gemv_fused_kernel<T, KW, TPC, UNROLL>, reserved, smem) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "ternary_gemv_fused_kernel: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(cudaGetLastError()));
     const unsigned ctas = (unsigned)((p.N + 16 * TPC - 1) / (16 * TPC));
     cudaError_t e = launch_kernel(ternary_gemv_fused_kernel<T, KW, TPC, UNROLL>, dim3(ctas), dim3(NW * 32), smem, st, p);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "ternary_gemv_fused_kernel: %s", cudaGetErrorString(e));

@@ -428,13 +428,10 @@ static int launch_w4_decode(w4dec::Params &p, cudaStream_t st)
     int smem = 0, grid = 0;
     if (!w4dec_plan(p, &smem, &grid))
         return fail(NSLQ_ERR_UNSUPPORTED, "w4a16_decode_kernel: K=%lld does not fit shared memory", (long long)p.K);
-    static int reserved = 0;
-    if (smem > reserved) {
-        if (cudaFuncSetAttribute(w4dec::w4a16_decode_kernel<XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-            return fail(NSLQ_ERR_CUDA, "w4a16_decode_kernel: cannot reserve %d bytes of shared memory: %s", smem,
-                        cudaGetErrorString(cudaGetLastError()));
-        reserved = smem;
-    }
+    static std::atomic<size_t> reserved[kMaxDevices];
+    if (reserve_smem(w4dec::w4a16_decode_kernel<XT>, reserved, (size_t)smem) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "w4a16_decode_kernel: cannot reserve %d bytes of shared memory: %s", smem,
+                    cudaGetErrorString(cudaGetLastError()));
     CUtensorMap tmap_w;
     int rc = sm100::make_map_2d(&tmap_w, p.codes, (uint64_t)(p.K / 2), (uint64_t)p.N, w4dec::PK_ROW, w4dec::BW, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;

@@ -293,13 +293,10 @@ template <int BN>
 static int launch_w4_gemm(const uint8_t *codes, const void *x, w4gemm::Params &p, cudaStream_t st)
 {
     using C = w4gemm::Cfg<BN>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(w4gemm::w4a16_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
-            return fail(NSLQ_ERR_CUDA, "w4a16_gemm_kernel: cannot reserve %d bytes of shared memory: %s", C::SMEM,
-                        cudaGetErrorString(cudaGetLastError()));
-        attr_set = true;
-    }
+    static std::atomic<size_t> reserved[kMaxDevices];
+    if (reserve_smem(w4gemm::w4a16_gemm_kernel<BN>, reserved, (size_t)C::SMEM) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "w4a16_gemm_kernel: cannot reserve %d bytes of shared memory: %s", C::SMEM,
+                    cudaGetErrorString(cudaGetLastError()));
     CUtensorMap tmap_a, tmap_w;
     int rc = sm100::make_map_2d(&tmap_a, x, (uint64_t)p.K * 2, (uint64_t)p.M, w4gemm::BKB, w4gemm::BM, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;

@@ -404,26 +404,14 @@ static int launch_w4(const W4Params &p, cudaStream_t st)
     return check_launch("w4a16_gemv_kernel");
 }
 
-static int sm_count_cached()
-{
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    }
-    return n;
-}
+static int sm_count_cached() { return sm_count_current(); }
 
 template <typename T, int NT>
 static int launch_w4_persistent(const W4Params &p, size_t smem, cudaStream_t st)
 {
-    static size_t reserved = 0;
-    if (smem > 48 * 1024 && smem > reserved) {
-        if (cudaFuncSetAttribute(w4a16_gemv_persistent_kernel<T, NT, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return fail(NSLQ_ERR_CUDA, "w4a16_gemv_persistent_kernel: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(cudaGetLastError()));
-        reserved = smem;
-    }
+    static std::atomic<size_t> reserved[kMaxDevices];
+    if (reserve_smem(w4a16_gemv_persistent_kernel<T, NT, 4>, reserved, smem) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "w4a16_gemv_persistent_kernel: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(cudaGetLastError()));
     const int ntiles = (int)((p.N + 15) / 16);
     const int per_sm = (NT == 1 && smem <= 100 * 1024) ? 2 : 1;
     const int slots = sm_count_cached() * per_sm;

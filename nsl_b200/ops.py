@@ -170,6 +170,48 @@ class BitLinear:
                                                    _tag(out.dtype), _stream()))
         return out
 
+    def gathered_workspace(self, M):
+        need = int(lib().nslq_bitlinear_gathered_workspace_bytes(M, self.K, self.N))
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=self.packed.device)
+        return self._ws
+
+    def forward_gathered(self, comm, x, y_full, bias=None, workspace=None):
+        """This rank's row shard of W applied to the replicated x; the result lands in columns
+        [rank*N, (rank+1)*N) of y_full ([M, world*N], from comm.symm_empty) on EVERY rank.
+        Bracket a group of these calls with comm.barrier() (nslq_bitlinear_forward_gathered)."""
+        _cuda2d(x, "x")
+        M = x.shape[0]
+        if tuple(y_full.shape) != (M, comm.world * self.N):
+            raise ValueError("y_full must be [M, world*N_shard]")
+        ws = workspace if workspace is not None else self.gathered_workspace(M)
+        check(lib().nslq_bitlinear_forward_gathered(comm._h, self._h, _ptr(x), _tag(x.dtype), M, _ptr(y_full),
+                                                    _tag(y_full.dtype), _ptr(bias), _ptr(ws), ws.numel(), _stream()))
+        return y_full
+
+    def forward_quantized_gathered(self, comm, qa, y_full, bias=None, scratch=None):
+        M = qa["scale"].shape[0]
+        if scratch is None and M <= 16:
+            scratch = self.gathered_workspace(M)
+        check(lib().nslq_bitlinear_forward_quantized_gathered(
+            comm._h, self._h, _ptr(qa["q_perm"]), _ptr(qa["scale"]), _ptr(qa["rowsum"]), M, _ptr(y_full),
+            _tag(y_full.dtype), _ptr(bias), _ptr(scratch), scratch.numel() if scratch is not None else 0, _stream()))
+        return y_full
+
+    def forward_quantized_cols(self, qa, copies, col0, bias=None):
+        """Writes the [M, N] result as columns [col0, col0+N) of every tensor in `copies`
+        (each [M, ld], same ld and dtype): nslq_bitlinear_forward_quantized_cols."""
+        M = qa["scale"].shape[0]
+        ld = copies[0].shape[1]
+        for t in copies:
+            if tuple(t.shape) != (M, ld) or t.dtype != copies[0].dtype or not t.is_contiguous():
+                raise ValueError("copies must be contiguous [M, ld] tensors of one dtype")
+        arr = (C.c_void_p * len(copies))(*[t.data_ptr() for t in copies])
+        scratch = self.gathered_workspace(M) if M <= 16 else None
+        check(lib().nslq_bitlinear_forward_quantized_cols(
+            self._h, _ptr(qa["q_perm"]), _ptr(qa["scale"]), _ptr(qa["rowsum"]), M, arr, len(copies), ld, col0,
+            _tag(copies[0].dtype), _ptr(bias), _ptr(scratch), scratch.numel() if scratch is not None else 0, _stream()))
+
     def forward_quantized(self, qa, out_dtype=torch.float32, return_acc=False, bias=None, residual=None, out=None):
         """qa: the dict act_quant_i8 returns (uses q_perm, scale, rowsum)."""
         M = qa["scale"].shape[0]

@@ -77,3 +77,30 @@ def test_no_oracle_in_product():
             if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.lower(), os.path.join(dirpath, f)
+
+
+def test_sharding_argument_checks_without_gpu(built):
+    """nslq_shard_* refuse bad ranks, null communicators and null buffers before touching a device."""
+    from nsl_b200 import _lib
+    l = _lib.lib()
+    h = C.c_void_p()
+    assert l.nslq_shard_init(None, 3, 2, C.byref(h)) == -1 and b"rank 3 of 2" in l.nslq_last_error()
+    assert l.nslq_shard_init(None, 0, 9, C.byref(h)) == -1              # more than NSLQ_MAX_RANKS
+    assert l.nslq_shard_init(None, 0, 2, C.byref(h)) == -1 and b"unique id" in l.nslq_last_error()
+    assert l.nslq_shard_init(None, 0, 1, None) == -1
+    assert l.nslq_shard_unique_id(None) == -1
+    assert l.nslq_allgather_cols(None, None, 1, 1, 16, None, None, None) == -1
+    assert l.nslq_peer_barrier(None, None) == -1
+    assert l.nslq_symm_alloc(None, 1024, C.byref(h)) == -1
+    assert l.nslq_shard_wait(None, None, 10) == -1
+    assert l.nslq_bitlinear_gathered_workspace_bytes(8, 3200, 1080) == l.nslq_bitlinear_workspace_bytes(8, 3200) + 34560
+    assert l.nslq_bitlinear_gathered_workspace_bytes(256, 4096, 512) == l.nslq_bitlinear_workspace_bytes(256, 4096)
+    w = C.c_void_p()
+    assert l.nslq_bitlinear_create(C.c_void_p(256), 16, 64, 1.0, C.byref(w)) == 0
+    arr = (C.c_void_p * 1)(C.c_void_p(4096))
+    # columns [8, 24) do not fit rows of 16
+    assert l.nslq_bitlinear_forward_quantized_cols(w, C.c_void_p(256), C.c_void_p(256), C.c_void_p(256), 4, arr, 1, 16, 8, 1,
+                                                   None, None, 0, None) == -2
+    assert l.nslq_bitlinear_forward_quantized_cols(w, C.c_void_p(256), C.c_void_p(256), C.c_void_p(256), 4, arr, 9, 16, 0, 1,
+                                                   None, None, 0, None) == -1
+    l.nslq_bitlinear_destroy(w)
