@@ -52,6 +52,7 @@ bool ternary_decode_fused_supported(const void *, const void *, int, int64_t, in
 int ternary_decode_fused_dispatch(const uint8_t *, const void *, int, int, int64_t, int64_t, float, void *, int, int32_t *,
                                   const float *, const float *, cudaStream_t);
 int ternary_decode_status(int *);
+int ternary_gemv_status(int *);
 bool ternary_gemm_supported(const void *, const void *, int64_t, int64_t, int64_t);
 int ternary_gemm_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int64_t, int64_t,
                           int64_t, float, void *, int, int32_t *, const float *, const float *, const OutSpec *, cudaStream_t);
@@ -184,13 +185,14 @@ int nslq_device_status(int *status)
     if (!status) return fail(NSLQ_ERR_ARG, "nslq_device_status: null output");
     if (cudaDeviceSynchronize() != cudaSuccess)
         return fail(NSLQ_ERR_CUDA, "nslq_device_status: %s", cudaGetErrorString(cudaGetLastError()));
-    int a = 0, b = 0, c = 0, d = 0;
+    int a = 0, b = 0, c = 0, d = 0, e = 0;
     int rc = ternary_gemm_status(&a);
     if (rc) return rc;
     if ((rc = w4a16_gemm_status(&b))) return rc;
     if ((rc = ternary_decode_status(&c))) return rc;
     if ((rc = w4a16_decode_status(&d))) return rc;
-    *status = a ? a : (b ? b : (c ? c : d));
+    if ((rc = ternary_gemv_status(&e))) return rc;
+    *status = a ? a : (b ? b : (c ? c : (d ? d : e)));
     return NSLQ_OK;
 }
 

@@ -12,6 +12,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "quant_core.cuh"
 
 namespace nslq {
 
@@ -44,52 +45,6 @@ static __device__ __forceinline__ int block_sum(int v, int *smem)
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
     return r;
-}
-
-// Sixteen consecutive elements of a row as fp32: four 16-byte loads for fp32, two for the 16-bit types.
-template <typename T> struct Group16;
-template <> struct Group16<float> {
-    static __device__ __forceinline__ void load(const float *row, int g, float (&f)[16]) {
-        const float4 *p = reinterpret_cast<const float4 *>(row) + 4 * (int64_t)g;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { const float4 v = p[j]; f[4 * j] = v.x; f[4 * j + 1] = v.y; f[4 * j + 2] = v.z; f[4 * j + 3] = v.w; }
-    }
-};
-template <> struct Group16<__half> {
-    static __device__ __forceinline__ void load(const __half *row, int g, float (&f)[16]) {
-        const uint4 *p = reinterpret_cast<const uint4 *>(row) + 2 * (int64_t)g;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const uint4 v = p[j];
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&w[e]));
-                f[8 * j + 2 * e] = a.x; f[8 * j + 2 * e + 1] = a.y;
-            }
-        }
-    }
-};
-template <> struct Group16<__nv_bfloat16> {
-    static __device__ __forceinline__ void load(const __nv_bfloat16 *row, int g, float (&f)[16]) {
-        const uint4 *p = reinterpret_cast<const uint4 *>(row) + 2 * (int64_t)g;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const uint4 v = p[j];
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) { f[8 * j + 2 * e] = __uint_as_float(w[e] << 16); f[8 * j + 2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u); }
-        }
-    }
-};
-
-// Four int32 in [-128, 127] -> one word, q0 in the low byte (two saturating pack instructions).
-static __device__ __forceinline__ uint32_t pack4_sat(int q0, int q1, int q2, int q3)
-{
-    uint32_t hi, w;
-    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(q3), "r"(q2), "r"(0));
-    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(q1), "r"(q0), "r"(hi));
-    return w;
 }
 
 // One group of 16 quantised and stored: natural order and/or the order the matmul kernels consume
@@ -132,13 +87,6 @@ static __device__ __forceinline__ int quant_group(const float (&f)[16], float in
     sum = __dp4a((int)pw.y, 0x01010101, sum);
     sum = __dp4a((int)pw.z, 0x01010101, sum);
     return __dp4a((int)pw.w, 0x01010101, sum);
-}
-
-static __device__ __forceinline__ float absmax16(const float (&f)[16], float m)
-{
-#pragma unroll
-    for (int e = 0; e < 16; ++e) m = fmaxf(m, fabsf(f[e]));
-    return m;
 }
 
 // VEC = true: K % 16 == 0 and 16-byte aligned rows; a thread owns whole groups of 16 consecutive

@@ -27,7 +27,8 @@
 //
 // Also here: a scalar kernel for shapes the streaming kernel cannot take
 // (K % 64 != 0 or unaligned rows); same arithmetic, natural-order activations.
-#include "common.cuh"
+#include "quant_core.cuh"
+#include "sm100_common.cuh"
 #include "ternary_mma.cuh"
 
 namespace nslq {
@@ -295,6 +296,413 @@ ternary_gemv_fused_kernel(const FusedParams p)
     }
 }
 
+// ---------------------------------------------------------------- bulk-copy decode kernel (M <= 4)
+// The same product with the weight slab brought in by the copy engine.  A CTA owns ROWS
+// consecutive output rows; in NSL's layout their packed bytes are ONE contiguous range of the
+// weight (ROWS * K/4 bytes), so the CTA's first instruction issues a handful of cp.async.bulk
+// copies (one per tile of 16 rows, each with its own mbarrier) that land the whole slab in
+// shared memory without occupying a register or an issue slot.  Only then does it wait for the
+// preceding kernel (the weights never depend on it) and quantise the token rows.  A CTA needs
+// ~70 KB and 256 threads, so three are resident per SM: with dependent launch the next two
+// calls of a decode chain already have their weights in flight while this one does arithmetic,
+// which is what a 7 MB matrix needs to approach HBM speed (the whole matrix is in flight at once).
+//
+// Shared-memory reads of the slab: lane (g, t) of an m16n8k32 fragment reads 16 bytes of rows g
+// and g+8; a quarter-warp (the unit of a 128-bit access) is rows {2p, 2p+1} x t = 0..3.  Rows are
+// K/4 bytes apart, unpadded (the copy is linear), so WHICH 16-byte piece lane t takes within an
+// 8-piece block is chosen from the row stride such that the two rows' pieces fall in disjoint
+// banks (`pat` below); any assignment is valid because every row of an MMA uses the same k for
+// the same t and the quantised activations are stored per piece.  The activations' pieces are
+// 80 bytes apart for the same reason.
+struct BulkParams {
+    const uint8_t *w;      // [N][K/4]
+    const void *x;         // [M][K] fp32 / fp16 / bf16
+    void *y;               // [M][N]
+    int32_t *acc_out;      // [M][N] or null
+    const float *bias;     // [N] or null
+    const float *residual; // [M][N] or null
+    int64_t N, K;
+    int M, y_dtype;
+    float weight_scale;
+    uint32_t pat;          // 8 nibbles: piece of lane t in sub-step 0 (nibbles 0-3) and 1 (nibbles 4-7)
+};
+
+constexpr int BULK_THREADS = 256;
+constexpr int BULK_QPIECE = 80;       // bytes between consecutive 64-k pieces of a quantised row
+
+// acc + sum_b (unsigned byte b of a) * (signed byte b of x)
+static __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t x, int acc)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(x), "r"(acc));
+    return d;
+}
+
+static __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// The same CTA with the products on the integer ALUs (dp4a) instead of mma.sync: the form used for
+// one and two tokens.  Measured on this part: with eight warps and at most sixteen accumulator
+// chains per warp the mma.sync form spends 1.5-2 us multiplying a 64-row slab (one sub-step of
+// 16 MMAs, their 64 ANDs and 8 shared-memory loads takes ~800 cycles at two warps per scheduler),
+// twice the time of this form, and its registers allow two CTAs per SM where this one fits three.
+//
+// Warp w owns rows 8w..8w+7 of the slab.  A lane owns one 32-bit word of packed weights (16 trits)
+// per pass, the same word index for all eight rows: it loads the 16 bytes of quantised activations
+// that belong to that word once per pass (consumption order: four words, one per position class)
+// and then, per row, one 4-byte word of weights -- a warp reads 128 consecutive bytes of a row, so
+// the unpadded slab is conflict-free -- and per class one AND (w & (0x03030303 << 2i) = the four
+// codes of the class, scaled by 4^i) and one dp4a.u32.s32.  Row sums are reduced by shuffles.
+template <typename T, int ROWS, int MT>
+__global__ void __launch_bounds__(BULK_THREADS, 3)
+ternary_gemv_bulk_dp4a_kernel(const BulkParams p)
+{
+    using namespace sm100;
+    static_assert(ROWS == 64 || ROWS == 32, "rows per CTA");
+    constexpr int RT = ROWS / 16;                             // copy chunks (16 rows each)
+    constexpr int KW = 64 / ROWS;                             // warps sharing a row set split the passes
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row_bytes = (int)(p.K >> 2);
+    const int nwords = row_bytes >> 2;                        // 32-bit words (16 trits) per row
+    const int qrow = (int)p.K;                                // bytes of one quantised token row, unpadded
+    uint8_t *w_s = smem;
+    uint8_t *q_s = smem + (size_t)ROWS * row_bytes;
+    int *red = reinterpret_cast<int *>(q_s + (((size_t)p.M * qrow + 15) & ~(size_t)15));   // [8 warps][8 rows][FUSED_MAX_M] (KW > 1 only)
+    float *part_f = reinterpret_cast<float *>(red + 8 * 32 * 4);          // [8][FUSED_MAX_M]
+    int *part_i = reinterpret_cast<int *>(part_f + 8 * FUSED_MAX_M);      // [8][FUSED_MAX_M]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(part_i + 8 * FUSED_MAX_M);   // [RT]
+    const int64_t n0 = (int64_t)blockIdx.x * ROWS;
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int r = 0; r < RT; ++r) mbar_init(smem_u32(bars + r), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+#pragma unroll
+        for (int r = 0; r < RT; ++r) {
+            const int64_t first = n0 + 16 * r;
+            const int64_t rows = p.N - first < 16 ? p.N - first : 16;
+            if (rows > 0) {
+                const uint32_t bytes = (uint32_t)(rows * row_bytes);
+                mbar_arrive_expect_tx(smem_u32(bars + r), bytes);
+                bulk_load(smem_u32(w_s + (size_t)16 * r * row_bytes), p.w + first * row_bytes, bytes, smem_u32(bars + r));
+            } else {
+                mbar_arrive(smem_u32(bars + r));
+            }
+        }
+    }
+    // (The next kernel of the stream is released late, after the multiply: measured in chains of these
+    // calls, an early release made the chain 25 % slower -- the dependents' CTAs and copies then crowd
+    // this grid's own -- while a late one still hides their launch and prefetch under this grid's tail.)
+    pdl_wait();
+
+    // ---- quantise the token rows (registers hold a thread's groups between the two passes)
+    const T *x = reinterpret_cast<const T *>(p.x);
+    const int ngroups = (int)(p.K >> 4);
+    constexpr int XG = MT == 1 ? 2 : 1;                       // groups per thread and token kept in registers
+    float xv[MT][XG][16];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        float mx = 0.0f;
+        if (m < p.M) {
+#pragma unroll
+            for (int i = 0; i < XG; ++i) {
+                const int gi = i * BULK_THREADS + threadIdx.x;
+                if (gi < ngroups) { Group16<T>::load(x + (int64_t)m * p.K, gi, xv[m][i]); mx = absmax16(xv[m][i], mx); }
+            }
+            for (int gi = XG * BULK_THREADS + threadIdx.x; gi < ngroups; gi += BULK_THREADS) {
+                float f[16];
+                Group16<T>::load(x + (int64_t)m * p.K, gi, f);
+                mx = absmax16(f, mx);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) part_f[warp * FUSED_MAX_M + m] = mx;
+    }
+    __syncthreads();                                          // also publishes the barrier initialisation
+    float scale[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        scale[m] = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) scale[m] = fmaxf(scale[m], part_f[w * FUSED_MAX_M + m]);
+        int sum = 0;
+        if (m < p.M) {
+            const float inv = __fdiv_rn(127.0f, scale[m]);
+            const bool fast = inv < INFINITY;                 // CTA-uniform; false for inf and NaN
+            auto put = [&](const float (&f)[16], int gi) {
+                int q[16];
+                if (fast) quant16<true>(f, inv, q); else quant16<false>(f, inv, q);
+                *reinterpret_cast<uint4 *>(q_s + (size_t)m * qrow + (size_t)gi * 16) = pack_perm16(q, sum);
+            };
+#pragma unroll
+            for (int i = 0; i < XG; ++i) {
+                const int gi = i * BULK_THREADS + threadIdx.x;
+                if (gi < ngroups) put(xv[m][i], gi);
+            }
+            for (int gi = XG * BULK_THREADS + threadIdx.x; gi < ngroups; gi += BULK_THREADS) {
+                float f[16];
+                Group16<T>::load(x + (int64_t)m * p.K, gi, f);
+                put(f, gi);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) part_i[warp * FUSED_MAX_M + m] = sum;
+    }
+    __syncthreads();
+
+    // ---- multiply: warp -> rows 8*(warp / KW) .. +7, passes warp % KW, + KW, ... (32 words per pass)
+    const int rset = warp / KW, kw = warp % KW;
+    const uint8_t *wr_s = w_s + (size_t)(8 * rset) * row_bytes;
+    const int npass = (nwords + 31) >> 5;
+    int tot[MT][8];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int r = 0; r < 8; ++r) tot[m][r] = 0;
+    const bool landed = mbar_wait_warp(smem_u32(bars + (8 * rset) / 16), 0, 0x801);
+    if (landed) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m >= p.M) break;
+            int acc[8][4];
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[r][i] = 0;
+            for (int ps = kw; ps < npass; ps += KW) {
+                const int wi = 32 * ps + lane;
+                if (wi < nwords) {
+                    const uint4 xw = *reinterpret_cast<const uint4 *>(q_s + (size_t)m * qrow + (size_t)wi * 16);
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        const uint32_t ww = *reinterpret_cast<const uint32_t *>(wr_s + (size_t)r * row_bytes + (size_t)wi * 4);
+                        acc[r][0] = dp4a_us(ww & 0xc0c0c0c0u, xw.x, acc[r][0]);
+                        acc[r][1] = dp4a_us(ww & 0x30303030u, xw.y, acc[r][1]);
+                        acc[r][2] = dp4a_us(ww & 0x0c0c0c0cu, xw.z, acc[r][2]);
+                        acc[r][3] = dp4a_us(ww & 0x03030303u, xw.w, acc[r][3]);
+                    }
+                }
+            }
+            // class sums are exact multiples of 64, 16, 4, 1
+#pragma unroll
+            for (int r = 0; r < 8; ++r) tot[m][r] = (acc[r][0] >> 6) + (acc[r][1] >> 4) + (acc[r][2] >> 2) + acc[r][3];
+        }
+    }
+    pdl_launch_dependents();
+    // The 32 lanes of a warp hold partial sums of the same eight rows.  Transposing butterfly: at each of
+    // the first three steps a lane keeps half of its rows and hands the other half to its partner, so the
+    // eight sums cost 4 + 2 + 1 + 1 + 1 shuffles instead of forty (shuffles share one unit per SM and all
+    // eight warps arrive here together).  Afterwards lane l holds the total of row 4*b4 + 2*b3 + b2 of l.
+    int rowtot[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        int v4[4], v2[2];
+        const bool hi16 = lane & 16, hi8 = lane & 8, hi4 = lane & 4;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int keep = hi16 ? tot[m][4 + i] : tot[m][i], give = hi16 ? tot[m][i] : tot[m][4 + i];
+            v4[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int keep = hi8 ? v4[2 + i] : v4[i], give = hi8 ? v4[i] : v4[2 + i];
+            v2[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+        }
+        const int keep = hi4 ? v2[1] : v2[0], give = hi4 ? v2[0] : v2[1];
+        int v = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        rowtot[m] = v;
+    }
+    const int myrow = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+    if (KW > 1) {                                             // K was split over KW warps: add through shared memory
+        if ((lane & 3) == 0) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) red[(warp * 8 + myrow) * FUSED_MAX_M + m] = rowtot[m];
+        }
+        __syncthreads();
+        if (kw != 0) return;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            rowtot[m] = 0;
+#pragma unroll
+            for (int w = 0; w < KW; ++w) rowtot[m] += red[((rset * KW + w) * 8 + myrow) * FUSED_MAX_M + m];
+        }
+    }
+    // of the four lanes that hold a row's total, lane (l & 3) == m stores token m
+    const int64_t n = n0 + 8 * rset + myrow;
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        if ((lane & 3) == m && m < p.M && n < p.N) {
+            int rs = 0;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) rs += part_i[w * FUSED_MAX_M + m];
+            const int a = rowtot[m] - rs;
+            const int64_t o = (int64_t)m * p.N + n;
+            if (p.acc_out) p.acc_out[o] = a;
+            float v = bitlinear_finalize(a, scale[m], p.weight_scale);
+            if (p.bias) v = __fadd_rn(v, p.bias[n]);
+            if (p.residual) v = __fadd_rn(v, p.residual[o]);
+            store_out(p.y, p.y_dtype, o, v);
+        }
+    }
+}
+
+// The mma.sync form.  ROWS = 64 or 32 output rows per CTA, NW warps.  A warp owns one 16-row tile
+// and every KQ-th sub-step (four pieces per row) of its K range, on eight independent accumulator
+// chains (2 word pairs x 4 position classes).  Used for three and four tokens, where the dp4a form's
+// integer work (proportional to the token count) exceeds this form's.  Measured at one token on a
+// 64-row slab of K = 3200: 2.1 us for this phase with eight warps, more with sixteen (64 registers
+// per thread then, with spills); the tensor pipe itself is busy for under half a microsecond.
+template <typename T, int ROWS, int NW>
+__global__ void __launch_bounds__(NW * 32, (NW <= 8) ? 3 : 2)
+ternary_gemv_bulk_kernel(const BulkParams p)
+{
+    using namespace sm100;
+    static_assert(ROWS == 64 || ROWS == 32, "rows per CTA");
+    constexpr int RT = ROWS / 16, KQ = NW / RT, NTHR = NW * 32;
+    static_assert(NW % RT == 0, "warps per tile");
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int row_bytes = (int)(p.K >> 2);
+    const int npieces = row_bytes >> 4;                      // 16-byte pieces (64 trits) per row
+    const int qrow = npieces * BULK_QPIECE;                   // bytes of one quantised token row in shared memory
+    uint8_t *w_s = smem;
+    uint8_t *q_s = smem + (size_t)ROWS * row_bytes;
+    int *red = reinterpret_cast<int *>(q_s + (((size_t)p.M * qrow + 15) & ~(size_t)15));   // [NW][32][4]
+    float *part_f = reinterpret_cast<float *>(red + NW * 32 * 4);         // [NW][FUSED_MAX_M]
+    int *part_i = reinterpret_cast<int *>(part_f + NW * FUSED_MAX_M);     // [NW][FUSED_MAX_M]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(part_i + NW * FUSED_MAX_M);  // [RT]
+    const int64_t n0 = (int64_t)blockIdx.x * ROWS;
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int r = 0; r < RT; ++r) mbar_init(smem_u32(bars + r), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+#pragma unroll
+        for (int r = 0; r < RT; ++r) {
+            const int64_t first = n0 + 16 * r;
+            const int64_t rows = p.N - first < 16 ? p.N - first : 16;
+            if (rows > 0) {
+                const uint32_t bytes = (uint32_t)(rows * row_bytes);
+                mbar_arrive_expect_tx(smem_u32(bars + r), bytes);
+                bulk_load(smem_u32(w_s + (size_t)16 * r * row_bytes), p.w + first * row_bytes, bytes, smem_u32(bars + r));
+            } else {
+                mbar_arrive(smem_u32(bars + r));
+            }
+        }
+    }
+    // The weights are on their way.  Everything below reads what the preceding kernel produced (x) or
+    // writes what it may still read (y).
+    pdl_wait();
+
+    // ---- quantise the M token rows into shared memory (the arithmetic of act_quant_kernel).  A thread
+    // owns whole groups of 16 consecutive elements: they become the four words of the consumption order
+    // with no exchange between threads.  The row is read twice (maximum, then rounding); the second
+    // read hits the L1 cache.
+    const T *x = reinterpret_cast<const T *>(p.x);
+    const int ngroups = (int)(p.K >> 4);
+    for (int m = 0; m < p.M; ++m) {
+        float mx = 0.0f;
+        for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
+            float f[16];
+            Group16<T>::load(x + (int64_t)m * p.K, gi, f);
+            mx = absmax16(f, mx);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) part_f[warp * FUSED_MAX_M + m] = mx;
+    }
+    __syncthreads();                                          // also publishes the barrier initialisation
+    for (int m = 0; m < p.M; ++m) {
+        float scale = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) scale = fmaxf(scale, part_f[w * FUSED_MAX_M + m]);
+        const float inv = __fdiv_rn(127.0f, scale);
+        const bool fast = inv < INFINITY;                     // CTA-uniform; false for inf and NaN
+        int sum = 0;
+        for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
+            float f[16];
+            Group16<T>::load(x + (int64_t)m * p.K, gi, f);
+            int q[16];
+            if (fast) quant16<true>(f, inv, q); else quant16<false>(f, inv, q);
+            *reinterpret_cast<uint4 *>(q_s + (size_t)m * qrow + (gi >> 2) * BULK_QPIECE + (gi & 3) * 16) = pack_perm16(q, sum);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) part_i[warp * FUSED_MAX_M + m] = sum;
+    }
+    __syncthreads();
+
+    // ---- multiply: warp (tile, kq) takes sub-steps kq, kq + KQ, ... of its tile
+    const int tile = warp / KQ, kq = warp % KQ;
+    const bool tok_ok = g < p.M;
+    const uint8_t *ra_s = w_s + (size_t)(16 * tile + g) * row_bytes;      // rows g and g+8 of the tile
+    const uint8_t *rb_s = ra_s + (size_t)8 * row_bytes;
+    const uint8_t *xq_s = q_s + (size_t)(tok_ok ? g : 0) * qrow;
+    const int pc0 = (p.pat >> (4 * t)) & 15, pc1 = (p.pat >> (16 + 4 * t)) & 15;
+    int first1 = 8;                                           // lowest piece of the second sub-step (warp-uniform)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) first1 = min(first1, (int)((p.pat >> (16 + 4 * i)) & 15));
+    Acc4 acc0, acc1;
+    acc_zero(acc0);
+    acc_zero(acc1);
+    const bool landed = mbar_wait_warp(smem_u32(bars + tile), 0, 0x801);
+    if (landed) {
+        const int nsub = 2 * ((npieces + 7) >> 3);
+        for (int u = kq; u < nsub; u += KQ) {
+            const int b = u >> 1, sub = u & 1;
+            if (sub && 8 * b + first1 >= npieces) continue;  // warp-uniform: the row ends inside the first sub-step
+            const int pc = 8 * b + (sub ? pc1 : pc0);
+            const bool ok = pc < npieces;
+            const uint4 zero = make_uint4(0, 0, 0, 0);
+            const uint4 ra = ok ? *reinterpret_cast<const uint4 *>(ra_s + pc * 16) : zero;
+            const uint4 rb = ok ? *reinterpret_cast<const uint4 *>(rb_s + pc * 16) : zero;
+            uint4 xq[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                xq[j] = (ok && tok_ok) ? *reinterpret_cast<const uint4 *>(xq_s + pc * BULK_QPIECE + j * 16) : zero;
+            chunk_mma2(acc0, acc1, ra, rb, xq);
+        }
+    }
+    pdl_launch_dependents();                                  // late, as in the dp4a form
+#pragma unroll
+    for (int r = 0; r < 4; ++r) red[(warp * 32 + lane) * 4 + r] = acc_value(acc0, r) + acc_value(acc1, r);
+    __syncthreads();
+
+    // ---- ROWS rows x up to 4 tokens; consecutive threads take consecutive rows
+    for (int e = threadIdx.x; e < ROWS * FUSED_MAX_M; e += NTHR) {
+        const int row = e % ROWS, tok = e / ROWS;
+        const int64_t n = n0 + row;
+        if (tok >= p.M || n >= p.N) continue;
+        const int tl = row >> 4, rr = row & 15;
+        const int src_lane = (rr & 7) * 4 + (tok >> 1);
+        const int src_reg = ((rr >> 3) << 1) | (tok & 1);
+        int a = 0, rs = 0;
+#pragma unroll
+        for (int w = 0; w < KQ; ++w) a += red[((tl * KQ + w) * 32 + src_lane) * 4 + src_reg];
+#pragma unroll
+        for (int w = 0; w < NW; ++w) rs += part_i[w * FUSED_MAX_M + tok];
+        a -= rs;
+        float sc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) sc = fmaxf(sc, part_f[w * FUSED_MAX_M + tok]);
+        const int64_t o = (int64_t)tok * p.N + n;
+        if (p.acc_out) p.acc_out[o] = a;
+        float v = bitlinear_finalize(a, sc, p.weight_scale);
+        if (p.bias) v = __fadd_rn(v, p.bias[n]);
+        if (p.residual) v = __fadd_rn(v, p.residual[o]);
+        store_out(p.y, p.y_dtype, o, v);
+    }
+}
+
 // Scalar kernel for any K % 4 == 0: one thread per (token, output row), natural
 // order int8 activations, byte loads.  Correctness path for odd shapes only.
 __global__ void __launch_bounds__(128)
@@ -383,6 +791,90 @@ static int pick_fused(const FusedParams &p, cudaStream_t st)
     return launch_fused<T, 8, 1>(p, st);
 }
 
+// Bank-conflict-free piece assignment for a row stride of `row_bytes` (see the kernel's comment): the
+// pieces lanes t = 0..3 take in the two sub-steps of an 8-piece block, one nibble each.
+static uint32_t bulk_pattern(int64_t row_bytes)
+{
+    const int s = (int)((row_bytes / 4) % 32);     // bank distance between consecutive rows
+    if (s == 8 || s == 24) return 0x76325410u;     // {0,1,4,5} then {2,3,6,7}
+    if (s % 8 == 4) return 0x75316420u;            // {0,2,4,6} then {1,3,5,7}
+    return 0x76543210u;                            // s == 16: conflict-free as is; s == 0: two-way conflicts whatever the order
+}
+
+static int bulk_rows(int64_t K)
+{
+    const int64_t row_bytes = K / 4;
+    if (64 * row_bytes <= 64 * 1024) return 64;
+    if (32 * row_bytes <= 96 * 1024) return 32;
+    return 0;
+}
+
+constexpr int BULK_MMA_WARPS = 8;
+
+static size_t bulk_smem(int rows, int M, int64_t K, int nw = 8)
+{
+    const size_t qrow = (size_t)(K / 64) * BULK_QPIECE;
+    return (size_t)rows * (K / 4) + (((size_t)M * qrow + 15) & ~(size_t)15) + (size_t)nw * 32 * 4 * 4 + (size_t)nw * FUSED_MAX_M * 8 + 4 * 8 + 64;
+}
+
+template <typename T, int ROWS>
+static int launch_bulk(const BulkParams &p, cudaStream_t st)
+{
+    constexpr int NW = BULK_MMA_WARPS;
+    const size_t smem = bulk_smem(ROWS, p.M, p.K, NW);
+    static std::atomic<size_t> reserved[kMaxDevices];
+    static std::atomic<int> carved[kMaxDevices];
+    if (!carved[device_index()].load(std::memory_order_acquire)) {
+        // Several CTAs of this kernel (and of the next call) must fit an SM side by side, each with its slab in
+        // shared memory: ask for the largest shared-memory carve-out instead of the one sized for a single CTA.
+        cudaFuncSetAttribute(ternary_gemv_bulk_kernel<T, ROWS, NW>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        carved[device_index()].store(1, std::memory_order_release);
+    }
+    if (reserve_smem(ternary_gemv_bulk_kernel<T, ROWS, NW>, reserved, smem) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "ternary_gemv_bulk_kernel: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(cudaGetLastError()));
+    const unsigned ctas = (unsigned)((p.N + ROWS - 1) / ROWS);
+    cudaError_t e = launch_kernel(ternary_gemv_bulk_kernel<T, ROWS, NW>, dim3(ctas), dim3(NW * 32), smem, st, p);
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "ternary_gemv_bulk_kernel: %s", cudaGetErrorString(e));
+    return check_launch("ternary_gemv_bulk_kernel");
+}
+
+template <typename T, int ROWS, int MT>
+static int launch_bulk_dp4a(const BulkParams &p, cudaStream_t st)
+{
+    const size_t smem = bulk_smem(ROWS, p.M, p.K);
+    static std::atomic<size_t> reserved[kMaxDevices];
+    static std::atomic<int> carved[kMaxDevices];
+    if (!carved[device_index()].load(std::memory_order_acquire)) {
+        cudaFuncSetAttribute(ternary_gemv_bulk_dp4a_kernel<T, ROWS, MT>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        carved[device_index()].store(1, std::memory_order_release);
+    }
+    if (reserve_smem(ternary_gemv_bulk_dp4a_kernel<T, ROWS, MT>, reserved, smem) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "ternary_gemv_bulk_dp4a_kernel: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(cudaGetLastError()));
+    const unsigned ctas = (unsigned)((p.N + ROWS - 1) / ROWS);
+    cudaError_t e = launch_kernel(ternary_gemv_bulk_dp4a_kernel<T, ROWS, MT>, dim3(ctas), dim3(BULK_THREADS), smem, st, p);
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "ternary_gemv_bulk_dp4a_kernel: %s", cudaGetErrorString(e));
+    return check_launch("ternary_gemv_bulk_dp4a_kernel");
+}
+
+template <typename T>
+static int pick_bulk(const BulkParams &p, cudaStream_t st)
+{
+    if (p.M <= 2) {                      // one or two tokens: integer ALUs (see the kernel's comment)
+        if (bulk_rows(p.K) == 64) return p.M == 1 ? launch_bulk_dp4a<T, 64, 1>(p, st) : launch_bulk_dp4a<T, 64, 2>(p, st);
+        return p.M == 1 ? launch_bulk_dp4a<T, 32, 1>(p, st) : launch_bulk_dp4a<T, 32, 2>(p, st);
+    }
+    return bulk_rows(p.K) == 64 ? launch_bulk<T, 64>(p, st) : launch_bulk<T, 32>(p, st);
+}
+
+// The bulk-copy kernel takes the call when the slab of its CTA and the quantised rows fit shared memory.
+static bool bulk_supported(int M, int64_t K)
+{
+    const int rows = bulk_rows(K);
+    return rows != 0 && bulk_smem(rows, M, K, BULK_MMA_WARPS) <= 160 * 1024;
+}
+
+int ternary_gemv_status(int *out) { return sm100::read_wait_status(out); }
+
 // x [M][K] in its own dtype, M <= 4, K % 64 == 0, 16-byte aligned x and w, M*K <= 160 KiB.
 bool ternary_gemv_fused_supported(const void *w, const void *x, int64_t M, int64_t K)
 {
@@ -393,6 +885,15 @@ int ternary_gemv_fused_dispatch(const uint8_t *w, const void *x, int x_dtype, in
                                 float weight_scale, void *y, int y_dtype, int32_t *acc_out, const float *bias,
                                 const float *residual, cudaStream_t st)
 {
+    if (bulk_supported(M, K)) {
+        BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale, bulk_pattern(K / 4)};
+        switch (x_dtype) {
+        case NSLQ_DTYPE_F32: return pick_bulk<float>(b, st);
+        case NSLQ_DTYPE_FP16: return pick_bulk<__half>(b, st);
+        case NSLQ_DTYPE_BF16: return pick_bulk<__nv_bfloat16>(b, st);
+        default: return fail(NSLQ_ERR_ARG, "BitLinear: x_dtype %d not in {F32,FP16,BF16}", x_dtype);
+        }
+    }
     FusedParams p{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale};
     switch (x_dtype) {
     case NSLQ_DTYPE_F32: return pick_fused<float>(p, st);

@@ -13,7 +13,8 @@ import torch
 from ._lib import check, lib
 
 F64, F32, FP16, BF16, INT8, I32 = 0, 1, 2, 3, 4, 9
-_TAG = {torch.float64: F64, torch.float32: F32, torch.float16: FP16, torch.bfloat16: BF16}
+_TAG = {torch.float64: F64, torch.float32: F32, torch.float16: FP16, torch.bfloat16: BF16, torch.int8: INT8,
+        torch.int32: I32}
 
 
 def _tag(dtype):

@@ -88,7 +88,9 @@ def test_errors(ops):
     x = torch.zeros(2, 100, device="cuda")
     with pytest.raises(NslqError):
         ops.act_quant_i8(x, plain=True, perm=True)      # q_perm needs K % 16 == 0
-    with pytest.raises(TypeError):
+    with pytest.raises(NslqError):                      # int32 has a tensor tag, but the quantiser takes floats only
         ops.act_quant_i8(torch.zeros(2, 16, device="cuda", dtype=torch.int32))
+    with pytest.raises(TypeError):                      # a dtype with no NSL tensor tag at all
+        ops.act_quant_i8(torch.zeros(2, 16, device="cuda", dtype=torch.int64))
     with pytest.raises(ValueError):
         ops.act_quant_i8(torch.zeros(2, 16))            # CPU tensor: no CPU path
