@@ -225,7 +225,7 @@ class PrefillGemm(Workload):
             self.xh.append(x.cpu().pin_memory())
             self.xst.append(torch.empty_like(x))
             self.ys.append(torch.empty(self.M, rows, device="cuda", dtype=self.ydt))
-            if world > 1 and self.mode == "peer":
+            if world > 1 and self.mode in ("peer", "ce"):
                 self.ygs.append(comm.symm_empty((self.M, n), self.ydt))        # [M, N], every rank stores into it
             elif world > 1:
                 self.ygs.append(torch.empty(world, self.M, rows, device="cuda", dtype=self.ydt))
@@ -239,7 +239,7 @@ class PrefillGemm(Workload):
         self.e2e_streams = None
         self.kernel_launches = 2                               # per kernel_only() pass
         # 2 x (act quant + GEMM); sharded: + 2 flag barriers (peer) or 2 NCCL all-gathers, not counted as ours
-        self.launches_per_step = 4 + (2 if self.mode == "peer" else 0)
+        self.launches_per_step = 4 + (2 if self.mode in ("peer", "ce") else 0)
         self.h2d = self.M * (self.H + self.F) * 4
         self.d2h = self.M * (self.H + self.F) * es
         self.l2_note = "inputs larger than L2 (26+71 MB of x, 14 MB of W, %d MB of y per step)" % (self.d2h // 1000000)
@@ -255,6 +255,9 @@ class PrefillGemm(Workload):
     def one_call(self, i, x):
         if self.mode == "peer":
             self.layers[i].forward_gathered(self.comm, x, self.ygs[i], workspace=self.wss[i])
+        elif self.mode == "ce":
+            # the product goes into this rank's own copy of the [M, N] result (column block, row stride N)
+            self.layers[i].forward_cols(x, [self.ygs[i]], self.rank * self.layers[i].N, workspace=self.wss[i])
         else:
             self.layers[i].forward(x, out=self.ys[i], workspace=self.wss[i])
             if self.mode == "nccl":
@@ -284,6 +287,22 @@ class PrefillGemm(Workload):
             cur.wait_event(join)
             self.comm.barrier()
             return
+        if self.mode == "ce":
+            # Copy-engine plane: each projection writes its block into this rank's own copy; the copy engines
+            # then push the block to the peers on a second stream, under the next projection's kernels.
+            self.comm.barrier()
+            for i in range(2):
+                self.one_call(i, xs[i])
+                ready = torch.cuda.Event()
+                ready.record(cur)
+                self.side.wait_event(ready)
+                with torch.cuda.stream(self.side):
+                    self.comm.push_cols_async(self.ygs[i], self.layers[i].N)
+            done = torch.cuda.Event()
+            done.record(self.side)
+            cur.wait_event(done)
+            self.comm.barrier()
+            return
         # NCCL plane: the all-gather of the first projection's shards runs on a second stream under the
         # second projection's quantisation and GEMM (both captured in the graph).
         for i in range(2):
@@ -301,6 +320,8 @@ class PrefillGemm(Workload):
         for i in range(2):
             if self.mode == "peer":
                 self.layers[i].forward_quantized_gathered(self.comm, self.qas[i], self.ygs[i])
+            elif self.mode == "ce":
+                self.layers[i].forward_quantized_cols(self.qas[i], [self.ygs[i]], self.rank * self.layers[i].N)
             else:
                 self.layers[i].forward_quantized(self.qas[i], out=self.ys[i])
 
@@ -313,7 +334,7 @@ class PrefillGemm(Workload):
         rows = torch.arange(0, self.M, 16, device="cuda")
         for i, (n, k) in enumerate(self.SHAPES):
             ref = self.ops.BitLinear(self.full_w[i], 0.02).forward(self.xs[i][rows].contiguous(), out_dtype=self.ydt)
-            got = self.ygs[i] if self.mode == "peer" else self.ygs[i].permute(1, 0, 2).reshape(self.M, n)
+            got = self.ygs[i] if self.mode in ("peer", "ce") else self.ygs[i].permute(1, 0, 2).reshape(self.M, n)
             ok = ok and bool(torch.equal(got[rows], ref))
         return "gathered [M,N] of both projections bit-equal to the unsharded kernel on %d sampled rows: %s" % (
             rows.numel(), "yes" if ok else "NO")
@@ -729,7 +750,17 @@ def run_ours(args):
     comm = None
     if world > 1:
         from nsl_b200 import sharding
-        comm = sharding.Comm.from_torch()          # the library's own communicator (NCCL + peer memory)
+        # NCCL may print its version banner on stdout when a communicator is created; stdout carries the one
+        # JSON line, so the banner is sent to stderr
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            comm = sharding.Comm.from_torch()      # the library's own communicator (NCCL + peer memory)
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
     if args.no_pdl:
         lib().nslq_set_dependent_launch(0)
     peaks = load_peaks()
@@ -749,6 +780,10 @@ def run_ours(args):
     check = wl.gather_check() if hasattr(wl, "gather_check") else None
     if world == 1:
         par = "single GPU"
+    elif getattr(wl, "mode", "nccl") == "ce":
+        par = ("weight rows sharded x%d, x replicated; each GEMM writes its block into this rank's copy of the result and "
+               "the copy engines push it to every peer on a second stream (under the next projection), flag barriers "
+               "before and after" % world)
     elif getattr(wl, "mode", "nccl") == "peer":
         par = ("weight rows sharded x%d, x replicated; all-gather fused into the GEMM epilogue (tiles stored into every "
                "rank's copy over NVLink), two projections on two streams, flag barriers before and after" % world)
@@ -840,7 +875,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=WORKLOAD_KEYS)
     ap.add_argument("--streams", type=int, default=1,
                     help="decode_gemv: issue the independent calls of a step round-robin on this many streams")
-    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+    ap.add_argument("--gather", default="peer", choices=["peer", "ce", "nccl"],
                     help="N > 1, prefill: shards stored into every rank's copy by the GEMM epilogue, or ncclAllGather")
     ap.add_argument("--out-dtype", default="bf16", choices=["bf16", "f32"], help="prefill: dtype of y")
     ap.add_argument("--no-graph", action="store_true", help="issue launches directly instead of replaying a CUDA graph")

@@ -385,6 +385,14 @@ int nslq_peer_allgather_cols(nslq_comm_t *c, const void *y_local, int dtype, int
                              void *y_full, void *stream);
 
 /*
+ * The same exchange by the copy engines: this rank's column block, already in place in its own
+ * copy of y_full, is copied into every peer's copy with one strided cudaMemcpy2DAsync per peer
+ * on `stream`.  No SM takes part, so the transfer runs under the kernels of other streams -- the
+ * form to use when the block is produced by a kernel that fills every SM.
+ */
+int nslq_peer_push_cols_async(nslq_comm_t *c, void *y_full, int dtype, int64_t M, int64_t N_local, void *stream);
+
+/*
  * BitLinear on this rank's row shard of W with the all-gather fused in: y_full is the whole
  * [M][world*N_shard] result, inside a buffer of nslq_symm_alloc.  For M > 16 the tensor-core
  * GEMM's epilogue stores each finished tile into this rank's copy and into every peer's copy
@@ -404,8 +412,12 @@ int64_t nslq_bitlinear_gathered_workspace_bytes(int64_t M, int64_t K, int64_t N_
  * [M, N] result is written as columns [col0, col0+N) of rows of `ldy` elements into n_copies
  * (1..8) arrays at once -- y_copies is a HOST array of device pointers to the [M][ldy] arrays.
  * E.g. q, k and v projections writing the column blocks of one fused [M, 3*hidden] buffer, or a
- * test standing in for two ranks on one GPU.  y_scratch as above (M <= 16 only).
+ * test standing in for two ranks on one GPU.  y_scratch as above (M <= 16 only); the form without
+ * _quantized quantises x first and takes the workspace of the gathered call.
  */
+int nslq_bitlinear_forward_cols(const nslq_bitlinear_t *w, const void *x, int x_dtype, int64_t M,
+                                void *const *y_copies, int n_copies, int64_t ldy, int64_t col0, int y_dtype,
+                                const float *bias, void *workspace, int64_t workspace_bytes, void *stream);
 int nslq_bitlinear_forward_quantized_cols(const nslq_bitlinear_t *w, const int8_t *q_perm, const float *scale,
                                           const int32_t *rowsum, int64_t M, void *const *y_copies, int n_copies,
                                           int64_t ldy, int64_t col0, int y_dtype, const float *bias,

@@ -46,7 +46,9 @@ SIGNATURES = {
     "nslq_peer_barrier": (i32, [vp, vp]),
     "nslq_shard_status": (i32, [vp, C.POINTER(i32)]),
     "nslq_peer_allgather_cols": (i32, [vp, vp, i32, i64, i64, vp, vp]),
+    "nslq_peer_push_cols_async": (i32, [vp, vp, i32, i64, i64, vp]),
     "nslq_bitlinear_gathered_workspace_bytes": (i64, [i64, i64, i64]),
+    "nslq_bitlinear_forward_cols": (i32, [vp, vp, i32, i64, C.POINTER(vp), i32, i64, i64, i32, vp, vp, i64, vp]),
     "nslq_bitlinear_forward_quantized_cols": (i32, [vp, vp, vp, vp, i64, C.POINTER(vp), i32, i64, i64, i32, vp, vp, i64, vp]),
     "nslq_bitlinear_forward_gathered": (i32, [vp, vp, vp, i32, i64, vp, i32, vp, vp, i64, vp]),
     "nslq_bitlinear_forward_quantized_gathered": (i32, [vp, vp, vp, vp, vp, i64, vp, i32, vp, vp, i64, vp]),

@@ -550,29 +550,69 @@ int nslq_bitlinear_forward_quantized_gathered(nslq_comm_t *c, const nslq_bitline
                                                  bias, y_scratch, y_scratch_bytes, stream);
 }
 
+int nslq_bitlinear_forward_cols(const nslq_bitlinear_t *w, const void *x, int x_dtype, int64_t M, void *const *y_copies,
+                                int n_copies, int64_t ldy, int64_t col0, int y_dtype, const float *bias, void *workspace,
+                                int64_t workspace_bytes, void *stream)
+{
+    if (!w || !x || !y_copies) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_forward_cols: null argument");
+    if (M < 0) return fail(NSLQ_ERR_SHAPE, "nslq_bitlinear_forward_cols: M=%lld", (long long)M);
+    if (M == 0) return NSLQ_OK;
+    if (w->K % 64 != 0 || !aligned16(w->packed))
+        return fail(NSLQ_ERR_UNSUPPORTED, "nslq_bitlinear_forward_cols: needs K %% 64 == 0 and a 16-byte aligned weight (K=%lld)", (long long)w->K);
+    const int64_t need = nslq_bitlinear_gathered_workspace_bytes(M, w->K, w->N);
+    if (!workspace || workspace_bytes < need)
+        return fail(NSLQ_ERR_WORKSPACE, "nslq_bitlinear_forward_cols: workspace %lld bytes, need %lld", (long long)workspace_bytes, (long long)need);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_forward_cols: workspace not 256-byte aligned");
+    int8_t *q = (int8_t *)workspace;
+    float *scale = (float *)((char *)workspace + align256(M * w->K));
+    int32_t *rowsum = (int32_t *)((char *)scale + align256(M * 4));
+    void *y_scratch = (char *)rowsum + align256(M * 4);
+    int rc = act_quant_dispatch(x, x_dtype, M, w->K, nullptr, q, scale, rowsum, (cudaStream_t)stream);
+    if (rc) return rc;
+    return nslq_bitlinear_forward_quantized_cols(w, q, scale, rowsum, M, y_copies, n_copies, ldy, col0, y_dtype, bias, y_scratch,
+                                                 workspace_bytes - nslq_bitlinear_workspace_bytes(M, w->K), stream);
+}
+
 int nslq_bitlinear_forward_gathered(nslq_comm_t *c, const nslq_bitlinear_t *w, const void *x, int x_dtype, int64_t M,
                                     void *y_full, int y_dtype, const float *bias, void *workspace, int64_t workspace_bytes,
                                     void *stream)
 {
     int rc = comm_check(c, "nslq_bitlinear_forward_gathered");
     if (rc) return rc;
-    if (!w || !x || !y_full) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_forward_gathered: null argument");
-    if (M < 0) return fail(NSLQ_ERR_SHAPE, "nslq_bitlinear_forward_gathered: M=%lld", (long long)M);
-    if (M == 0) return NSLQ_OK;
-    if (w->K % 64 != 0 || !aligned16(w->packed))
-        return fail(NSLQ_ERR_UNSUPPORTED, "nslq_bitlinear_forward_gathered: needs K %% 64 == 0 and a 16-byte aligned weight (K=%lld)", (long long)w->K);
-    const int64_t need = nslq_bitlinear_gathered_workspace_bytes(M, w->K, w->N);
-    if (!workspace || workspace_bytes < need)
-        return fail(NSLQ_ERR_WORKSPACE, "nslq_bitlinear_forward_gathered: workspace %lld bytes, need %lld", (long long)workspace_bytes, (long long)need);
-    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_forward_gathered: workspace not 256-byte aligned");
-    int8_t *q = (int8_t *)workspace;
-    float *scale = (float *)((char *)workspace + align256(M * w->K));
-    int32_t *rowsum = (int32_t *)((char *)scale + align256(M * 4));
-    void *y_scratch = (char *)rowsum + align256(M * 4);
-    rc = act_quant_dispatch(x, x_dtype, M, w->K, nullptr, q, scale, rowsum, (cudaStream_t)stream);
+    if (!w || !y_full) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_forward_gathered: null argument");
+    const int es = y_dtype == NSLQ_DTYPE_F32 ? 4 : 2;
+    const int64_t n_total = w->N * c->world;
+    PeerPtrs pp = {};
+    if ((rc = comm_peer_ptrs(c, y_full, (M > 0 ? M : 0) * n_total * es, &pp))) return rc;
+    void *copies[NSLQ_MAX_RANKS];
+    copies[0] = y_full;                                   // this rank's own copy first
+    int n = 1;
+    for (int r = 0; r < c->world; ++r)
+        if (r != c->rank) copies[n++] = pp.p[r];
+    return nslq_bitlinear_forward_cols(w, x, x_dtype, M, copies, n, n_total, w->N * c->rank, y_dtype, bias, workspace,
+                                       workspace_bytes, stream);
+}
+
+int nslq_peer_push_cols_async(nslq_comm_t *c, void *y_full, int dtype, int64_t M, int64_t N_local, void *stream)
+{
+    int rc = comm_check(c, "nslq_peer_push_cols_async");
     if (rc) return rc;
-    return nslq_bitlinear_forward_quantized_gathered(c, w, q, scale, rowsum, M, y_full, y_dtype, bias, y_scratch,
-                                                     workspace_bytes - nslq_bitlinear_workspace_bytes(M, w->K), stream);
+    const int es = elem_size(dtype);
+    if (!es) return fail(NSLQ_ERR_ARG, "nslq_peer_push_cols_async: dtype tag %d", dtype);
+    if (!y_full) return fail(NSLQ_ERR_ARG, "nslq_peer_push_cols_async: null buffer");
+    if (M <= 0 || N_local <= 0) return M == 0 ? NSLQ_OK : fail(NSLQ_ERR_SHAPE, "nslq_peer_push_cols_async: M=%lld N_local=%lld", (long long)M, (long long)N_local);
+    const size_t row = (size_t)N_local * es, pitch = row * c->world, off = row * c->rank;
+    PeerPtrs dst = {};
+    if ((rc = comm_peer_ptrs(c, y_full, (int64_t)(M * pitch), &dst))) return rc;
+    // one strided copy per peer, by the copy engines: no SM is involved, so the transfer runs under
+    // whatever kernels follow on other streams
+    for (int i = 1; i < c->world; ++i) {
+        const int r = (c->rank + i) % c->world;              // staggered, so the ranks do not all write to the same peer first
+        cudaError_t e = cudaMemcpy2DAsync((char *)dst.p[r] + off, pitch, (const char *)y_full + off, pitch, row, (size_t)M,
+                                          cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+        if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "nslq_peer_push_cols_async: copy to rank %d: %s", r, cudaGetErrorString(e));
+    }
+    return NSLQ_OK;
 }
 
 int nslq_shard_status(nslq_comm_t *c, int *status)

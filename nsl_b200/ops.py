@@ -199,6 +199,16 @@ class BitLinear:
             _tag(y_full.dtype), _ptr(bias), _ptr(scratch), scratch.numel() if scratch is not None else 0, _stream()))
         return y_full
 
+    def forward_cols(self, x, copies, col0, bias=None, workspace=None):
+        """Quantises x and writes the [M, N] result as columns [col0, col0+N) of every tensor in `copies`
+        (each [M, ld]): nslq_bitlinear_forward_cols."""
+        _cuda2d(x, "x")
+        M, ld = x.shape[0], copies[0].shape[1]
+        arr = (C.c_void_p * len(copies))(*[t.data_ptr() for t in copies])
+        ws = workspace if workspace is not None else self.gathered_workspace(M)
+        check(lib().nslq_bitlinear_forward_cols(self._h, _ptr(x), _tag(x.dtype), M, arr, len(copies), ld, col0,
+                                                _tag(copies[0].dtype), _ptr(bias), _ptr(ws), ws.numel(), _stream()))
+
     def forward_quantized_cols(self, qa, copies, col0, bias=None):
         """Writes the [M, N] result as columns [col0, col0+N) of every tensor in `copies`
         (each [M, ld], same ld and dtype): nslq_bitlinear_forward_quantized_cols."""

@@ -106,6 +106,10 @@ class Comm:
         check(lib().nslq_peer_allgather_cols(self._h, _ptr(y_local), _tag(y_local.dtype), M, n, _ptr(y_full), _stream()))
         return y_full
 
+    def push_cols_async(self, y_full, n_local):
+        """Copy-engine form: this rank's column block of y_full ([M, world*n_local], shared) -> every peer."""
+        check(lib().nslq_peer_push_cols_async(self._h, _ptr(y_full), _tag(y_full.dtype), y_full.shape[0], n_local, _stream()))
+
     def status(self):
         v = C.c_int()
         check(lib().nslq_shard_status(self._h, C.byref(v)))
