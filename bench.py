@@ -697,6 +697,67 @@ def run_decoder(torch, batch, peaks, prompt=512, steps=256, warm=8):
     return out
 
 
+# ----------------------------------------------------------------------------- sharded decoder workload
+def run_sharded_decoder(torch, comm, dist, peaks, batch=256, context=2048, n_layers=4, reps=10):
+    """configs[4]: 7B-class ternary decoder, batch 256 decode at context 2048, weights column-sharded over
+    the ranks.  n_layers distinct layers are built and timed (all 32 have the same shapes; the whole model's
+    KV cache is 275 GB); tok/s is batch / (32 x time per layer)."""
+    from nsl_b200 import ops, sharded_decoder
+    m = sharded_decoder.ShardedDecodeLayers(comm, batch, context, n_layers)
+    cfg = m.cfg
+
+    def graph_us(fn, per=1):
+        for _ in range(2):
+            fn()
+        g = capture(torch, fn)
+        g.replay()
+        ms = timed(torch, lambda i: g.replay(), reps, dist)
+        return ms * 1e3 / reps / per
+
+    layer_us = graph_us(m.step, n_layers)
+    # the pieces, each over the n_layers distinct layers (weights and caches larger than L2 in total)
+    x = m.x
+    qa_h = ops.rmsnorm_act_quant_i8(x, m.layers[0]["n1"], cfg.eps, plain=False, perm=True)
+    q0, k0, v0 = m.qkv(m.layers[0], qa_h)
+    a0 = m.attention(m.layers[0], q0, k0, v0)
+    qa_f = ops.act_quant_i8(m.h_full, plain=False, perm=True)
+    g0 = m.layers[0]["gate"].forward_quantized(qa_h, out_dtype=torch.bfloat16)
+    parts = {
+        "rmsnorm_quant": graph_us(lambda: [ops.rmsnorm_act_quant_i8(x, L["n1"], cfg.eps, plain=False, perm=True) for L in m.layers], n_layers),
+        "qkv_linears": graph_us(lambda: [m.qkv(L, qa_h) for L in m.layers], n_layers),
+        "attention": graph_us(lambda: [m.attention(L, q0, k0, v0) for L in m.layers], n_layers),
+        "attn_out_gather": graph_us(lambda: [m.gather_act(a0, m.a_full) for _ in m.layers], n_layers),
+        "o_linear_local": graph_us(lambda: [L["o"].forward_quantized(qa_h, out_dtype=torch.bfloat16) for L in m.layers], n_layers),
+        "o_linear_gathered": graph_us(lambda: [m.linear_gathered(L["o"], qa_h, m.o_full) for L in m.layers], n_layers),
+        "gate_up_linears": graph_us(lambda: [(L["gate"].forward_quantized(qa_h, out_dtype=torch.bfloat16),
+                                              L["up"].forward_quantized(qa_h, out_dtype=torch.bfloat16)) for L in m.layers], n_layers),
+        "swiglu_gather": graph_us(lambda: [m.gather_act(g0, m.h_full) for _ in m.layers], n_layers),
+        "down_linear_local": graph_us(lambda: [L["down"].forward_quantized(qa_f, out_dtype=torch.bfloat16) for L in m.layers], n_layers),
+        "down_linear_gathered": graph_us(lambda: [m.linear_gathered(L["down"], qa_f, m.d_full) for L in m.layers], n_layers),
+    }
+    parts = {k: round(v, 2) for k, v in parts.items()}
+    G = comm.world
+    comm_us = parts["attn_out_gather"] + parts["swiglu_gather"] + (parts["o_linear_gathered"] - parts["o_linear_local"]) + \
+        (parts["down_linear_gathered"] - parts["down_linear_local"])
+    kv_floor_us = m.kv_bytes_per_layer / (peaks["hbm_gbs"] * 1e9) * 1e6
+    out = {"workload": "ternary_7b_decoder_b%d_ctx%d_column_sharded_x%d" % (batch, context, G),
+           "decode_tok_s": round(batch / (cfg.layers * layer_us * 1e-6), 1), "us_per_layer": round(layer_us, 1),
+           "layers_timed": n_layers, "layers_model": cfg.layers,
+           "per_layer_us": parts, "communication_us_per_layer": round(comm_us, 1),
+           "exchange_bytes_per_layer_per_rank": int((3 * cfg.hidden + cfg.ffn) * batch * 2 * (G - 1) / G),
+           "kv_read_floor_us_per_layer": round(kv_floor_us, 1),
+           "note": "one CUDA graph per step over the timed layers; q/k/v stay local, attention is head-sharded, four "
+                   "all-gathers per layer (attention output, o_proj output, SiLU(gate)*up, down output) by peer stores + "
+                   "flag barrier; embedding, final norm and lm_head not included; one GPU cannot hold this workload "
+                   "(KV cache 275 GB)"}
+    st = comm.status()
+    if st:
+        out["status"] = st
+    del m
+    torch.cuda.empty_cache()
+    return out
+
+
 # ----------------------------------------------------------------------------- measurement
 def measure(torch, wl, steps, warmup, use_graph, dist, sampler=None, want_e2e=True):
     """value (whole job), the dominant kernel alone, and the host-to-host number of one workload."""
@@ -828,6 +889,14 @@ def run_ours(args):
             torch.cuda.empty_cache()
         line["also"] = also
         line["decoder"] = [run_decoder(torch, b, peaks) for b in (1, 8, 64)]
+    if world > 1 and args.workload == DEFAULT_WORKLOAD and not args.no_also:
+        sd = run_sharded_decoder(torch, comm, dist, peaks)
+        if rank == 0:
+            line["sharded_decoder"] = sd
+    elif world == 1 and rank == 0 and args.workload == DEFAULT_WORKLOAD and not args.no_also:
+        line["sharded_decoder"] = {"workload": "ternary_7b_decoder_b256_ctx2048_column_sharded",
+                                   "unavailable": "needs 2, 4 or 8 GPUs: the KV cache of batch 256 at context 2048 is 275 GB "
+                                                  "(8.6 GB per layer), more than one GPU holds; run with --gpus N"}
     if rank == 0:
         line["device_status"] = status
         print(json.dumps(line))

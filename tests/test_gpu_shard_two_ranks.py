@@ -86,6 +86,24 @@ def _worker(rank, world, port, out_dir):
         tol = 2e-2 if M > 16 else 1e-3          # M > 16: see tests/test_gpu_w4a16.py for the bound of that kernel
         if not np.all(np.abs(got - want) <= tol * np.maximum(np.abs(want), rms)):
             fails.append("w4 M=%d" % M)
+    # two decode layers of a small decoder, column-sharded over the two ranks, against the same layers
+    # unsharded on this GPU (every linear is bit-exact and heads are independent, so the residual
+    # stream must come out bit-equal)
+    from nsl_b200 import sharded_decoder
+
+    class Small:
+        hidden, heads, head_dim, ffn, layers, vocab = 512, 4, 128, 1024, 2, 1000
+        eps, rope_theta = 1e-5, 10000.0
+
+    for batch in (8, 48):
+        sh = sharded_decoder.ShardedDecodeLayers(comm, batch, 60, 2, cfg=Small, seed=3, kv_from_full=True)
+        one = sharded_decoder.ShardedDecodeLayers(sharding.Comm(0, 1), batch, 60, 2, cfg=Small, seed=3, kv_from_full=True)
+        one.x.copy_(sh.x)
+        sh.step()
+        one.step()
+        torch.cuda.synchronize()
+        if not torch.equal(sh.x, one.x):
+            fails.append("sharded decoder layers differ from the unsharded ones (batch %d)" % batch)
     if comm.status() != 0 or ops.device_status() != 0:
         fails.append("status word set")
     with open(os.path.join(out_dir, "rank%d.txt" % rank), "w") as f:
