@@ -51,7 +51,7 @@ NCU_TRAFFIC = {"ternary_gemv_fused_kernel": 6.93e6, "ternary_gemm_kernel": 28.4e
 
 
 def load_peaks():
-    """Measured peaks of this pool (driver-written file), else the stated fallback."""
+    """Measured peaks of the machine (MEASURED_PEAKS.json beside this file), else the stated fallback."""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         with open(p) as f:
@@ -177,7 +177,7 @@ class Workload:
             ach, unit = per_launch / (kernel_ms * 1e-3) / 1e12, self.unit
             peak = peaks["bf16_tflops"] * (2.0 if self.int8 else 1.0)
             src = ("2 x " if self.int8 else "") + peaks["source"] + " bf16 burst" + \
-                  (" (this pool has no measured int8 figure; datasheet int8 dense = 4500)" if self.int8 else "")
+                  (" (no measured int8 figure is available; datasheet int8 dense = 4500)" if self.int8 else "")
         return {"bound": self.bound, "kernel": self.kernel_name, "achieved": round(ach, 1), "peak": round(peak, 1),
                 "unit": unit, "frac": round(ach / peak, 4),
                 "traffic": NCU_TRAFFIC.get(self.kernel_name) if self.world == 1 else None,

@@ -62,7 +62,8 @@ typedef struct NslAwqPackedWeight {
 /*
  * GPU arm of nsl_awq_matmul (crates/nsl-runtime/src/awq.rs:261-310): input [M,K] on the device
  * (f32, fp16 or bf16), packed = NslAwqPackedWeight* (host buffers; uploaded and re-laid out once,
- * cached by pointer).  Null pointers: message on stderr and 0, like the original.
+ * cached by pointer and device).  fp32 input reaches the 16-bit kernels split into three bf16 parts
+ * whose sum is x exactly.  Null pointers: message on stderr and 0, like the original.
  */
 int64_t nsl_awq_matmul_cuda(int64_t input, int64_t packed, int64_t group_size, int64_t out);
 /* GPU arm of nsl_gptq_matmul (crates/nsl-runtime/src/gptq.rs:646-653): same computation. */
@@ -70,20 +71,48 @@ int64_t nsl_gptq_matmul_cuda(int64_t input, int64_t packed, int64_t group_size, 
 
 /*
  * GPU arm of nsl_qtensor_matmul_mixed (crates/nsl-runtime/src/quantize.rs:547-585): x [...,K] on
- * the device @ dequantize(qw [K,N]); every dtype/granularity the original accepts.  Like the
- * original it prints and aborts when qw is not 2-D or the inner dimensions differ.
+ * the device @ dequantize(qw [K,N]); every dtype/granularity the original accepts.  INT4 weights
+ * quantised per tensor, per channel along axis 1 or per group along axis 0 (group a multiple of 128,
+ * K a multiple of 64) are re-laid out once and multiplied by the streaming / tensor-core W4A16
+ * kernels; the other forms run a generic kernel.  Like the original it prints and aborts when qw is
+ * not 2-D or the inner dimensions differ.
  */
 int64_t nsl_qtensor_matmul_mixed_cuda(int64_t x, int64_t qw, int64_t out);
 
-/* Drops the device copy cached for a weight (call from nsl_awq_free / nsl_qtensor_free). */
+/* Drops the device copies cached for a weight on every device (call from nsl_awq_free / nsl_qtensor_free). */
 void nsl_quant_forget_cuda(int64_t weight);
+
+/*
+ * The CUDA stream (cudaStream_t as i64) on which the calling THREAD's shim calls launch; 0 = the
+ * legacy default stream, which is also the initial setting.  NSL launches on a per-thread compute
+ * stream (crates/nsl-runtime/src/cuda/mod.rs:1931-1940): the runtime passes that stream here once.
+ */
+void nsl_quant_set_stream_cuda(int64_t stream);
+
+/*
+ * Sizes the calling thread's device scratch (quantised activations of nsl_bitlinear_forward beyond
+ * the built-in 512 KiB area, split rows of fp32 activations for the W4 kernels) on the current
+ * device to at least `bytes`, so that later forward calls allocate nothing.  Without it the scratch
+ * grows on first need (cudaMalloc inside that one call).  Returns `bytes`, or 0 on failure.
+ */
+int64_t nsl_quant_reserve_cuda(int64_t bytes);
+
+/*
+ * GPU arm of nsl_awq_pre_scale_weight (crates/nsl-runtime/src/awq.rs:330-383): out[r,c] =
+ * weight[r,c] * scales[c]^alpha in f32.  weight and out: f32 [K,N] on the device; scales: HOST
+ * pointer to scales_len floats, as in the original (0 or a length other than N = plain copy).  The
+ * powers are taken on the host with the same libm powf, so the result is the original's bit for bit.
+ */
+int64_t nsl_awq_pre_scale_weight_cuda(int64_t weight, int64_t scales, int64_t scales_len, double alpha, int64_t out);
 
 /*
  * BitLinear: NSL has no runtime entry point for it (crates/nsl-codegen/tests/bitnet_logit_match.rs:44-52),
  * so this trio is new.  pack: `packed_bytes` = LoadedTernaryWeight.packed_bytes in HOST memory
  * ([out_dim][hidden_dim/4], crates/nsl-codegen/src/bitnet/loader.rs:47-56), uploaded once; returns a
- * handle or 0.  forward: x [M,hidden] on the device (f32/fp16/bf16), out [M,out_dim] on the device
- * (f32/fp16/bf16); returns out or 0.
+ * handle or 0 (0 also for bytes that hold the reserved code 0b11, which NSL's try_unpack_byte rejects:
+ * crates/nsl-codegen/src/bitnet/pack.rs:60-67).  forward: x [M,hidden] on the device (f32/fp16/bf16),
+ * out [M,out_dim] on the device (f32/fp16/bf16); returns out or 0.  Decode-sized calls use the
+ * library's built-in scratch area; larger ones the thread's scratch (nsl_quant_reserve_cuda).
  */
 int64_t nsl_bitlinear_pack(int64_t packed_bytes, int64_t out_dim, int64_t hidden_dim, double weight_scale);
 int64_t nsl_bitlinear_forward(int64_t handle, int64_t x, int64_t out);

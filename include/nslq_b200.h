@@ -49,10 +49,14 @@ extern "C" {
 int         nslq_version(void);
 const char *nslq_last_error(void);
 
-/* Every wait inside the kernels (mbarrier phases of the tensor-core GEMM) is
- * bounded in time; a kernel whose wait expires records a nonzero code and ends
- * normally instead of spinning.  This reads that word of the current device into
- * *status (0 = no wait ever expired) and clears it.  Synchronises the device. */
+/* Every wait inside the kernels (mbarrier phases of the tensor-core kernels, the
+ * landing of a weight slab) is bounded; a kernel whose wait expires records a
+ * nonzero code and ends normally instead of spinning.  nslq_decode_attention
+ * records 0x901 when it found its position outside [0, max_ctx) and did nothing.
+ * This reads those words of the current device into *status (0 = nothing
+ * happened) and clears them.  The reads are ordinary device-to-host copies on
+ * the legacy default stream: they wait for work issued before them on blocking
+ * streams; work on non-blocking streams must be synchronised by the caller. */
 int nslq_device_status(int *status);
 
 /* Kernels are launched with the programmatic-dependent-launch attribute, so that
@@ -106,8 +110,8 @@ int nslq_rmsnorm_act_quant_i8(const void *x, int x_dtype, const float *weight, d
 
 /*
  * SiLU(gate) * up fused in front of the quantisation of the down projection's input (SwiGLU FFN of
- * the BitNet decoder, gate/up/down in stdlib-level model code; the survey of the reference lists it
- * with the RMSNorm prologue as the linear's fused neighbours):
+ * the BitNet decoder; gate, up and down live in stdlib-level model code of NSL, so this is a fused
+ * neighbour of the linear like the RMSNorm prologue, not a replacement of a runtime function):
  *   h[r,k] = (f32)( gate[r,k] / (1 + exp(-gate[r,k])) * up[r,k] )       fp32 arithmetic
  *   then scale/q/rowsum of h exactly as nslq_act_quant_i8.
  * gate, up: [M,K] of the same dtype in {F32, FP16, BF16} with row strides gate_ld, up_ld in elements
@@ -134,8 +138,10 @@ int nslq_swiglu_act_quant_i8(const void *gate, const void *up, int dtype, int64_
  *   cos_table, sin_table  f32 [max_ctx, D/2]
  *   pos    device pointer to the int64 position (read by the kernel, so a CUDA graph can advance it)
  *   out    bf16 [B,H,D]
- * D % 4 == 0, D <= 128, H % Hkv == 0, max_ctx % 4 == 0.  fp32 arithmetic; a position outside
- * [0, max_ctx) makes the kernel do nothing.
+ * D % 4 == 0, D <= 128, H % Hkv == 0, max_ctx % 4 == 0.  fp32 arithmetic.  A position outside
+ * [0, max_ctx) makes the kernel do nothing (out and the caches keep their bytes) and record
+ * 0x901 in the status word nslq_device_status reads: a replayed decode loop must be stopped by
+ * its host before the cache is full.
  */
 int nslq_decode_attention(const void *q, const void *k_new, const void *v_new,
                           int64_t q_batch_stride, int64_t k_batch_stride, int64_t v_batch_stride,
@@ -162,6 +168,16 @@ typedef struct nslq_bitlinear nslq_bitlinear_t;
 int  nslq_bitlinear_create(const uint8_t *packed, int64_t N, int64_t K, float weight_scale,
                            nslq_bitlinear_t **out);
 void nslq_bitlinear_destroy(nslq_bitlinear_t *w);
+
+/*
+ * NSL's packed representation rejects the reserved code 0b11 (try_unpack_byte,
+ * crates/nsl-codegen/src/bitnet/pack.rs:60-67; KAT bytes 0xFF and 0xC0).  The kernels do not look:
+ * they would multiply such a field as +2.  This pass counts the bytes of the weight that hold it
+ * (one reduction kernel, then a synchronisation of `stream`), stores the count in *invalid_bytes
+ * (may be NULL) and returns NSLQ_ERR_ARG when it is not zero.  Call it once after
+ * nslq_bitlinear_create for weights of unknown origin.
+ */
+int nslq_bitlinear_validate(const nslq_bitlinear_t *w, int64_t *invalid_bytes, void *stream);
 
 /* Bytes of device scratch nslq_bitlinear_forward needs for M tokens of width K
  * (quantised activations, scales, row sums). */
@@ -209,13 +225,17 @@ int nslq_bitlinear_forward_quantized(const nslq_bitlinear_t *w, const int8_t *q_
  * for.  The scratch (quantised activations, scales, row sums) lives instead in a
  * fixed area of nslq_noalloc_scratch_bytes() = 512 KiB inside the library's device
  * image -- every GPU that loads the library carries it until the process ends --
- * and this call allocates nothing, on the host or the device.
+ * and the call itself requests no memory, on the host or the device (no cudaMalloc,
+ * cudaFree or allocating library routine).
  *
  *  - Sizes: nslq_bitlinear_workspace_bytes(M, K) must fit the area (e.g. 16 tokens
  *    of width 16384, or 128 of width 3200); larger requests return
  *    NSLQ_ERR_WORKSPACE and say so.  No bias / residual / accumulator outputs.
  *  - The first call on each device looks up the area's device address (with that
- *    device current).  Make that first call before any stream capture begins.
+ *    device current).  With CUDA's lazy module loading that look-up can be the moment
+ *    the driver places the library's image -- its 512 KiB included -- on the device,
+ *    so it is the one call that may take device memory and time.  Make that first
+ *    call during set-up, before any stream capture begins.
  *  - All calls on a device share the one area, and it keeps the previous call's
  *    bytes.  Nothing needs clearing (each call overwrites what it reads), but two
  *    calls whose kernels can overlap on the GPU -- different streams, or different
@@ -254,6 +274,18 @@ int nslq_w4a16_create_nk(const uint8_t *codes, const void *scales, int scale_dty
  */
 int nslq_w4a16_create_awq_kn(const uint8_t *data, const double *scales, const double *zeros,
                              int64_t K, int64_t N, int64_t group_size, nslq_w4a16_t **out);
+/*
+ * Weight stored as an NSL QuantizedTensor of shape [K,N] -- the orientation nsl_qtensor_matmul_mixed
+ * requires (crates/nsl-runtime/src/quantize.rs:547-573) -- INT4, device pointers: nibble index k*N+n
+ * (low nibble = even index), scales f32 and zero points u8 indexed as the reference indexes them
+ * (quantize.rs:366-417).  Accepted: per tensor; per channel along axis 1 (one scale per column n);
+ * per group along axis 0 (one scale per run of `group_size` rows k, shared by every column -- what
+ * `per_group` means for a [K,N] tensor in the reference).  Re-laid out once on the GPU into the
+ * [N,K] streaming order; nothing is borrowed.  Other granularities: NSLQ_ERR_UNSUPPORTED.
+ */
+int nslq_w4a16_create_qtensor_kn(const uint8_t *data, const float *scale, const uint8_t *zero_point,
+                                 int64_t K, int64_t N, int granularity, int gran_axis, int64_t group_size,
+                                 nslq_w4a16_t **out);
 void nslq_w4a16_destroy(nslq_w4a16_t *w);
 
 /*
@@ -265,6 +297,18 @@ void nslq_w4a16_destroy(nslq_w4a16_t *w);
  */
 int nslq_w4a16_forward(const nslq_w4a16_t *w, const void *x, int x_dtype, int64_t M,
                        void *y, int y_dtype, void *stream);
+
+/*
+ * The same product for fp32 activations (NSL's default dtype for GPU tensors,
+ * crates/nsl-runtime/src/cuda/mod.rs:395-551) on the 16-bit kernels, without rounding x: each
+ * element is split into three bf16 parts whose sum is x exactly, the kernels run on the 3M
+ * stacked rows (the weights are still streamed once) and the three parts of the result are
+ * added in fp32.  scratch: device memory of
+ * nslq_w4a16_f32x_scratch_bytes(w, M), 256-byte aligned.
+ */
+int64_t nslq_w4a16_f32x_scratch_bytes(const nslq_w4a16_t *w, int64_t M);
+int nslq_w4a16_forward_f32x(const nslq_w4a16_t *w, const float *x, int64_t M, void *y, int y_dtype,
+                            void *scratch, int64_t scratch_bytes, void *stream);
 
 /* ========================================================================== */
 /* Pack-at-load: the reference's weight quantisers, on the GPU                 */

@@ -22,6 +22,7 @@ SIGNATURES = {
     "nslq_rmsnorm_act_quant_i8": (i32, [vp, i32, vp, f64, i64, i64, vp, vp, vp, vp, vp, vp]),
     "nslq_bitlinear_create": (i32, [vp, i64, i64, f32, C.POINTER(vp)]),
     "nslq_bitlinear_destroy": (None, [vp]),
+    "nslq_bitlinear_validate": (i32, [vp, C.POINTER(i64), vp]),
     "nslq_bitlinear_workspace_bytes": (i64, [i64, i64]),
     "nslq_bitlinear_forward": (i32, [vp, vp, i32, i64, vp, i32, vp, vp, vp, vp, i64, vp]),
     "nslq_bitlinear_forward_quantized": (i32, [vp, vp, vp, vp, i64, vp, i32, vp, vp, vp, vp]),
@@ -29,7 +30,10 @@ SIGNATURES = {
     "nslq_noalloc_scratch_bytes": (i64, []),
     "nslq_w4a16_create_nk": (i32, [vp, vp, i32, vp, i32, i64, i64, i64, C.POINTER(vp)]),
     "nslq_w4a16_create_awq_kn": (i32, [vp, vp, vp, i64, i64, i64, C.POINTER(vp)]),
+    "nslq_w4a16_create_qtensor_kn": (i32, [vp, vp, vp, i64, i64, i32, i32, i64, C.POINTER(vp)]),
     "nslq_w4a16_destroy": (None, [vp]),
+    "nslq_w4a16_f32x_scratch_bytes": (i64, [vp, i64]),
+    "nslq_w4a16_forward_f32x": (i32, [vp, vp, i64, vp, i32, vp, i64, vp]),
     "nslq_w4a16_forward": (i32, [vp, vp, i32, i64, vp, i32, vp]),
     "nslq_ternary_quantize_pack": (i32, [vp, i32, i64, vp, vp, vp]),
     "nslq_int4_quantize_nk": (i32, [vp, i32, i64, i64, i64, vp, vp, vp, vp]),
@@ -60,6 +64,9 @@ SHIM_SIGNATURES = {
     "nsl_gptq_matmul_cuda": (i64, [i64, i64, i64, i64, i64]),
     "nsl_qtensor_matmul_mixed_cuda": (i64, [i64, i64, i64]),
     "nsl_quant_forget_cuda": (None, [i64]),
+    "nsl_quant_set_stream_cuda": (None, [i64]),
+    "nsl_quant_reserve_cuda": (i64, [i64]),
+    "nsl_awq_pre_scale_weight_cuda": (i64, [i64, i64, i64, C.c_double, i64]),
     "nsl_bitlinear_pack": (i64, [i64, i64, i64, C.c_double]),
     "nsl_bitlinear_forward": (i64, [i64, i64, i64]),
     "nsl_bitlinear_free": (None, [i64]),

@@ -53,6 +53,7 @@ int ternary_decode_fused_dispatch(const uint8_t *, const void *, int, int, int64
                                   const float *, const float *, cudaStream_t);
 int ternary_decode_status(int *);
 int ternary_gemv_status(int *);
+int decode_attention_status(int *);
 bool ternary_gemm_supported(const void *, const void *, int64_t, int64_t, int64_t);
 int ternary_gemm_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int64_t, int64_t,
                           int64_t, float, void *, int, int32_t *, const float *, const float *, const OutSpec *, cudaStream_t);
@@ -169,6 +170,58 @@ __global__ void awq_tables_kernel(const double *__restrict__ scales, const doubl
     zc_out[i] = (float)(-z / s);
 }
 
+// QuantizedTensor [K,N] (index rules of crates/nsl-runtime/src/quantize.rs:366-417, :436-537) -> the
+// [N][G] tables of the streaming kernels, for the granularities whose scale index does not depend on
+// k inside a group of `gs` consecutive k: per tensor (one scale), per channel along axis 1 (scale[n]),
+// per group along axis 0 (scale[k / group], shared by every n).
+__global__ void qtensor_tables_kernel(const float *__restrict__ scale, const uint8_t *__restrict__ zp, int gran, int64_t N,
+                                      int G, float *__restrict__ scale_out, float *__restrict__ zc_out)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N * G) return;
+    const int64_t n = i / G;
+    const int g = (int)(i % G);
+    const int64_t si = gran == 0 ? 0 : (gran == 1 ? n : g);
+    scale_out[i] = scale[si];
+    zc_out[i] = (float)zp[si];
+}
+
+// Counts the bytes of a packed ternary weight that hold the reserved 2-bit code 0b11.
+__global__ void __launch_bounds__(256) count_invalid_codes_kernel(const uint8_t *__restrict__ packed, int64_t nbytes,
+                                                                  unsigned long long *__restrict__ count)
+{
+    unsigned long long bad = 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nbytes; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t b = packed[i];
+        bad += ((b & (b >> 1)) & 0x55u) != 0;              // some field has both bits set
+    }
+    for (int o = 16; o > 0; o >>= 1) bad += __shfl_xor_sync(0xffffffffu, bad, o);
+    if ((threadIdx.x & 31) == 0 && bad) atomicAdd(count, bad);
+}
+
+// fp32 activations for the 16-bit kernels without rounding them: x = hi + mid + lo, three bf16 parts
+// (each remainder is exact in fp32 and is rounded again: 3 x 8 significant bits cover fp32's 24), stacked
+// as rows [0, M) = hi, [M, 2M) = mid, [2M, 3M) = lo; the three parts of the result are added afterwards.
+__global__ void split_f32_bf16_kernel(const float *__restrict__ x, int64_t n, __nv_bfloat16 *__restrict__ out)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = x[i];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(hi);
+    const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+    out[i] = hi;
+    out[n + i] = mid;
+    out[2 * n + i] = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+}
+
+__global__ void add_parts_kernel(const float *__restrict__ yy, int64_t n, void *__restrict__ y, int y_dtype)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    store_out(y, y_dtype, i, (yy[2 * n + i] + yy[n + i]) + yy[i]);
+}
+
 }  // namespace nslq
 
 // ------------------------------------------------------------------ extern "C"
@@ -183,8 +236,8 @@ void nslq_set_dependent_launch(int enable) { g_use_pdl = enable ? 1 : 0; }
 int nslq_device_status(int *status)
 {
     if (!status) return fail(NSLQ_ERR_ARG, "nslq_device_status: null output");
-    if (cudaDeviceSynchronize() != cudaSuccess)
-        return fail(NSLQ_ERR_CUDA, "nslq_device_status: %s", cudaGetErrorString(cudaGetLastError()));
+    // The words live in device memory: reading them waits for the work in front of the read (the
+    // copies below run on the legacy default stream, which orders them behind every blocking stream).
     int a = 0, b = 0, c = 0, d = 0, e = 0;
     int rc = ternary_gemm_status(&a);
     if (rc) return rc;
@@ -192,7 +245,9 @@ int nslq_device_status(int *status)
     if ((rc = ternary_decode_status(&c))) return rc;
     if ((rc = w4a16_decode_status(&d))) return rc;
     if ((rc = ternary_gemv_status(&e))) return rc;
-    *status = a ? a : (b ? b : (c ? c : (d ? d : e)));
+    int f = 0;
+    if ((rc = decode_attention_status(&f))) return rc;
+    *status = a ? a : (b ? b : (c ? c : (d ? d : (e ? e : f))));
     return NSLQ_OK;
 }
 
@@ -238,6 +293,27 @@ int nslq_bitlinear_create(const uint8_t *packed, int64_t N, int64_t K, float wei
 }
 
 void nslq_bitlinear_destroy(nslq_bitlinear_t *w) { free(w); }
+
+int nslq_bitlinear_validate(const nslq_bitlinear_t *w, int64_t *invalid_bytes, void *stream)
+{
+    if (!w) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_validate: null handle");
+    unsigned long long *d = nullptr, h = 0;
+    if (cudaMalloc(&d, sizeof(h)) != cudaSuccess || cudaMemsetAsync(d, 0, sizeof(h), (cudaStream_t)stream) != cudaSuccess) {
+        if (d) cudaFree(d);
+        return fail(NSLQ_ERR_CUDA, "nslq_bitlinear_validate: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+    const int64_t nb = w->N * (w->K / 4);
+    const unsigned blocks = (unsigned)(nb / 256 / 8 + 1 < 1184 ? nb / 256 / 8 + 1 : 1184);
+    count_invalid_codes_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(w->packed, nb, d);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&h, d, sizeof(h), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    cudaFree(d);
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "nslq_bitlinear_validate: %s", cudaGetErrorString(e));
+    if (invalid_bytes) *invalid_bytes = (int64_t)h;
+    if (h) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_validate: %llu packed bytes hold the reserved 2-bit code 0b11 (not a trit)", h);
+    return NSLQ_OK;
+}
 
 // workspace layout: [q_perm or q_plain: M*K, 256-aligned][scale: M f32, 256-aligned][rowsum: M i32]
 int64_t nslq_bitlinear_workspace_bytes(int64_t M, int64_t K)
@@ -393,6 +469,38 @@ int nslq_w4a16_create_awq_kn(const uint8_t *data, const double *scales, const do
     return NSLQ_OK;
 }
 
+int nslq_w4a16_create_qtensor_kn(const uint8_t *data, const float *scale, const uint8_t *zero_point, int64_t K, int64_t N,
+                                 int granularity, int gran_axis, int64_t group_size, nslq_w4a16_t **out)
+{
+    if (!data || !scale || !zero_point || !out) return fail(NSLQ_ERR_ARG, "nslq_w4a16_create_qtensor_kn: null argument");
+    // the forms whose scale index is constant over each run of `gs` consecutive k of a column
+    int64_t gs = 0;
+    if (granularity == 0 || (granularity == 1 && gran_axis == 1)) gs = (K % 128 == 0) ? 128 : K;
+    else if (granularity == 2 && gran_axis == 0) gs = group_size;
+    else return fail(NSLQ_ERR_UNSUPPORTED, "nslq_w4a16_create_qtensor_kn: granularity %d along axis %d has no per-(column, k-group) form", granularity, gran_axis);
+    int rc = w4_check_shape("nslq_w4a16_create_qtensor_kn", N, K, gs);
+    if (rc) return rc;
+    if ((K * N) % 2 != 0) return fail(NSLQ_ERR_SHAPE, "nslq_w4a16_create_qtensor_kn: K*N must be even");
+    nslq_w4a16 *h = (nslq_w4a16 *)calloc(1, sizeof(nslq_w4a16));
+    if (!h) return fail(NSLQ_ERR_ARG, "nslq_w4a16_create_qtensor_kn: out of host memory");
+    h->N = N; h->K = K; h->gs = (int)gs; h->G = (int)((K + gs - 1) / gs); h->zp_integer = 1;
+    if ((rc = w4_alloc_tables(h))) { nslq_w4a16_destroy(h); return rc; }
+    if (cudaMalloc(&h->codes_owned, (size_t)(N * (K / 2))) != cudaSuccess) {
+        nslq_w4a16_destroy(h);
+        return fail(NSLQ_ERR_CUDA, "nslq_w4a16_create_qtensor_kn: cudaMalloc failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+    h->codes = h->codes_owned;
+    const int64_t nb = N * (K / 2);
+    awq_repack_codes_kernel<<<(unsigned)((nb + 255) / 256), 256>>>(data, K, N, h->codes_owned);   // same nibble index: row*N + col
+    if ((rc = check_launch("awq_repack_codes_kernel"))) { nslq_w4a16_destroy(h); return rc; }
+    qtensor_tables_kernel<<<(unsigned)((N * h->G + 255) / 256), 256>>>(scale, zero_point, granularity, N, h->G, h->scale, h->zc);
+    if ((rc = check_launch("qtensor_tables_kernel"))) { nslq_w4a16_destroy(h); return rc; }
+    if ((rc = w4_transpose_tables(h))) { nslq_w4a16_destroy(h); return rc; }
+    if (cudaDeviceSynchronize() != cudaSuccess) { nslq_w4a16_destroy(h); return fail(NSLQ_ERR_CUDA, "nslq_w4a16_create_qtensor_kn: %s", cudaGetErrorString(cudaGetLastError())); }
+    *out = h;
+    return NSLQ_OK;
+}
+
 void nslq_w4a16_destroy(nslq_w4a16_t *w)
 {
     if (!w) return;
@@ -433,6 +541,34 @@ int nslq_w4a16_forward(const nslq_w4a16_t *w, const void *x, int x_dtype, int64_
         return NSLQ_OK;
     }
     return w4a16_scalar_dispatch(w->codes, w->scale, w->zc, w->N, w->K, w->G, w->gs, x, x_dtype, M, y, y_dtype, st);
+}
+
+int64_t nslq_w4a16_f32x_scratch_bytes(const nslq_w4a16_t *w, int64_t M)
+{
+    if (!w || M <= 0) return 0;
+    return align_up(3 * M * w->K * 2, 256) + align_up(3 * M * w->N * 4, 256);
+}
+
+int nslq_w4a16_forward_f32x(const nslq_w4a16_t *w, const float *x, int64_t M, void *y, int y_dtype, void *scratch,
+                            int64_t scratch_bytes, void *stream)
+{
+    if (!w || !x || !y) return fail(NSLQ_ERR_ARG, "nslq_w4a16_forward_f32x: null argument");
+    if (!out_elem_size(y_dtype)) return fail(NSLQ_ERR_ARG, "nslq_w4a16_forward_f32x: y_dtype %d not in {F32,FP16,BF16}", y_dtype);
+    if (M < 0) return fail(NSLQ_ERR_SHAPE, "nslq_w4a16_forward_f32x: M=%lld", (long long)M);
+    if (M == 0) return NSLQ_OK;
+    const int64_t need = nslq_w4a16_f32x_scratch_bytes(w, M);
+    if (!scratch || scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255u))
+        return fail(NSLQ_ERR_WORKSPACE, "nslq_w4a16_forward_f32x: scratch %lld bytes (256-byte aligned), need %lld", (long long)scratch_bytes, (long long)need);
+    cudaStream_t st = (cudaStream_t)stream;
+    __nv_bfloat16 *xs = (__nv_bfloat16 *)scratch;
+    float *yy = (float *)((char *)scratch + align_up(3 * M * w->K * 2, 256));
+    const int64_t nx = M * w->K, ny = M * w->N;
+    split_f32_bf16_kernel<<<(unsigned)((nx + 255) / 256), 256, 0, st>>>(x, nx, xs);
+    int rc = check_launch("split_f32_bf16_kernel");
+    if (rc) return rc;
+    if ((rc = nslq_w4a16_forward(w, xs, NSLQ_DTYPE_BF16, 3 * M, yy, NSLQ_DTYPE_F32, stream))) return rc;
+    add_parts_kernel<<<(unsigned)((ny + 255) / 256), 256, 0, st>>>(yy, ny, y, y_dtype);
+    return check_launch("add_parts_kernel");
 }
 
 int nslq_ternary_quantize_pack(const void *w, int w_dtype, int64_t numel, uint8_t *packed, float *scale, void *stream)

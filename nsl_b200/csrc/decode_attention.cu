@@ -39,6 +39,9 @@ static __device__ __forceinline__ float warp_sum(float v)
     return v;
 }
 
+// 0 = ok; 0x901 = a launch found its position outside [0, max_ctx) and did nothing.
+static __device__ int g_attn_status = 0;
+
 struct AttnParams {
     const __nv_bfloat16 *q, *k_new, *v_new;   // [B,H,D], [B,Hkv,D], [B,Hkv,D]; rows of a sequence contiguous
     int64_t q_bs, k_bs, v_bs;                 // elements between consecutive sequences of q, k_new, v_new
@@ -79,7 +82,12 @@ decode_attention_kernel(const AttnParams p)
         xin[u] = d < 2 * p.D ? __bfloat162float(d < p.D ? qg[d] : kg[d - p.D]) : 0.0f;
     }
     const int pos = (int)*p.pos;
-    if (pos < 0 || pos >= p.max_ctx) return;              // nothing sensible to do; the host checks the range it can see (every CTA of a cluster takes this exit together)
+    if (pos < 0 || pos >= p.max_ctx) {                    // every CTA of a cluster takes this exit together
+        // Nothing sensible to do -- but not silently: a decode loop replayed past the end of its cache would
+        // otherwise keep emitting tokens from stale outputs.  The status word is read by nslq_device_status.
+        if (threadIdx.x == 0) atomicCAS(&g_attn_status, 0, 0x901);
+        return;
+    }
     if (SPLIT > 1) cg::this_cluster().sync();             // every CTA of the cluster runs before anyone writes into rank 0's shared memory
     const int half = p.D >> 1, nl = p.D >> 2;             // lanes that hold four dimensions each
     // this CTA's slice [jb, je) of the n = pos + 1 keys (whole groups of 16; later ranks may be empty)
@@ -333,6 +341,16 @@ int decode_attention_dispatch(const void *q, const void *k_new, const void *v_ne
     }
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "decode_attention_kernel: %s", cudaGetErrorString(e));
     return check_launch("decode_attention_kernel");
+}
+
+int decode_attention_status(int *out)
+{
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int)) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "nslq_device_status: %s", cudaGetErrorString(cudaGetLastError()));
+    if (v != 0) cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int));
+    *out = v;
+    return NSLQ_OK;
 }
 
 }  // namespace nslq

@@ -82,6 +82,7 @@ class BitNetDecoder:
         self.key_index = torch.arange(max_ctx, device="cuda")
         self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
         self.graph = None
+        self.host_pos = 0
         # Sibling projections (q/k/v, gate/up) of a decode step run on side streams: at a few dozen rows
         # one projection occupies 25 to 68 of the 148 SMs, so three of them fit side by side.
         self.side = [torch.cuda.Stream(), torch.cuda.Stream()] if side_streams else []
@@ -149,24 +150,31 @@ class BitNetDecoder:
         last = _rms_norm(x.view(B, T, cfg.hidden)[:, -1], self.final_norm, cfg.eps).to(torch.bfloat16)
         self.tokens.copy_((last @ self.lm_head.t()).argmax(-1))
         self.pos.fill_(T)
+        self.host_pos = T
 
     # ------------------------------------------------------------------ one decode step (graph-capturable)
     def _step(self):
         cfg, B = self.cfg, self.B
         self.fork = bool(self.side)
         x = self.embed[self.tokens].float()                               # [B, h] residual stream, fp32
-        for li, L in enumerate(self.layers):
-            q, k, v = self._norm_lin_shared([L["q"], L["k"], L["v"]], x, L["n1"])
-            # RoPE, cache append and single-query attention: one launch of the library
-            a = ops.decode_attention(q, k, v, self.k_cache[li], self.v_cache[li], self.cos, self.sin, self.pos,
-                                     self.sm_scale)
-            x = self._lin(L["o"], a.reshape(B, cfg.heads * cfg.head_dim), x)
-            g, u = self._norm_lin_shared([L["gate"], L["up"]], x, L["n2"])
-            x = self._swiglu_down(L["down"], g, u, x)
+        for li in range(len(self.layers)):
+            x = self.decode_layer(li, x)
         logits = _rms_norm(x, self.final_norm, cfg.eps).to(torch.bfloat16) @ self.lm_head.t()
         self.tokens.copy_(logits.argmax(-1))
         self.pos.add_(1)
         self.fork = False
+
+    def decode_layer(self, li, x):
+        """One layer of a decode step on the fp32 residual stream x [B, hidden]; appends to layer li's cache
+        at the current position."""
+        cfg, B, L = self.cfg, self.B, self.layers[li]
+        q, k, v = self._norm_lin_shared([L["q"], L["k"], L["v"]], x, L["n1"])
+        # RoPE, cache append and single-query attention: one launch of the library
+        a = ops.decode_attention(q, k, v, self.k_cache[li], self.v_cache[li], self.cos, self.sin, self.pos,
+                                 self.sm_scale)
+        x = self._lin(L["o"], a.reshape(B, cfg.heads * cfg.head_dim), x)
+        g, u = self._norm_lin_shared([L["gate"], L["up"]], x, L["n2"])
+        return self._swiglu_down(L["down"], g, u, x)
 
     def capture(self):
         s = torch.cuda.Stream()
@@ -185,10 +193,16 @@ class BitNetDecoder:
         self.tokens.copy_(keep_tok)
 
     def decode(self, steps):
+        # the position lives on the device (the graph advances it); the host keeps its own count so that a
+        # loop cannot run past the end of the cache, where the attention kernel would do nothing
+        if self.host_pos + steps > self.max_ctx:
+            raise ValueError("decode(%d) from position %d would pass the end of the KV cache (%d rows)"
+                             % (steps, self.host_pos, self.max_ctx))
         if self.graph is None:
             self.capture()
         for _ in range(steps):
             self.graph.replay()
+        self.host_pos += steps
 
     def step_bytes(self, ctx):
         """Algorithmic HBM bytes of one decode step at context length ctx."""

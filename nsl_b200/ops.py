@@ -142,6 +142,16 @@ class BitLinear:
         if h and lib is not None:              # module globals are already gone at interpreter shutdown
             lib().nslq_bitlinear_destroy(h)
 
+    def invalid_bytes(self):
+        """Number of packed bytes that hold the reserved 2-bit code 0b11 (0 for a well-formed weight)."""
+        n = C.c_int64()
+        lib().nslq_bitlinear_validate(self._h, C.byref(n), _stream())
+        return n.value
+
+    def validate(self):
+        """Raises NslqError if the weight holds the reserved code (nslq_bitlinear_validate)."""
+        check(lib().nslq_bitlinear_validate(self._h, None, _stream()))
+
     def workspace(self, M):
         need = int(lib().nslq_bitlinear_workspace_bytes(M, self.K))
         if self._ws is None or self._ws.numel() < need:
@@ -306,6 +316,7 @@ def awq_quantize_kn(w, group_size):
 
 def device_status():
     """Nonzero if a bounded wait inside a kernel expired since the last call (then cleared)."""
+    torch.cuda.synchronize()      # torch's side streams are non-blocking: the library's read does not wait for them
     v = C.c_int()
     check(lib().nslq_device_status(C.byref(v)))
     return v.value

@@ -3,10 +3,12 @@
 Some callers of this library cannot hand it device memory: NSL's runtime owns every
 device allocation through its caching allocator, a decode loop cannot stall on
 cudaMalloc, a late-loaded plug-in may find the device already reserved.  For them the
-library keeps a fixed 512 KiB scratch area in its own device image.  This test checks
-that the entry point gives exactly what nslq_bitlinear_forward gives (bit-equal
-outputs; the other BitLinear tests already pin that one to the CPU checker), on two
-calls in a row that share the area, and that oversized requests are refused in words.
+library keeps a fixed 512 KiB scratch area in its own device image.  These tests check
+that the entry point gives exactly what nslq_bitlinear_forward gives and what the CPU
+checker gives (bit-equal), on calls in a row that share the area -- including calls
+issued back to back on one stream with no synchronisation between them, with and
+without dependent launch -- that a call leaves the free device memory as it found it,
+and that oversized requests are refused in words.
 
 The file name sorts last on purpose: a run that stops at the first failure has
 already run every other test by the time it gets here.
@@ -48,6 +50,41 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row():
     layer.forward_noalloc(x1, got1)
     torch.cuda.synchronize()
     assert torch.equal(got, want) and torch.equal(got1, want1)
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("pdl", [1, 0])
+def test_back_to_back_calls_share_the_area_and_match_the_cpu_checker(oracle, pdl):
+    """Three calls that all use the built-in area (tensor-core path at M = 96 and 40, quantise + decode
+    kernel at M = 8), different inputs, separate outputs, one stream, no synchronisation in between:
+    each must still equal the workspace entry point and the CPU checker; free device memory must not
+    move across the calls."""
+    from nsl_b200 import lib, ops
+    rng = np.random.default_rng(99)
+    N, K, ws = 272, 3200, 0.031
+    c = rng.integers(0, 3, size=(N, K // 4, 4), dtype=np.uint8)
+    packed = ((c[..., 0] << 6) | (c[..., 1] << 4) | (c[..., 2] << 2) | c[..., 3]).astype(np.uint8)
+    layer = ops.BitLinear(torch.from_numpy(packed).cuda(), ws)
+    xs = [rng.standard_normal((M, K)).astype(np.float32) for M in (96, 40, 8)]
+    xd = [torch.from_numpy(x).cuda() for x in xs]
+    outs = [torch.full((x.shape[0], N), float("nan"), device="cuda") for x in xs]
+    wants = [layer.forward(x) for x in xd]
+    lib().nslq_set_dependent_launch(pdl)
+    try:
+        layer.forward_noalloc(xd[2], outs[2])                    # first use on this device (address look-up) outside the measured window
+        torch.cuda.synchronize()
+        free0 = torch.cuda.mem_get_info()[0]
+        for x, o in zip(xd, outs):
+            layer.forward_noalloc(x, o)                          # no synchronisation between the three
+        torch.cuda.synchronize()
+        free1 = torch.cuda.mem_get_info()[0]
+    finally:
+        lib().nslq_set_dependent_launch(1)
+    assert free1 == free0, "a no-allocation call changed the free device memory"
+    for x, o, w in zip(xs, outs, wants):
+        assert torch.equal(o, w), "M=%d differs from the workspace entry point" % x.shape[0]
+        _, _, _, y_ref = oracle.bitlinear_forward_packed(x, packed, N, ws, threads=4)
+        assert np.array_equal(o.cpu().numpy().view(np.uint32), y_ref.view(np.uint32)), "M=%d differs from the CPU checker" % x.shape[0]
     assert ops.device_status() == 0
 
 
