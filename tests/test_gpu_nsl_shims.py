@@ -163,7 +163,7 @@ def test_qtensor_int4_reaches_the_streaming_kernels(lib, oracle, gran, axis, gs,
     lib.nsl_quant_set_stream_cuda(st.cuda_stream)
     assert lib.nsl_quant_reserve_cuda(1 << 20) == 1 << 20
     try:
-        for M in (1, 3, 5):
+        for M in (1, 3, 12, 40):                 # 3 M stacked rows for fp32 x: decode kernel up to M = 5, tensor-core GEMM beyond
             x = rng.standard_normal((M, K)).astype(np.float32)
             xt = torch.from_numpy(x).cuda().to(xdt)
             yt = torch.empty(M, N, device="cuda")

@@ -25,10 +25,9 @@ def close(got, want, rel):
     return bool(np.all(np.abs(got - want) <= tol)), float(np.max(np.abs(got - want) / (np.abs(want) + 1e-9)))
 
 
-def close_rms(got, want, rel, floor=2.0):
-    """|err| <= rel*|want| + floor*rel*rms(row): a relative bound with the row's own scale as the
-    floor for outputs near zero.  Rounding every weight to bf16 (2^-9 relative each) alone moves
-    an output by up to ~1.4e-2 of the row rms on these inputs, hence floor = 2 at rel = 1e-2."""
+def close_rms(got, want, rel, floor=1.0):
+    """|err| <= rel*|want| + floor*rel*rms(row): the stated relative bound, with the row's own
+    scale as the floor for outputs near zero (an output is a sum of K terms of mixed sign)."""
     got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
     rms = np.sqrt((want ** 2).mean(axis=-1, keepdims=True))
     err = np.abs(got - want)
@@ -45,12 +44,8 @@ def test_streaming_kernel_bf16(ops, oracle, M, N, K, gs):
     y32 = host(w.forward(dev(x).to(torch.bfloat16), out_dtype=torch.float32))
     ybf = host(w.forward(dev(x).to(torch.bfloat16)))
     want = oracle.w4a16_matmul_nk(x, codes, scale, zp, N, K, gs, threads=4)
-    if M > 16:      # tensor-core path: weights pass through bf16, so the bf16 tolerance applies
-        ok, worst = close_rms(y32, want, 1e-2)
-        assert ok, worst
-    else:
-        ok, worst = close(y32, want, 1e-3)
-        assert ok, worst
+    ok, worst = close(y32, want, 1e-3)              # every M: the codes reach the tensor core exactly
+    assert ok, worst
     ok, worst = close_rms(ybf, want, 1e-2)
     assert ok, worst
 
@@ -109,10 +104,13 @@ def test_awq_layout(ops, oracle):
 
 
 @pytest.mark.parametrize("M,N,K,gs", [(17, 192, 128, 128), (64, 256, 256, 64), (130, 200, 512, 128),
-                                      (256, 1000, 1024, 128), (300, 448, 4096, 128), (40, 8, 64, 64)])
+                                      (256, 1000, 1024, 128), (300, 448, 4096, 128), (40, 8, 64, 64),
+                                      (129, 130, 1024, 256), (1000, 384, 2048, 512)])
 def test_tensor_core_gemm(ops, oracle, M, N, K, gs):
-    """M > 16 with bf16 activations runs the tcgen05 kernel: weights are dequantised to bf16
-    ((q-zp)*scale rounded once), products accumulate in fp32.  Tolerance: rel 1e-2 (bf16)."""
+    """M > 16 with 16-bit activations runs the tcgen05 GEMM: integer codes on the tensor core, a fresh
+    fp32 accumulator per 128 k, scale and zero point applied in fp32.  fp32 outputs within rel 1e-3
+    of the f64 reference (measured: a few 1e-6 of the row rms), bf16 outputs within rel 1e-2.
+    Shapes with groups that are not multiples of 128 run the decode kernels in chunks of 16 tokens."""
     rng = np.random.default_rng(M + N + K)
     q, codes, scale, zp = make_w4_case(rng, N, K, gs)
     x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
@@ -122,14 +120,18 @@ def test_tensor_core_gemm(ops, oracle, M, N, K, gs):
     ybf = host(w.forward(xd))
     assert ops.device_status() == 0
     want = oracle.w4a16_matmul_nk(x, codes, scale, zp, N, K, gs, threads=8)
-    ok, worst = close_rms(y32, want, 1e-2)
+    ok, worst = close_rms(y32, want, 1e-3)
     assert ok, worst
     ok, worst = close_rms(ybf, want, 1e-2)
     assert ok, worst
-    # against the exact product with the same bf16-rounded weights the kernel builds: fp32 accumulation only
-    wdeq = bf16_round(((q.astype(np.float32) - np.repeat(zp, gs, 1).astype(np.float32)) * np.repeat(scale, gs, 1)))
-    exact = x.astype(np.float64) @ wdeq.astype(np.float64).T
-    ok, worst = close_rms(y32, exact, 1e-4, floor=1.0)
+    # only fp32 accumulation separates the kernel from the reference: well inside a tenth of the bound
+    ok, worst = close_rms(y32, want, 1e-4)
+    assert ok, worst
+    # fp16 activations take the same path (1024 + q instead of 128 + q)
+    xh = x.astype(np.float16)
+    yh = host(w.forward(dev(xh), out_dtype=torch.float32))
+    wanth = oracle.w4a16_matmul_nk(xh.astype(np.float32), codes, scale, zp, N, K, gs, threads=8)
+    ok, worst = close_rms(yh, wanth, 1e-3)
     assert ok, worst
 
 
@@ -145,6 +147,9 @@ def test_tensor_core_gemm_workload_size(ops, oracle):
     rows = np.array([0, 1, 127, 128, 200, 255])
     want = oracle.w4a16_matmul_nk(x[rows], codes, scale, zp, N, K, gs, threads=8)
     ok, worst = close_rms(y[rows], want, 1e-2)
+    assert ok, worst
+    y32 = host(w.forward(dev(x).to(torch.bfloat16), out_dtype=torch.float32))
+    ok, worst = close_rms(y32[rows], want, 1e-3)
     assert ok, worst
     # every row equals the same row run through the streaming kernel within the same tolerance
     y_rows = host(torch.cat([w.forward(dev(x[i:i + 16]).to(torch.bfloat16)) for i in range(0, M, 16)]))
