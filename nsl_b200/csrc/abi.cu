@@ -69,7 +69,7 @@ int w4a16_decode_dispatch(const uint8_t *, const float *, const float *, int64_t
                           int, void *, int, cudaStream_t);   // tables transposed, [G][N]
 int w4a16_decode_status(int *);
 bool w4a16_gemm_supported(const void *, const void *, int, int64_t, int64_t, int64_t, int64_t);
-int w4a16_gemm_dispatch(const uint8_t *, const float *, const float *, int64_t, int64_t, int, int, const void *, int, int64_t,
+int w4a16_gemm_dispatch(const uint8_t *, const float *, const float *, int, int64_t, int64_t, int, int, const void *, int, int64_t,
                         void *, int, cudaStream_t);   // tables transposed, [G][N]
 
 int ternary_quantize_pack_dispatch(const void *, int, int64_t, uint8_t *, float *, cudaStream_t);
@@ -522,7 +522,7 @@ int nslq_w4a16_forward(const nslq_w4a16_t *w, const void *x, int x_dtype, int64_
     if (M == 0) return NSLQ_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (M > 16 && w4a16_gemm_supported(w->codes, x, x_dtype, M, w->N, w->K, w->gs))
-        return w4a16_gemm_dispatch(w->codes, w->scale_t, w->zc_t, w->N, w->K, w->G, w->gs, x, x_dtype, M, y, y_dtype, st);
+        return w4a16_gemm_dispatch(w->codes, w->scale_t, w->zc_t, w->zp_integer, w->N, w->K, w->G, w->gs, x, x_dtype, M, y, y_dtype, st);
     if (w4a16_gemv_supported(w->codes, x, x_dtype, w->K, w->gs)) {
         for (int64_t m0 = 0; m0 < M; m0 += 16) {
             const int mc = (int)((M - m0) < 16 ? (M - m0) : 16);

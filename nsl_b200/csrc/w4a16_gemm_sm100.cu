@@ -42,28 +42,32 @@ namespace w4gemm {
 using namespace sm100;
 
 constexpr int BW = 128;                  // weight rows per tile = MMA M = TMEM lanes
-constexpr int BT = 128;                  // tokens per tile = MMA N
 constexpr int BKK = 128;                 // k per pipeline step (one accumulator block)
 constexpr int THREADS = 576;             // 18 warps: 0 TMA, 1 MMA, 2-9 unpack, 10-17 epilogue
-constexpr int X_SUB = BT * 128;          // one 128-byte-swizzled sub-tile: 128 tokens x 64 k of 16-bit values
-constexpr int X_BYTES = 2 * X_SUB;       // 32 KiB
 constexpr int P_ROW = BKK / 2;           // packed bytes per weight row and step
 constexpr int P_BYTES = BW * P_ROW;      // 8 KiB
-constexpr int T_BYTES = X_BYTES + P_BYTES;   // one copy stage, a multiple of 1024
-constexpr int TS = 5;                    // copy stages
 constexpr int A_COLS = BKK / 2;          // TMEM columns of one operand stage (two 16-bit values per column)
 constexpr int AS = 4;                    // operand stages: columns 256..511
-constexpr int NB = 2;                    // accumulator buffers of BT columns: 0..255
+constexpr int NB = 2;                    // accumulator buffers, at columns 0 and 128
 constexpr int ND = 8;                    // ring of "step retired" barriers
 constexpr int XR = 8;                    // ring of per-step token sums: the unpack warps run at most AS + NB steps ahead of the epilogue
 constexpr int EG = 16;                   // tokens per tcgen05.ld of the epilogue
-constexpr int HALF_T = BT / 2;           // tokens per epilogue warp
-constexpr int XSUM_BYTES = XR * BT * 4;
 constexpr int BAR_BYTES = 512;
-constexpr int SMEM = TS * T_BYTES + XSUM_BYTES + BAR_BYTES + 1024;
-static_assert(SMEM <= 232448, "over the 227 KiB a CTA may use");
-static_assert(TS < ND && AS < ND && XR >= AS + NB + 1, "ring depths");
-static_assert(NB * BT + AS * A_COLS == 512, "tensor memory columns");
+static_assert(AS < ND && XR >= AS + NB + 1, "ring depths");
+
+// BT = tokens per tile = MMA N: 128, or 96 / 64 where that wastes fewer SM-rounds on the shape.
+template <int BT> struct Cfg {
+    static_assert(BT == 64 || BT == 96 || BT == 128, "token tile");
+    static constexpr int X_SUB = BT * 128;            // one 128-byte-swizzled sub-tile: BT tokens x 64 k of 16-bit values
+    static constexpr int X_BYTES = 2 * X_SUB;
+    static constexpr int T_BYTES = X_BYTES + P_BYTES; // one copy stage, a multiple of 1024
+    static constexpr int TS = (BT == 128) ? 5 : (BT == 96 ? 6 : 7);   // copy stages
+    static constexpr int HALF_T = BT / 2;             // tokens per epilogue warp
+    static constexpr int XSUM_BYTES = XR * BT * 4;
+    static constexpr int SMEM = TS * T_BYTES + XSUM_BYTES + BAR_BYTES + 1024;
+    static_assert(SMEM <= 232448, "over the 227 KiB a CTA may use");
+    static_assert(TS < ND && T_BYTES % 1024 == 0 && HALF_T % EG == 0, "stage geometry");
+};
 
 struct Params {
     const float *scale_t;    // [G][N] (transposed table: a lane per row reads coalesced)
@@ -74,7 +78,7 @@ struct Params {
     int tiles_t, tiles_w, nkb;   // token tiles, weight-row tiles, blocks of 128 k
 };
 
-template <bool BF16> static __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t accumulate)
+template <bool BF16, int BT> static __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t accumulate)
 {
     constexpr uint32_t fmt = BF16 ? 1u : 0u;
     constexpr uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BT >> 3) << 17) | ((uint32_t)(BW >> 4) << 24);
@@ -111,10 +115,16 @@ template <> struct OutStore<__half> {
 };
 
 // ---------------------------------------------------------------- kernel
-template <typename XT>
+// ZPI: the zero points are whole numbers (QuantizedTensor form).  The unpack warps then subtract
+// (MAGIC + zp) from (MAGIC + q) with one packed 16-bit subtraction -- exact, both are integers below
+// 2^8 (bf16) or 2^11 (fp16) -- so the tensor core multiplies q - zp itself: no token sums, one FMA per
+// value in the epilogue.  Fractional zero points (AWQ's float zeros) keep the form with the sums.
+template <typename XT, bool ZPI, int BT>
 __global__ void __launch_bounds__(THREADS, 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const Params p)
 {
+    using C = Cfg<BT>;
+    constexpr int X_SUB = C::X_SUB, X_BYTES = C::X_BYTES, T_BYTES = C::T_BYTES, TS = C::TS, HALF_T = C::HALF_T, XSUM_BYTES = C::XSUM_BYTES;
     constexpr bool BF16 = std::is_same<XT, __nv_bfloat16>::value;
     constexpr uint32_t MAGIC_HI = BF16 ? 0x43434343u : 0x64646464u;
     constexpr float MAGIC = BF16 ? 128.0f : 1024.0f;
@@ -208,12 +218,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                 if (!(ok = mbar_wait_warp(afull_bar(a), aph, 0x1202, abort_flag))) break;                    // codes stored (and the copy stage landed)
                 tc_fence_after();
                 if (leader) {
-                    const uint32_t a_tmem = tmem_base + NB * BT + a * A_COLS;
-                    const uint32_t d_tmem = tmem_base + sb * BT;
+                    const uint32_t a_tmem = tmem_base + 256 + a * A_COLS;
+                    const uint32_t d_tmem = tmem_base + sb * 128;
 #pragma unroll
                     for (int k16 = 0; k16 < 8; ++k16) {        // 16 k = 32 bytes of a token row = 8 TMEM columns per MMA
                         const uint64_t bdesc = smem_desc(base + s * T_BYTES + (k16 >> 2) * X_SUB) + 2u * (k16 & 3);
-                        umma_f16_ts<BF16>(d_tmem, a_tmem + 8u * k16, bdesc, k16 != 0);
+                        umma_f16_ts<BF16, BT>(d_tmem, a_tmem + 8u * k16, bdesc, k16 != 0);
                     }
                     umma_commit(done_bar(it));
                 }
@@ -234,10 +244,29 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         const int group = (warp - 2) >> 2;           // group 0 takes even steps, group 1 odd
         const int row = q * 32 + lane;               // weight row of the tile = token of the tile
         const int total = my_tiles * p.nkb;
+        const int bpg = p.gs / BKK;
         int s = group % TS;
         uint32_t a = group % AS, sph = 0;
         bool ok = true;
+        uint32_t zsub = 0;                           // two copies of MAGIC + zp of this row and group, as 16-bit floats
+        float z_next = 0.0f;
+        auto fetch_z = [&](int step) {               // MAGIC + zero point of this thread's row in the group of pipeline step `step`
+            const int jt = step / p.nkb, kb = step - jt * p.nkb;
+            const int tile = (int)blockIdx.x + jt * (int)gridDim.x;
+            int64_t nrow = (int64_t)(tile / p.tiles_t) * BW + row;
+            if (nrow >= p.N) nrow = p.N - 1;         // rows past N: any constants, their results are not stored
+            return MAGIC + __ldg(p.zc_t + (int64_t)(kb / bpg) * p.N + nrow);
+        };
         for (int it = group; it < total && ok; it += 2) {
+            if (ZPI) {
+                // this step's constant was fetched during the previous step of this group; fetch the next one now
+                if (it == group) z_next = fetch_z(it);
+                const float z = z_next;
+                if (it + 2 < total) z_next = fetch_z(it + 2);
+                uint32_t h;
+                if constexpr (BF16) h = __bfloat16_as_ushort(__float2bfloat16_rn(z)); else h = __half_as_ushort(__float2half_rn(z));
+                zsub = h | (h << 16);
+            }
             if (!(ok = mbar_wait_warp(raw_bar(s), sph, 0x1301, abort_flag))) break;
             const uint8_t *stage = base_ptr + s * T_BYTES;
             // packed row: 64 bytes, SWIZZLE_64B (16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3))
@@ -250,7 +279,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             // positions do not matter for a sum over the whole row)
             float sum = 0.0f;
 #pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {
+            for (int sub = 0; sub < ((ZPI || row >= BT) ? 0 : 2); ++sub) {
                 const uint8_t *xr = stage + sub * X_SUB + row * 128;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
@@ -269,7 +298,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             }
             if (it >= AS && !(ok = mbar_wait_warp(done_bar(it - AS), done_par(it - AS), 0x1302, abort_flag))) break;   // operand stage reusable
             tc_fence_after();
-            xsum[(it & (XR - 1)) * BT + row] = sum;
+            if (!ZPI && row < BT) xsum[(it & (XR - 1)) * BT + row] = sum;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {            // 32 packed bytes = 64 k = 32 columns
                 const uint32_t wv[8] = {pv[2 * h].x, pv[2 * h].y, pv[2 * h].z, pv[2 * h].w,
@@ -277,7 +306,19 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                 uint32_t r[32];
 #pragma unroll
                 for (int jw = 0; jw < 8; ++jw) expand8<MAGIC_HI>(wv[jw], r + 4 * jw);
-                tmem_st32_issue(tmem_base + ((uint32_t)(q * 32) << 16) + NB * BT + a * A_COLS + 32u * h, r);
+                if (ZPI) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        if constexpr (BF16) {
+                            const __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&r[c]), *reinterpret_cast<const __nv_bfloat162 *>(&zsub));
+                            r[c] = *reinterpret_cast<const uint32_t *>(&d);
+                        } else {
+                            const __half2 d = __hsub2(*reinterpret_cast<const __half2 *>(&r[c]), *reinterpret_cast<const __half2 *>(&zsub));
+                            r[c] = *reinterpret_cast<const uint32_t *>(&d);
+                        }
+                    }
+                }
+                tmem_st32_issue(tmem_base + ((uint32_t)(q * 32) << 16) + 256 + a * A_COLS + 32u * h, r);
             }
             tmem_st_wait();
             tc_fence_before();
@@ -305,37 +346,44 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             float yacc[HALF_T];
 #pragma unroll
             for (int t = 0; t < HALF_T; ++t) yacc[t] = 0.0f;
-            int g_have = -1;
-            float sc = 0.0f, cm = 0.0f;
+            // The group constants of a step are fetched one step ahead (a read from L2 costs about as much as a
+            // whole step here, and nothing else in this warp could cover it).
+            auto load_consts = [&](int kb, float &s_out, float &c_out) {
+                const int g = (kb < p.nkb ? kb : p.nkb - 1) / bpg;
+                s_out = __ldg(p.scale_t + (int64_t)g * p.N + nc);
+                c_out = ZPI ? 0.0f : -(MAGIC + __ldg(p.zc_t + (int64_t)g * p.N + nc));
+            };
+            float sc, cm, sc_next, cm_next;
+            load_consts(0, sc_next, cm_next);
             for (int kb = 0; kb < p.nkb && ok; ++kb, ++it) {
                 const uint32_t sb = it % NB;
-                const int g = kb / bpg;
-                if (g != g_have) {                    // the group's constants, read before the wait so that their latency hides behind it
-                    sc = __ldg(p.scale_t + (int64_t)g * p.N + nc);
-                    cm = -(MAGIC + __ldg(p.zc_t + (int64_t)g * p.N + nc));
-                    g_have = g;
-                }
+                sc = sc_next; cm = cm_next;
+                load_consts(kb + 1, sc_next, cm_next);
                 if (!(ok = mbar_wait_warp(done_bar(it), done_par(it), 0x1401, abort_flag))) break;
                 tc_fence_after();
                 const float4 *xs4 = reinterpret_cast<const float4 *>(xsum + (it & (XR - 1)) * BT + half * HALF_T);
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + sb * BT + half * HALF_T;
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + sb * 128 + half * HALF_T;
 #pragma unroll
                 for (int gi = 0; gi < HALF_T / EG; ++gi) {
                     uint32_t r[EG];
                     tmem_ld16(taddr + gi * EG, r);
                     float xs[EG];
+                    if (!ZPI) {
 #pragma unroll
-                    for (int e4 = 0; e4 < EG / 4; ++e4) {
-                        const float4 v = xs4[gi * (EG / 4) + e4];
-                        xs[4 * e4] = v.x; xs[4 * e4 + 1] = v.y; xs[4 * e4 + 2] = v.z; xs[4 * e4 + 3] = v.w;
+                        for (int e4 = 0; e4 < EG / 4; ++e4) {
+                            const float4 v = xs4[gi * (EG / 4) + e4];
+                            xs[4 * e4] = v.x; xs[4 * e4 + 1] = v.y; xs[4 * e4 + 2] = v.z; xs[4 * e4 + 3] = v.w;
+                        }
                     }
                     if (gi == HALF_T / EG - 1) {      // last read of this step's accumulator and token sums: hand them back
                         tc_fence_before();
                         mbar_arrive(acce_bar(sb));
                     }
 #pragma unroll
-                    for (int e = 0; e < EG; ++e)
-                        yacc[gi * EG + e] = fmaf(sc, fmaf(cm, xs[e], __uint_as_float(r[e])), yacc[gi * EG + e]);
+                    for (int e = 0; e < EG; ++e) {
+                        if (ZPI) yacc[gi * EG + e] = fmaf(sc, __uint_as_float(r[e]), yacc[gi * EG + e]);
+                        else yacc[gi * EG + e] = fmaf(sc, fmaf(cm, xs[e], __uint_as_float(r[e])), yacc[gi * EG + e]);
+                    }
                 }
             }
             if (ok && n_ok) {
@@ -373,13 +421,14 @@ bool w4a16_gemm_supported(const void *codes, const void *x, int x_dtype, int64_t
            aligned16(codes) && aligned16(x) && M > 0 && M < (1ll << 31) && N > 0 && N < (1ll << 31) && K < (1ll << 30);
 }
 
-template <typename XT>
+template <typename XT, bool ZPI, int BT>
 static int launch_w4_gemm(const uint8_t *codes, const void *x, w4gemm::Params &p, cudaStream_t st)
 {
     using namespace w4gemm;
+    using C = Cfg<BT>;
     static std::atomic<size_t> reserved[kMaxDevices];
-    if (reserve_smem(w4a16_gemm_kernel<XT>, reserved, (size_t)SMEM) != cudaSuccess)
-        return fail(NSLQ_ERR_CUDA, "w4a16_gemm_kernel: cannot reserve %d bytes of shared memory: %s", SMEM,
+    if (reserve_smem(w4a16_gemm_kernel<XT, ZPI, BT>, reserved, (size_t)C::SMEM) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "w4a16_gemm_kernel: cannot reserve %d bytes of shared memory: %s", C::SMEM,
                     cudaGetErrorString(cudaGetLastError()));
     CUtensorMap tmap_x, tmap_w;
     int rc = sm100::make_map_2d(&tmap_x, x, (uint64_t)p.K * 2, (uint64_t)p.M, 128, BT, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -391,9 +440,25 @@ static int launch_w4_gemm(const uint8_t *codes, const void *x, w4gemm::Params &p
     p.nkb = (int)(p.K / BKK);
     const int tiles = p.tiles_t * p.tiles_w;
     const int grid = tiles < sm100::sm_count() ? tiles : sm100::sm_count();
-    cudaError_t e = launch_kernel(w4a16_gemm_kernel<XT>, dim3(grid), dim3(THREADS), (size_t)SMEM, st, tmap_x, tmap_w, p);
+    cudaError_t e = launch_kernel(w4a16_gemm_kernel<XT, ZPI, BT>, dim3(grid), dim3(THREADS), (size_t)C::SMEM, st, tmap_x, tmap_w, p);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "w4a16_gemm_kernel: %s", cudaGetErrorString(e));
     return check_launch("w4a16_gemm_kernel");
+}
+
+// Token-tile width: the one that wastes fewer SM-rounds on the shape (ties go to the wider tile, which
+// re-reads the packed weights less often).
+template <typename XT, bool ZPI>
+static int pick_w4_gemm(const uint8_t *codes, const void *x, w4gemm::Params &p, cudaStream_t st)
+{
+    const int sms = sm100::sm_count();
+    auto cost = [&](int bt) {
+        const int64_t tiles = ((p.M + bt - 1) / bt) * ((p.N + w4gemm::BW - 1) / w4gemm::BW);
+        return (double)((tiles + sms - 1) / sms) * bt;
+    };
+    const double c128 = cost(128), c96 = cost(96), c64 = cost(64);
+    if (c128 <= c96 && c128 <= c64) return launch_w4_gemm<XT, ZPI, 128>(codes, x, p, st);
+    if (c96 <= c64) return launch_w4_gemm<XT, ZPI, 96>(codes, x, p, st);
+    return launch_w4_gemm<XT, ZPI, 64>(codes, x, p, st);
 }
 
 // One launch takes at most this many token rows (the same precaution as the ternary GEMM takes:
@@ -401,15 +466,17 @@ static int launch_w4_gemm(const uint8_t *codes, const void *x, w4gemm::Params &p
 constexpr int64_t W4_GEMM_MAX_ROWS = 4096;
 
 // scale_t, zc_t: the handle's transposed [G][N] tables.
-int w4a16_gemm_dispatch(const uint8_t *codes, const float *scale_t, const float *zc_t, int64_t N, int64_t K, int G, int gs,
-                        const void *x, int x_dtype, int64_t M, void *y, int y_dtype, cudaStream_t st)
+int w4a16_gemm_dispatch(const uint8_t *codes, const float *scale_t, const float *zc_t, int zp_integer, int64_t N, int64_t K, int G,
+                        int gs, const void *x, int x_dtype, int64_t M, void *y, int y_dtype, cudaStream_t st)
 {
     const int es = y_dtype == NSLQ_DTYPE_F32 ? 4 : 2;
     for (int64_t m0 = 0; m0 < M; m0 += W4_GEMM_MAX_ROWS) {
         const int64_t mc = (M - m0) < W4_GEMM_MAX_ROWS ? (M - m0) : W4_GEMM_MAX_ROWS;
         w4gemm::Params p{scale_t, zc_t, (char *)y + m0 * N * es, mc, N, K, G, gs, y_dtype, 0, 0, 0};
         const void *xm = (const char *)x + m0 * K * 2;
-        int rc = x_dtype == NSLQ_DTYPE_BF16 ? launch_w4_gemm<__nv_bfloat16>(codes, xm, p, st) : launch_w4_gemm<__half>(codes, xm, p, st);
+        int rc;
+        if (x_dtype == NSLQ_DTYPE_BF16) rc = zp_integer ? pick_w4_gemm<__nv_bfloat16, true>(codes, xm, p, st) : pick_w4_gemm<__nv_bfloat16, false>(codes, xm, p, st);
+        else rc = zp_integer ? pick_w4_gemm<__half, true>(codes, xm, p, st) : pick_w4_gemm<__half, false>(codes, xm, p, st);
         if (rc) return rc;
     }
     return NSLQ_OK;

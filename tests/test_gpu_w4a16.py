@@ -92,7 +92,7 @@ def test_scalar_kernel_small_groups_and_f32_x(ops, oracle):
 def test_awq_layout(ops, oracle):
     """AwqPackedWeight form: [K,N] nibbles, f64 scales / float zeros (awq.rs:104-144, :202-226)."""
     rng = np.random.default_rng(9)
-    for K, N, gs, M in [(256, 48, 128, 2), (128, 30, 128, 1), (64, 12, 32, 3)]:
+    for K, N, gs, M in [(256, 48, 128, 2), (128, 30, 128, 1), (64, 12, 32, 3), (512, 200, 128, 40), (256, 136, 256, 300)]:   # M > 16: fractional zero points on the tensor-core path
         wmat = rng.standard_normal((K, N)) * 0.05
         data, scales, zeros = oracle.awq_quantize(wmat, gs)
         x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
