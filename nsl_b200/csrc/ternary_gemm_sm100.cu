@@ -17,7 +17,8 @@
 //   warp 0      TMA producer: per step, cp.async.bulk.tensor copies (2-D, this CTA only)
 //               into a ring of copy stages: the int8 activation tile (BT tokens x 128 k
 //               per k-block, SWIZZLE_128B) and the packed weight tile (128 rows x 32
-//               bytes per k-block); out-of-range rows and the K tail are zero-filled.
+//               bytes per k-block, swizzled so that a thread per row reads without bank
+//               conflicts); out-of-range rows and the K tail are zero-filled.
 //   warps 8-15  unpack, two groups of four warps (one warp per TMEM lane quadrant) taking
 //               alternate k-blocks: each thread reads the 32 packed bytes of its weight
 //               row, expands them with (w >> s) & 0x03030303 into 32 words of u8 codes
@@ -330,10 +331,14 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         uint32_t a = group % C::AS, sph = 0, aph = 0;
         for (int it = group; it < total_it && ok; it += 2) {
             if (!(ok = mbar_wait_warp(raw_bar(s), sph, 0x301, abort_flag))) break;                            // packed tile landed
+            // The packed tile is copied with a 64-byte (KS = 2) or 32-byte (KS = 1) swizzle: 16-byte chunk c of row r
+            // sits at chunk c ^ ((r >> 1) & 3) resp. c ^ ((r >> 2) & 1), which spreads the eight rows a quarter-warp
+            // reads at once over all banks (unswizzled, rows 64 or 32 bytes apart collide four resp. two ways).
             const uint4 *pk = reinterpret_cast<const uint4 *>(base_ptr + s * C::T_BYTES + C::X_BYTES + row * C::PK_ROW);
+            const int sw = C::KS == 2 ? ((row >> 1) & 3) : ((row >> 2) & 1);
             uint4 pv[2 * C::KS];
 #pragma unroll
-            for (int i = 0; i < 2 * C::KS; ++i) pv[i] = pk[i];
+            for (int i = 0; i < 2 * C::KS; ++i) pv[i] = pk[i ^ sw];
             if (it >= C::AS && !(ok = mbar_wait_warp(done_bar(it - C::AS), done_par(it - C::AS), 0x302, abort_flag))) break;   // operand stage reusable
             tc_fence_after();
 #pragma unroll
@@ -430,7 +435,8 @@ static int launch_gemm(const void *q_perm, gemm::Params &p, cudaStream_t st)
     CUtensorMap tmap_x, tmap_w;
     int rc = sm100::make_map_2d(&tmap_x, q_perm, (uint64_t)p.K, (uint64_t)p.M, gemm::BK, BT, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    rc = sm100::make_map_2d(&tmap_w, p.w, (uint64_t)(p.K / 4), (uint64_t)p.N, C::PK_ROW, gemm::BW, CU_TENSOR_MAP_SWIZZLE_NONE);
+    rc = sm100::make_map_2d(&tmap_w, p.w, (uint64_t)(p.K / 4), (uint64_t)p.N, C::PK_ROW, gemm::BW,
+                            C::KS == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
     if (rc) return rc;
     p.tiles_t = (int)((p.M + BT - 1) / BT);
     p.tiles_w = (int)((p.N + gemm::BW - 1) / gemm::BW);
