@@ -34,6 +34,7 @@ extern "C" {
 #define NSLQ_ERR_WORKSPACE    -5 /* workspace missing or too small                  */
 #define NSLQ_ERR_COMM         -6 /* NCCL missing or a collective failed             */
 #define NSLQ_ERR_TIMEOUT      -7 /* a bounded wait on a collective reached its deadline */
+#define NSLQ_ERR_IO           -8 /* a file cannot be read or is not the container it should be */
 
 /* ---- dtype tags: NSL's NslTensor.dtype wire tags -------------------------
  * crates/nsl-runtime/src/tensor/mod.rs:246-256 */
@@ -150,6 +151,31 @@ int nslq_decode_attention(const void *q, const void *k_new, const void *v_new,
                           int64_t B, int64_t H, int64_t Hkv, int64_t D, int64_t max_ctx,
                           float sm_scale, void *out, void *stream);
 
+/*
+ * The three remaining launches of a greedy decode step, each one runtime function of NSL as one launch on
+ * device-resident data (one CTA per row; launch-latency work):
+ *
+ *  nslq_embed_gather   out[r,:] = (f32) table[tokens[r],:]   nsl_tensor_embedding_lookup
+ *                      (crates/nsl-runtime/src/tensor/mod.rs:2592-2680).  table [V,H] F32/FP16/BF16, tokens int64 [B].
+ *                      The reference bounds-checks host-resident ids and aborts; these ids live on the device,
+ *                      so the kernel checks: an id outside [0,V) gives a row of zeros and status 0xA01
+ *                      (nslq_device_status).
+ *  nslq_rmsnorm_rows   y[r,k] = (f32)(x[r,k] / rms[r] * weight[k]), rms = sqrt(mean x^2 + eps) in f64
+ *                      (nsl_tensor_rmsnorm, crates/nsl-runtime/src/tensor/mod.rs:3016-3035; the sum of squares
+ *                      is a tree, as in nslq_rmsnorm_act_quant_i8), then rounded to y_dtype in {F32,FP16,BF16}.
+ *  nslq_argmax_rows    out[r] = lowest index of the largest element of x[r,0:V] (row stride ld elements);
+ *                      a NaN never wins, a row with nothing above -inf gives 0: the loop of nsl_tensor_argmax
+ *                      (crates/nsl-runtime/src/sampling.rs:322-400).  int64 indices (the reference returns
+ *                      them as f64).  `counter` (device int64, may be NULL) is incremented by one: the
+ *                      position of a decode loop that lives on the device.
+ */
+int nslq_embed_gather(const void *table, int table_dtype, int64_t V, int64_t H, const int64_t *tokens, int64_t B,
+                      float *out, void *stream);
+int nslq_rmsnorm_rows(const float *x, const float *weight, double eps, int64_t M, int64_t K, void *y, int y_dtype,
+                      void *stream);
+int nslq_argmax_rows(const void *x, int x_dtype, int64_t M, int64_t V, int64_t ld, int64_t *out, int64_t *counter,
+                     void *stream);
+
 /* ========================================================================== */
 /* BitLinear (ternary W1.58 A8)                                                */
 /* ========================================================================== */
@@ -212,6 +238,25 @@ int nslq_bitlinear_forward_quantized(const nslq_bitlinear_t *w, const int8_t *q_
                                      const float *scale, const int32_t *rowsum, int64_t M,
                                      void *y, int y_dtype, int32_t *acc_out,
                                      const float *bias, const float *residual, void *stream);
+
+/*
+ * nslq_bitlinear_forward with the launch in front of it folded in: the input rows are
+ *   RMSNorm(x) with `norm_weight`, `eps`      (= nslq_rmsnorm_act_quant_i8, then forward_quantized), or
+ *   SiLU(gate) * up                           (= nslq_swiglu_act_quant_i8,  then forward_quantized),
+ * with the same bits as those two calls.  Up to four tokens (a decode step) every CTA of the one launch
+ * forms and quantises the rows for itself -- NSL's BitNet kernel config names this prologue (`fused_rmsnorm`,
+ * crates/nsl-codegen/src/bitnet/config.rs:23-31) and never emits it; above four tokens, or when a row
+ * does not fit the CTA's shared memory next to the weights, the call issues the two launches itself and
+ * needs the workspace of nslq_bitlinear_forward (pass it always).  K % 64 == 0; gate, up: [M,K], packed.
+ */
+int nslq_bitlinear_forward_rmsnorm(const nslq_bitlinear_t *w, const void *x, int x_dtype, int64_t M,
+                                   const float *norm_weight, double eps, void *y, int y_dtype, int32_t *acc_out,
+                                   const float *bias, const float *residual,
+                                   void *workspace, int64_t workspace_bytes, void *stream);
+int nslq_bitlinear_forward_swiglu(const nslq_bitlinear_t *w, const void *gate, const void *up, int dtype, int64_t M,
+                                  void *y, int y_dtype, int32_t *acc_out,
+                                  const float *bias, const float *residual,
+                                  void *workspace, int64_t workspace_bytes, void *stream);
 
 /*
  * nslq_bitlinear_forward without a caller workspace.  (No counterpart in NSL: the
@@ -326,6 +371,27 @@ int nslq_ternary_quantize_pack(const void *w, int w_dtype, int64_t numel, uint8_
                                void *stream);
 
 /*
+ * load_bitnet_b158_safetensors (crates/nsl-codegen/src/bitnet/loader.rs:200-220): every tensor of the
+ * safetensors file at `path` whose name ends in one of the seven BitLinear projection suffixes
+ * (.self_attn.{q,k,v,o}_proj.weight, .mlp.{gate,up,down}_proj.weight; loader.rs:100-111), stored as F32,
+ * F16 or BF16, is copied to the current device and quantised there by nslq_ternary_quantize_pack.  An
+ * entry of the set is the reference's LoadedTernaryWeight (loader.rs:47-56): name, packed bytes (in DEVICE
+ * memory, owned by the set: pass them to nslq_bitlinear_create with N = shape[0], K = shape[1]), the
+ * shape from the header, and the absmean scale (= weight_scale).  Entries come in the order of their
+ * bytes in the file (the reference's order is that of a hash map).  Errors, as the reference's
+ * LoaderError: NSLQ_ERR_IO (Io, Safetensors: unreadable file, malformed header, byte ranges that do not
+ * match shape or file), NSLQ_ERR_SHAPE (AlignmentError: element count % 4), NSLQ_ERR_UNSUPPORTED
+ * (UnsupportedDtype); nothing is returned then.  Other tensors (embeddings, norms, lm_head) are skipped,
+ * as in the reference.  Synchronises `stream` once per tensor: a load-time call.
+ */
+typedef struct nslq_ternary_set nslq_ternary_set_t;
+int nslq_bitnet_load_safetensors(const char *path, void *stream, nslq_ternary_set_t **out);
+int64_t nslq_ternary_set_size(const nslq_ternary_set_t *set);
+int nslq_ternary_set_entry(const nslq_ternary_set_t *set, int64_t i, const char **name, const uint8_t **packed,
+                           int64_t *packed_bytes, const int64_t **shape, int *ndim, float *scale);
+void nslq_ternary_set_destroy(nslq_ternary_set_t *set);
+
+/*
  * nsl_qtensor_quantize for INT4, per-group along axis 1 of a [N,K] tensor
  * (crates/nsl-runtime/src/quantize.rs:224-266, :366-417): f64 arithmetic, scale =
  * (max-min)/15 (stored f32), zp = round(-min/scale) clamped, q = round(x/scale+zp)
@@ -335,6 +401,23 @@ int nslq_ternary_quantize_pack(const void *w, int w_dtype, int64_t numel, uint8_
  */
 int nslq_int4_quantize_nk(const void *w, int w_dtype, int64_t N, int64_t K, int64_t group_size,
                           uint8_t *codes, float *scale, uint8_t *zero_point, void *stream);
+
+/*
+ * nsl_qtensor_quantize and nsl_qtensor_dequantize in every form the reference has
+ * (crates/nsl-runtime/src/quantize.rs:283-426, :436-537): dtype 0 = INT8 (codes 0..255), 1 = INT4 (two
+ * codes per byte over the flat row-major index, low nibble = even index); granularity 0 = per tensor,
+ * 1 = per channel along `axis`, 2 = per group of `group_size` along `axis`, for a tensor of up to 8
+ * dimensions (`shape`: HOST array).  f64 arithmetic as in compute_scale_zp / quantize_val /
+ * dequantize_val (quantize.rs:224-266); minimum and maximum by atomics (order-independent), so data,
+ * scale (f32) and zero_point (u8) are the reference's bytes.  nslq_qtensor_num_scales = compute_num_scales
+ * (quantize.rs:72-96) sizes scale and zero_point.  src: F64 or F32 device tensor; dequantise writes F64 (what
+ * the reference returns) or F32.  quantize allocates a small scratch and synchronises `stream`: a load-time call.
+ */
+int64_t nslq_qtensor_num_scales(const int64_t *shape, int ndim, int granularity, int axis, int64_t group_size);
+int nslq_qtensor_quantize(const void *src, int src_dtype, const int64_t *shape, int ndim, int dtype, int granularity,
+                          int axis, int64_t group_size, uint8_t *data, float *scale, uint8_t *zero_point, void *stream);
+int nslq_qtensor_dequantize(const uint8_t *data, const float *scale, const uint8_t *zero_point, const int64_t *shape, int ndim,
+                            int dtype, int granularity, int axis, int64_t group_size, void *out, int out_dtype, void *stream);
 
 /*
  * awq_quantize_cpu (crates/nsl-runtime/src/awq.rs:104-144): weight [K,N] (F64 or F32),

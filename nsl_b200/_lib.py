@@ -26,6 +26,8 @@ SIGNATURES = {
     "nslq_bitlinear_workspace_bytes": (i64, [i64, i64]),
     "nslq_bitlinear_forward": (i32, [vp, vp, i32, i64, vp, i32, vp, vp, vp, vp, i64, vp]),
     "nslq_bitlinear_forward_quantized": (i32, [vp, vp, vp, vp, i64, vp, i32, vp, vp, vp, vp]),
+    "nslq_bitlinear_forward_rmsnorm": (i32, [vp, vp, i32, i64, vp, C.c_double, vp, i32, vp, vp, vp, vp, i64, vp]),
+    "nslq_bitlinear_forward_swiglu": (i32, [vp, vp, vp, i32, i64, vp, i32, vp, vp, vp, vp, i64, vp]),
     "nslq_bitlinear_forward_noalloc": (i32, [vp, vp, i32, i64, vp, i32, vp]),
     "nslq_noalloc_scratch_bytes": (i64, []),
     "nslq_w4a16_create_nk": (i32, [vp, vp, i32, vp, i32, i64, i64, i64, C.POINTER(vp)]),
@@ -37,6 +39,17 @@ SIGNATURES = {
     "nslq_w4a16_forward": (i32, [vp, vp, i32, i64, vp, i32, vp]),
     "nslq_ternary_quantize_pack": (i32, [vp, i32, i64, vp, vp, vp]),
     "nslq_int4_quantize_nk": (i32, [vp, i32, i64, i64, i64, vp, vp, vp, vp]),
+    "nslq_embed_gather": (i32, [vp, i32, i64, i64, vp, i64, vp, vp]),
+    "nslq_rmsnorm_rows": (i32, [vp, vp, C.c_double, i64, i64, vp, i32, vp]),
+    "nslq_argmax_rows": (i32, [vp, i32, i64, i64, i64, vp, vp, vp]),
+    "nslq_bitnet_load_safetensors": (i32, [C.c_char_p, vp, C.POINTER(vp)]),
+    "nslq_ternary_set_size": (i64, [vp]),
+    "nslq_ternary_set_entry": (i32, [vp, i64, C.POINTER(C.c_char_p), C.POINTER(vp), C.POINTER(i64), C.POINTER(C.POINTER(i64)),
+                                     C.POINTER(i32), C.POINTER(C.c_float)]),
+    "nslq_ternary_set_destroy": (None, [vp]),
+    "nslq_qtensor_num_scales": (i64, [C.POINTER(i64), i32, i32, i32, i64]),
+    "nslq_qtensor_quantize": (i32, [vp, i32, C.POINTER(i64), i32, i32, i32, i32, i64, vp, vp, vp, vp]),
+    "nslq_qtensor_dequantize": (i32, [vp, vp, vp, C.POINTER(i64), i32, i32, i32, i32, i64, vp, i32, vp]),
     "nslq_awq_quantize_kn": (i32, [vp, i32, i64, i64, i64, vp, vp, vp, vp]),
     "nslq_shard_rows": (i32, [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]),
     "nslq_shard_unique_id": (i32, [vp]),

@@ -7,7 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnslq_b200.so")
 
-SOURCES = ["abi.cu", "act_quant.cu", "ternary_gemv.cu", "ternary_decode_sm100.cu", "ternary_gemm_sm100.cu", "w4a16_gemv.cu", "w4a16_gemm_sm100.cu", "w4a16_decode_sm100.cu", "noalloc.cu", "shard_comm.cu", "decode_attention.cu", "pack_at_load.cu", "nsl_shims.cu"]
+SOURCES = ["abi.cu", "act_quant.cu", "ternary_gemv.cu", "ternary_decode_sm100.cu", "ternary_gemm_sm100.cu", "w4a16_gemv.cu", "w4a16_gemm_sm100.cu", "w4a16_decode_sm100.cu", "noalloc.cu", "shard_comm.cu", "decode_attention.cu", "decode_glue.cu", "pack_at_load.cu", "bitnet_loader.cu", "nsl_shims.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

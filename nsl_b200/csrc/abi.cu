@@ -43,6 +43,9 @@ int ternary_gemv_dispatch(const uint8_t *, const int8_t *, const float *, const 
 int ternary_scalar_dispatch(const uint8_t *, const int8_t *, const float *, int64_t, int64_t, int64_t, float,
                             void *, int, int32_t *, const float *, const float *, cudaStream_t);
 bool ternary_gemv_fused_supported(const void *, const void *, int64_t, int64_t);
+bool ternary_gemv_src_supported(const void *, const void *, const void *, const float *, int64_t, int64_t);
+int ternary_gemv_src_dispatch(const uint8_t *, const void *, const void *, const float *, double, int, int, int64_t, int64_t, float, void *,
+                              int, int32_t *, const float *, const float *, cudaStream_t);
 int ternary_gemv_fused_dispatch(const uint8_t *, const void *, int, int, int64_t, int64_t, float, void *, int, int32_t *,
                                 const float *, const float *, cudaStream_t);
 bool ternary_decode_supported(const void *, const void *, int64_t, int64_t, int64_t);
@@ -54,6 +57,7 @@ int ternary_decode_fused_dispatch(const uint8_t *, const void *, int, int, int64
 int ternary_decode_status(int *);
 int ternary_gemv_status(int *);
 int decode_attention_status(int *);
+int decode_glue_status(int *);
 bool ternary_gemm_supported(const void *, const void *, int64_t, int64_t, int64_t);
 int ternary_gemm_dispatch(const uint8_t *, const int8_t *, const float *, const int32_t *, int64_t, int64_t,
                           int64_t, float, void *, int, int32_t *, const float *, const float *, const OutSpec *, cudaStream_t);
@@ -75,6 +79,9 @@ int w4a16_gemm_dispatch(const uint8_t *, const float *, const float *, int, int6
 int ternary_quantize_pack_dispatch(const void *, int, int64_t, uint8_t *, float *, cudaStream_t);
 int int4_quantize_nk_dispatch(const void *, int, int64_t, int64_t, int64_t, uint8_t *, float *, uint8_t *, cudaStream_t);
 int awq_quantize_kn_dispatch(const void *, int, int64_t, int64_t, int64_t, uint8_t *, double *, double *, cudaStream_t);
+int qtensor_quantize_dispatch(const void *, int, const int64_t *, int, int, int, int, int64_t, uint8_t *, float *, uint8_t *, cudaStream_t);
+int qtensor_dequantize_dispatch(const uint8_t *, const float *, const uint8_t *, const int64_t *, int, int, int, int, int64_t, void *, int, cudaStream_t);
+int64_t qtensor_num_scales(const int64_t *, int, int, int, int64_t);
 
 // Which decode kernel for M <= 16 tokens.  The tensor-memory kernel (ternary_decode_kernel) streams
 // at 4-5 TB/s but has ~5 us of start-up (TMEM allocation, token staging, pipeline fill); the
@@ -247,7 +254,9 @@ int nslq_device_status(int *status)
     if ((rc = ternary_gemv_status(&e))) return rc;
     int f = 0;
     if ((rc = decode_attention_status(&f))) return rc;
-    *status = a ? a : (b ? b : (c ? c : (d ? d : (e ? e : f))));
+    int g = 0;
+    if ((rc = decode_glue_status(&g))) return rc;
+    *status = a ? a : (b ? b : (c ? c : (d ? d : (e ? e : (f ? f : g)))));
     return NSLQ_OK;
 }
 
@@ -390,6 +399,53 @@ int nslq_bitlinear_forward(const nslq_bitlinear_t *w, const void *x, int x_dtype
     if (rc) return rc;
     return ternary_scalar_dispatch(w->packed, q, scale, M, w->N, w->K, w->weight_scale, y, y_dtype, acc_out, bias,
                                    residual, st);
+}
+
+// The RMSNorm or the SiLU(gate) * up in front of a projection, formed inside the projection's own launch for
+// up to four tokens; the same two launches as the separate entry points (bit-equal results) above that.
+static int forward_src(const char *who, const nslq_bitlinear_t *w, const void *x, const void *x2, const float *norm_w, double eps,
+                       int x_dtype, int64_t M, void *y, int y_dtype, int32_t *acc_out, const float *bias, const float *residual,
+                       void *workspace, int64_t workspace_bytes, void *stream)
+{
+    if (!w || !x || !y) return fail(NSLQ_ERR_ARG, "%s: null argument", who);
+    if (!out_elem_size(y_dtype)) return fail(NSLQ_ERR_ARG, "%s: y_dtype %d not in {F32,FP16,BF16}", who, y_dtype);
+    if (M < 0) return fail(NSLQ_ERR_SHAPE, "%s: M=%lld", who, (long long)M);
+    if (M == 0) return NSLQ_OK;
+    if (w->K % 64 != 0 || !aligned16(w->packed))
+        return fail(NSLQ_ERR_UNSUPPORTED, "%s: K=%lld must be a multiple of 64 and the weight 16-byte aligned", who, (long long)w->K);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (ternary_gemv_src_supported(w->packed, x, x2, norm_w, M, w->K))
+        return ternary_gemv_src_dispatch(w->packed, x, x2, norm_w, eps, x_dtype, (int)M, w->N, w->K, w->weight_scale, y, y_dtype,
+                                         acc_out, bias, residual, st);
+    const int64_t need = nslq_bitlinear_workspace_bytes(M, w->K);
+    if (!workspace || workspace_bytes < need)
+        return fail(NSLQ_ERR_WORKSPACE, "%s: workspace %lld bytes, need %lld", who, (long long)workspace_bytes, (long long)need);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(NSLQ_ERR_ARG, "%s: workspace not 256-byte aligned", who);
+    int8_t *q = (int8_t *)workspace;
+    float *scale = (float *)((char *)workspace + align_up(M * w->K, 256));
+    int32_t *rowsum = (int32_t *)((char *)scale + align_up(M * 4, 256));
+    const int rc = norm_w ? rmsnorm_act_quant_dispatch(x, x_dtype, norm_w, eps, M, w->K, nullptr, nullptr, q, scale, rowsum, st)
+                          : swiglu_act_quant_dispatch(x, x2, x_dtype, M, w->K, w->K, w->K, nullptr, nullptr, q, scale, rowsum, st);
+    if (rc) return rc;
+    return nslq_bitlinear_forward_quantized(w, q, scale, rowsum, M, y, y_dtype, acc_out, bias, residual, stream);
+}
+
+int nslq_bitlinear_forward_rmsnorm(const nslq_bitlinear_t *w, const void *x, int x_dtype, int64_t M, const float *norm_weight,
+                                   double eps, void *y, int y_dtype, int32_t *acc_out, const float *bias, const float *residual,
+                                   void *workspace, int64_t workspace_bytes, void *stream)
+{
+    if (!norm_weight) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_forward_rmsnorm: null norm weight");
+    return forward_src("nslq_bitlinear_forward_rmsnorm", w, x, nullptr, norm_weight, eps, x_dtype, M, y, y_dtype, acc_out, bias,
+                       residual, workspace, workspace_bytes, stream);
+}
+
+int nslq_bitlinear_forward_swiglu(const nslq_bitlinear_t *w, const void *gate, const void *up, int dtype, int64_t M, void *y,
+                                  int y_dtype, int32_t *acc_out, const float *bias, const float *residual, void *workspace,
+                                  int64_t workspace_bytes, void *stream)
+{
+    if (!up) return fail(NSLQ_ERR_ARG, "nslq_bitlinear_forward_swiglu: null up");
+    return forward_src("nslq_bitlinear_forward_swiglu", w, gate, up, nullptr, 0.0, dtype, M, y, y_dtype, acc_out, bias, residual,
+                       workspace, workspace_bytes, stream);
 }
 
 // ---------------------------------------------------------------- W4A16
@@ -595,6 +651,25 @@ int nslq_awq_quantize_kn(const void *w, int w_dtype, int64_t K, int64_t N, int64
     if (N <= 0 || K <= 0 || group_size <= 0) return fail(NSLQ_ERR_SHAPE, "nslq_awq_quantize_kn: K=%lld N=%lld group=%lld", (long long)K, (long long)N, (long long)group_size);
     if ((K * N) % 8 != 0) return fail(NSLQ_ERR_SHAPE, "nslq_awq_quantize_kn: K*N = %lld must be a multiple of 8", (long long)(K * N));
     return awq_quantize_kn_dispatch(w, w_dtype, K, N, group_size, data, scales, zeros, (cudaStream_t)stream);
+}
+
+int64_t nslq_qtensor_num_scales(const int64_t *shape, int ndim, int granularity, int axis, int64_t group_size)
+{
+    return qtensor_num_scales(shape, ndim, granularity, axis, group_size);
+}
+
+int nslq_qtensor_quantize(const void *src, int src_dtype, const int64_t *shape, int ndim, int dtype, int granularity, int axis,
+                          int64_t group_size, uint8_t *data, float *scale, uint8_t *zero_point, void *stream)
+{
+    if (!src || !data || !scale || !zero_point) return fail(NSLQ_ERR_ARG, "nslq_qtensor_quantize: null argument");
+    return qtensor_quantize_dispatch(src, src_dtype, shape, ndim, dtype, granularity, axis, group_size, data, scale, zero_point, (cudaStream_t)stream);
+}
+
+int nslq_qtensor_dequantize(const uint8_t *data, const float *scale, const uint8_t *zero_point, const int64_t *shape, int ndim, int dtype,
+                            int granularity, int axis, int64_t group_size, void *out, int out_dtype, void *stream)
+{
+    if (!data || !scale || !zero_point || !out) return fail(NSLQ_ERR_ARG, "nslq_qtensor_dequantize: null argument");
+    return qtensor_dequantize_dispatch(data, scale, zero_point, shape, ndim, dtype, granularity, axis, group_size, out, out_dtype, (cudaStream_t)stream);
 }
 
 int nslq_shard_rows(int64_t N, int world, int rank, int64_t *row0, int64_t *rows)

@@ -1,0 +1,187 @@
+// The three launches of a decode step that are neither a quantized linear nor attention: the embedding
+// rows of the current tokens, the RMSNorm in front of the output head, and the greedy choice of the next
+// token.  Each restates a runtime function of NSL as one launch, so that a decode step of the harness is
+// library launches from the first to the last (the head's bf16 GEMM aside):
+//
+//   nslq_embed_gather   nsl_tensor_embedding_lookup  crates/nsl-runtime/src/tensor/mod.rs:2592-2680
+//   nslq_rmsnorm_rows   nsl_tensor_rmsnorm           crates/nsl-runtime/src/tensor/mod.rs:3016-3035
+//   nslq_argmax_rows    nsl_tensor_argmax            crates/nsl-runtime/src/sampling.rs:322-400
+//
+// All three are one CTA per row and bound by launch latency at decode sizes.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+#include "quant_core.cuh"
+#include "rmsnorm_core.cuh"
+
+namespace nslq {
+
+static __device__ int g_glue_status = 0;      // 0xA01: a token id outside the embedding table
+
+template <typename T> static __device__ __forceinline__ float elem_to_float(T v);
+template <> __device__ __forceinline__ float elem_to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float elem_to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float elem_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// out[r, :] = (f32) table[tokens[r], :].  The reference checks host-resident ids and aborts; ids that live
+// on the device cannot be checked by the host without a synchronisation, so the kernel checks them: a row
+// whose id is out of range becomes zeros and the status word says so.
+template <typename T>
+__global__ void __launch_bounds__(256) embed_gather_kernel(const T *__restrict__ table, int64_t V, int64_t H,
+                                                           const int64_t *__restrict__ tokens, float *__restrict__ out)
+{
+    pdl_wait();
+    const int64_t r = blockIdx.x;
+    const int64_t tok = tokens[r];
+    const bool ok = tok >= 0 && tok < V;
+    if (!ok && threadIdx.x == 0) atomicCAS(&g_glue_status, 0, 0xA01);
+    const T *row = table + (ok ? tok : 0) * H;
+    for (int64_t i = threadIdx.x; i < H; i += blockDim.x) out[r * H + i] = ok ? elem_to_float(row[i]) : 0.0f;
+    pdl_launch_dependents();
+}
+
+// y[r, k] = (out dtype)(f32)(x[r,k] / rms * w[k]), rms = sqrt(mean x^2 + eps) in f64: the arithmetic of
+// nslq_rmsnorm_act_quant_i8's normalisation (rmsnorm_core.cuh), rounded once more when y is 16-bit.
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float *__restrict__ x, const float *__restrict__ w, double eps,
+                                                           double inv_k, int64_t K, void *__restrict__ y, int y_dtype)
+{
+    __shared__ double part[8];
+    pdl_wait();
+    const int64_t r = blockIdx.x;
+    const float *row = x + r * K;
+    FF a{0.0f, 0.0f};
+    bool bad = false;
+    for (int64_t i = threadIdx.x; i < K; i += 256) ff_add_sq(a, row[i], bad);
+    a = ff_warp_sum(a, __any_sync(0xffffffffu, bad));
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = (double)a.h + (double)a.l;
+    __syncthreads();
+    double tot = sum_partials<8>(part, 1);
+    if (!(tot <= 3.5e38)) {                                   // CTA-uniform: a row out of the fp32 path's range
+        double sq = 0.0;
+        for (int64_t i = threadIdx.x; i < K; i += 256) sq += (double)row[i] * (double)row[i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = sq;
+        __syncthreads();
+        tot = sum_partials<8>(part, 1);
+    }
+    const RmsScale rs = rms_scale(tot, (double)K, inv_k, eps);
+    for (int64_t i = threadIdx.x; i < K; i += 256) store_out(y, y_dtype, r * K + i, norm_ff(row[i], w[i], rs));
+    pdl_launch_dependents();
+}
+
+// out[r] = the lowest index of the largest element of row r; a NaN never wins and a row without any
+// element above -inf gives 0 (the reference's loop: `if v > best` from -inf, index 0).  `counter`, when
+// given, is advanced by one by the first CTA: the position of a decode loop, which lives on the device.
+constexpr int AM_THREADS = 1024;
+template <typename T>
+__global__ void __launch_bounds__(AM_THREADS) argmax_rows_kernel(const T *__restrict__ x, int64_t V, int64_t ld, int64_t *__restrict__ out,
+                                                                 int64_t *__restrict__ counter)
+{
+    __shared__ float sval[AM_THREADS / 32];
+    __shared__ int64_t sidx[AM_THREADS / 32];
+    pdl_wait();
+    const int64_t r = blockIdx.x;
+    const T *row = x + r * ld;
+    float best = -INFINITY;
+    int64_t bi = INT64_MAX;
+    for (int64_t i = threadIdx.x; i < V; i += AM_THREADS) {
+        const float v = elem_to_float(row[i]);
+        if (v > best) { best = v; bi = i; }
+    }
+    auto merge = [&](float ov, int64_t oi) {
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int64_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        merge(ov, oi);
+    }
+    if ((threadIdx.x & 31) == 0) { sval[threadIdx.x >> 5] = best; sidx[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = sval[threadIdx.x];
+        bi = sidx[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int64_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            merge(ov, oi);
+        }
+        if (threadIdx.x == 0) {
+            out[r] = bi == INT64_MAX ? 0 : bi;
+            if (counter && r == 0) *counter += 1;
+        }
+    }
+    pdl_launch_dependents();
+}
+
+int decode_glue_status(int *out)
+{
+    int v = 0;
+    const int zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_glue_status, sizeof(int)) != cudaSuccess)
+        return fail(NSLQ_ERR_CUDA, "decode_glue_status: %s", cudaGetErrorString(cudaGetLastError()));
+    if (v != 0) cudaMemcpyToSymbol(g_glue_status, &zero, sizeof(int));
+    *out = v;
+    return NSLQ_OK;
+}
+
+}  // namespace nslq
+
+using namespace nslq;
+
+extern "C" {
+
+int nslq_embed_gather(const void *table, int table_dtype, int64_t V, int64_t H, const int64_t *tokens, int64_t B, float *out, void *stream)
+{
+    if (!table || !tokens || !out) return fail(NSLQ_ERR_ARG, "nslq_embed_gather: null argument");
+    if (V <= 0 || H <= 0 || B < 0 || B > 0x7fffffffLL) return fail(NSLQ_ERR_SHAPE, "nslq_embed_gather: V=%lld H=%lld B=%lld", (long long)V, (long long)H, (long long)B);
+    if (B == 0) return NSLQ_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    switch (table_dtype) {
+    case NSLQ_DTYPE_F32: e = launch_kernel(embed_gather_kernel<float>, dim3((unsigned)B), dim3(256), 0, st, (const float *)table, V, H, tokens, out); break;
+    case NSLQ_DTYPE_FP16: e = launch_kernel(embed_gather_kernel<__half>, dim3((unsigned)B), dim3(256), 0, st, (const __half *)table, V, H, tokens, out); break;
+    case NSLQ_DTYPE_BF16: e = launch_kernel(embed_gather_kernel<__nv_bfloat16>, dim3((unsigned)B), dim3(256), 0, st, (const __nv_bfloat16 *)table, V, H, tokens, out); break;
+    default: return fail(NSLQ_ERR_ARG, "nslq_embed_gather: table dtype %d not in {F32,FP16,BF16}", table_dtype);
+    }
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "embed_gather_kernel: %s", cudaGetErrorString(e));
+    return check_launch("embed_gather_kernel");
+}
+
+int nslq_rmsnorm_rows(const float *x, const float *weight, double eps, int64_t M, int64_t K, void *y, int y_dtype, void *stream)
+{
+    if (!x || !weight || !y) return fail(NSLQ_ERR_ARG, "nslq_rmsnorm_rows: null argument");
+    if (M < 0 || K <= 0 || M > 0x7fffffffLL) return fail(NSLQ_ERR_SHAPE, "nslq_rmsnorm_rows: M=%lld K=%lld", (long long)M, (long long)K);
+    if (y_dtype != NSLQ_DTYPE_F32 && y_dtype != NSLQ_DTYPE_FP16 && y_dtype != NSLQ_DTYPE_BF16)
+        return fail(NSLQ_ERR_ARG, "nslq_rmsnorm_rows: y dtype %d not in {F32,FP16,BF16}", y_dtype);
+    if (M == 0) return NSLQ_OK;
+    const cudaError_t e = launch_kernel(rmsnorm_rows_kernel, dim3((unsigned)M), dim3(256), 0, (cudaStream_t)stream, x, weight, eps, 1.0 / (double)K, K, y, y_dtype);
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "rmsnorm_rows_kernel: %s", cudaGetErrorString(e));
+    return check_launch("rmsnorm_rows_kernel");
+}
+
+int nslq_argmax_rows(const void *x, int x_dtype, int64_t M, int64_t V, int64_t ld, int64_t *out, int64_t *counter, void *stream)
+{
+    if (!x || !out) return fail(NSLQ_ERR_ARG, "nslq_argmax_rows: null argument");
+    if (M < 0 || V <= 0 || ld < V || M > 0x7fffffffLL) return fail(NSLQ_ERR_SHAPE, "nslq_argmax_rows: M=%lld V=%lld ld=%lld", (long long)M, (long long)V, (long long)ld);
+    if (M == 0) return NSLQ_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    switch (x_dtype) {
+    case NSLQ_DTYPE_F32: e = launch_kernel(argmax_rows_kernel<float>, dim3((unsigned)M), dim3(AM_THREADS), 0, st, (const float *)x, V, ld, out, counter); break;
+    case NSLQ_DTYPE_FP16: e = launch_kernel(argmax_rows_kernel<__half>, dim3((unsigned)M), dim3(AM_THREADS), 0, st, (const __half *)x, V, ld, out, counter); break;
+    case NSLQ_DTYPE_BF16: e = launch_kernel(argmax_rows_kernel<__nv_bfloat16>, dim3((unsigned)M), dim3(AM_THREADS), 0, st, (const __nv_bfloat16 *)x, V, ld, out, counter); break;
+    default: return fail(NSLQ_ERR_ARG, "nslq_argmax_rows: dtype %d not in {F32,FP16,BF16}", x_dtype);
+    }
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "argmax_rows_kernel: %s", cudaGetErrorString(e));
+    return check_launch("argmax_rows_kernel");
+}
+
+}  // extern "C"

@@ -216,4 +216,176 @@ int awq_quantize_kn_dispatch(const void *w, int w_dtype, int64_t K, int64_t N, i
     return check_launch("awq_quantize_kn_kernel");
 }
 
+// ---------------------------------------------------------------- nsl_qtensor_quantize / _dequantize, every form
+// crates/nsl-runtime/src/quantize.rs:283-426 and :436-537: INT8 or INT4, per tensor / per channel / per
+// group along any axis of an n-dimensional tensor.  The tensor is seen as [outer][axis][inner]; the scale
+// index of an element follows the reference's loops (per channel: the channel; per group: outer * groups +
+// channel / group_size).  Minimum and maximum are order-independent, everything else is per element, so the
+// reference's bytes come out whatever the thread order.
+struct QtGeom {
+    int64_t total, axis_size, inner, ngroups;
+    int gran, gs, int4;
+};
+
+static __device__ __forceinline__ int64_t qt_scale_index(const QtGeom &g, int64_t flat)
+{
+    if (g.gran == 0) return 0;
+    const int64_t block = g.axis_size * g.inner;
+    const int64_t o = flat / block, ch = (flat - o * block) / g.inner;
+    return g.gran == 1 ? ch : o * g.ngroups + ch / g.gs;
+}
+
+// doubles as keys whose unsigned order is the numeric order (for atomicMin / atomicMax)
+static __device__ __forceinline__ unsigned long long dkey(double v)
+{
+    const unsigned long long b = (unsigned long long)__double_as_longlong(v);
+    return (b >> 63) ? ~b : (b | 0x8000000000000000ull);
+}
+static __device__ __forceinline__ double dunkey(unsigned long long k)
+{
+    return __longlong_as_double((long long)((k >> 63) ? (k & 0x7fffffffffffffffull) : ~k));
+}
+
+__global__ void qt_init_minmax_kernel(unsigned long long *mn, unsigned long long *mx, int64_t n)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { mn[i] = dkey(INFINITY); mx[i] = dkey(-INFINITY); }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) qt_minmax_kernel(const T *__restrict__ src, QtGeom g, unsigned long long *mn, unsigned long long *mx)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < g.total; i += (int64_t)gridDim.x * blockDim.x) {
+        const double v = (double)src[i];
+        if (v != v) continue;                       // the reference's comparisons never let a NaN win
+        const int64_t si = qt_scale_index(g, i);
+        atomicMin(mn + si, dkey(v));
+        atomicMax(mx + si, dkey(v));
+    }
+}
+
+__global__ void qt_scale_zp_kernel(const unsigned long long *mn_k, const unsigned long long *mx_k, int64_t n, double qmax,
+                                   float *__restrict__ scale_out, uint8_t *__restrict__ zp_out)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const double qmin = 0.0, mn = dunkey(mn_k[i]), mx = dunkey(mx_k[i]);
+    const double range = mx - mn;
+    if (range < 1e-7) {                             // quantize.rs:236-248: constant group
+        const double mid_q = round((qmin + qmax) / 2.0);
+        const double abs_val = fmax(fabs(mn), 1e-7);
+        const double sc = abs_val / mid_q;
+        zp_out[i] = (uint8_t)sat_u8(clampd(round(mid_q - mn / sc), qmin, qmax));
+        scale_out[i] = (float)sc;
+    } else {
+        const double sc = range / (qmax - qmin);
+        zp_out[i] = (uint8_t)sat_u8(clampd(round(-mn / sc), qmin, qmax));
+        scale_out[i] = (float)sc;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) qt_quantize_kernel(const T *__restrict__ src, QtGeom g, const float *__restrict__ scale,
+                                                          const uint8_t *__restrict__ zp, uint8_t *__restrict__ data)
+{
+    const double qmax = g.int4 ? 15.0 : 255.0;
+    const int64_t nbytes = g.int4 ? (g.total + 1) / 2 : g.total;
+    for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < nbytes; b += (int64_t)gridDim.x * blockDim.x) {
+        uint32_t out = 0;
+        const int per = g.int4 ? 2 : 1;
+        for (int e = 0; e < per; ++e) {
+            const int64_t i = b * per + e;
+            if (i >= g.total) break;
+            const int64_t si = qt_scale_index(g, i);
+            const uint32_t q = sat_u8(clampd(round((double)src[i] / (double)scale[si] + (double)zp[si]), 0.0, qmax));
+            out |= g.int4 ? ((q & 15u) << (4 * e)) : q;
+        }
+        data[b] = (uint8_t)out;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) qt_dequantize_kernel(const uint8_t *__restrict__ data, QtGeom g, const float *__restrict__ scale,
+                                                            const uint8_t *__restrict__ zp, T *__restrict__ out)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < g.total; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t q = g.int4 ? ((i & 1) ? (data[i >> 1] >> 4) : (data[i >> 1] & 15u)) : data[i];
+        const int64_t si = qt_scale_index(g, i);
+        out[i] = (T)(((double)q - (double)zp[si]) * (double)scale[si]);     // quantize.rs:263-266, f64
+    }
+}
+
+// *nscales = the length the reference gives scale and zero_point (compute_num_scales, quantize.rs:72-96: for
+// per-group it multiplies every other dimension, the inner ones too); *nused = the entries its loops write
+// (outer * groups, quantize.rs:375-420).  The entries past *nused are zero here (the reference leaves the
+// scales there uninitialised and the zero points 0).
+static int qt_geometry(const char *who, const int64_t *shape, int ndim, int dtype, int gran, int axis, int64_t gs, QtGeom *g, int64_t *nscales,
+                       int64_t *nused)
+{
+    if (!shape || ndim <= 0 || ndim > 8) return fail(NSLQ_ERR_SHAPE, "%s: ndim=%d (1..8)", who, ndim);
+    if (dtype != 0 && dtype != 1) return fail(NSLQ_ERR_ARG, "%s: unknown quantization dtype %d", who, dtype);
+    if (gran < 0 || gran > 2) return fail(NSLQ_ERR_ARG, "%s: unknown quantization granularity %d", who, gran);
+    if (gran != 0 && (axis < 0 || axis >= ndim)) return fail(NSLQ_ERR_ARG, "%s: axis %d of a %d-dimensional tensor", who, axis, ndim);
+    if (gran == 2 && gs <= 0) return fail(NSLQ_ERR_ARG, "%s: group size %lld", who, (long long)gs);
+    int64_t total = 1;
+    for (int i = 0; i < ndim; ++i) { if (shape[i] <= 0) return fail(NSLQ_ERR_SHAPE, "%s: dimension %d is %lld", who, i, (long long)shape[i]); total *= shape[i]; }
+    g->total = total; g->gran = gran; g->int4 = dtype == 1; g->gs = gran == 2 ? (int)gs : 1;
+    g->axis_size = gran ? shape[axis] : total; g->inner = 1;
+    for (int d = axis + 1; gran && d < ndim; ++d) g->inner *= shape[d];
+    g->ngroups = gran == 2 ? (g->axis_size + gs - 1) / gs : 1;
+    const int64_t outer = gran ? total / (g->axis_size * g->inner) : 1;
+    *nused = gran == 0 ? 1 : (gran == 1 ? g->axis_size : outer * g->ngroups);
+    *nscales = gran == 2 ? (total / g->axis_size) * g->ngroups : *nused;
+    return NSLQ_OK;
+}
+
+int qtensor_quantize_dispatch(const void *src, int src_dtype, const int64_t *shape, int ndim, int dtype, int gran, int axis, int64_t gs,
+                              uint8_t *data, float *scale, uint8_t *zp, cudaStream_t st)
+{
+    QtGeom g;
+    int64_t ns = 0, nall = 0;
+    int rc = qt_geometry("nslq_qtensor_quantize", shape, ndim, dtype, gran, axis, gs, &g, &nall, &ns);
+    if (rc) return rc;
+    if (src_dtype != NSLQ_DTYPE_F64 && src_dtype != NSLQ_DTYPE_F32) return fail(NSLQ_ERR_ARG, "nslq_qtensor_quantize: dtype %d not in {F64,F32}", src_dtype);
+    unsigned long long *mm = nullptr;                 // load-time call: a scratch of two keys per scale
+    if (cudaMalloc(&mm, (size_t)ns * 16) != cudaSuccess) return fail(NSLQ_ERR_CUDA, "nslq_qtensor_quantize: %s", cudaGetErrorString(cudaGetLastError()));
+    const unsigned sb = (unsigned)((ns + 255) / 256);
+    const unsigned eb = (unsigned)(g.total / 256 + 1 < 4736 ? g.total / 256 + 1 : 4736);
+    if (nall > ns) {
+        cudaMemsetAsync(scale + ns, 0, (size_t)(nall - ns) * 4, st);
+        cudaMemsetAsync(zp + ns, 0, (size_t)(nall - ns), st);
+    }
+    qt_init_minmax_kernel<<<sb, 256, 0, st>>>(mm, mm + ns, ns);
+    if (src_dtype == NSLQ_DTYPE_F64) qt_minmax_kernel<double><<<eb, 256, 0, st>>>((const double *)src, g, mm, mm + ns);
+    else qt_minmax_kernel<float><<<eb, 256, 0, st>>>((const float *)src, g, mm, mm + ns);
+    qt_scale_zp_kernel<<<sb, 256, 0, st>>>(mm, mm + ns, ns, g.int4 ? 15.0 : 255.0, scale, zp);
+    if (src_dtype == NSLQ_DTYPE_F64) qt_quantize_kernel<double><<<eb, 256, 0, st>>>((const double *)src, g, scale, zp, data);
+    else qt_quantize_kernel<float><<<eb, 256, 0, st>>>((const float *)src, g, scale, zp, data);
+    rc = check_launch("qt_quantize_kernel");
+    cudaStreamSynchronize(st);
+    cudaFree(mm);
+    return rc;
+}
+
+int qtensor_dequantize_dispatch(const uint8_t *data, const float *scale, const uint8_t *zp, const int64_t *shape, int ndim, int dtype,
+                                int gran, int axis, int64_t gs, void *out, int out_dtype, cudaStream_t st)
+{
+    QtGeom g;
+    int64_t ns = 0, nall = 0;
+    int rc = qt_geometry("nslq_qtensor_dequantize", shape, ndim, dtype, gran, axis, gs, &g, &nall, &ns);
+    if (rc) return rc;
+    const unsigned eb = (unsigned)(g.total / 256 + 1 < 4736 ? g.total / 256 + 1 : 4736);
+    if (out_dtype == NSLQ_DTYPE_F64) qt_dequantize_kernel<double><<<eb, 256, 0, st>>>(data, g, scale, zp, (double *)out);
+    else if (out_dtype == NSLQ_DTYPE_F32) qt_dequantize_kernel<float><<<eb, 256, 0, st>>>(data, g, scale, zp, (float *)out);
+    else return fail(NSLQ_ERR_ARG, "nslq_qtensor_dequantize: out dtype %d not in {F64,F32}", out_dtype);
+    return check_launch("qt_dequantize_kernel");
+}
+
+int64_t qtensor_num_scales(const int64_t *shape, int ndim, int gran, int axis, int64_t gs)
+{
+    QtGeom g;
+    int64_t ns = 0, nall = 0;
+    return qt_geometry("nslq_qtensor_num_scales", shape, ndim, 0, gran, axis, gs, &g, &nall, &ns) == NSLQ_OK ? nall : -1;
+}
+
 }  // namespace nslq

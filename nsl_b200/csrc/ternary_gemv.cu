@@ -28,6 +28,7 @@
 // Also here: a scalar kernel for shapes the streaming kernel cannot take
 // (K % 64 != 0 or unaligned rows); same arithmetic, natural-order activations.
 #include "quant_core.cuh"
+#include "rmsnorm_core.cuh"
 #include "sm100_common.cuh"
 #include "ternary_mma.cuh"
 
@@ -325,7 +326,36 @@ struct BulkParams {
     int M, y_dtype;
     float weight_scale;
     uint32_t pat;          // 8 nibbles: piece of lane t in sub-step 0 (nibbles 0-3) and 1 (nibbles 4-7)
+    // What the token rows are made of before they are quantised (the launches in front of a decode
+    // projection, done by every CTA for itself instead):
+    //   SRC_PLAIN    x
+    //   SRC_RMSNORM  (f32)(x / rms * norm_w), rms = sqrt(mean x^2 + eps) in f64  (nslq_rmsnorm_act_quant_i8)
+    //   SRC_SWIGLU   silu(x) * x2 in fp32                                        (nslq_swiglu_act_quant_i8)
+    int src;               // (a template argument of the kernels; kept here for the dispatch)
+    const void *x2;        // [M][K], SRC_SWIGLU
+    const float *norm_w;   // [K], SRC_RMSNORM
+    double eps, inv_k;     // inv_k = 1.0 / K
 };
+enum { SRC_PLAIN = 0, SRC_RMSNORM = 1, SRC_SWIGLU = 2 };
+
+// Group gi of token m before normalisation: x, or silu(x) * x2.
+template <typename T, int SRC>
+static __device__ __forceinline__ void src_load(const BulkParams &p, int m, int gi, float (&f)[16])
+{
+    Group16<T>::load(reinterpret_cast<const T *>(p.x) + (int64_t)m * p.K, gi, f);
+    if (SRC == SRC_SWIGLU) {
+        float u[16];
+        Group16<T>::load(reinterpret_cast<const T *>(p.x2) + (int64_t)m * p.K, gi, u);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) f[e] = swiglu_one(f[e], u[e]);
+    }
+}
+
+static __device__ __forceinline__ void ffsq16(FF &a, const float (&f)[16], bool &bad)
+{
+#pragma unroll
+    for (int e = 0; e < 16; ++e) ff_add_sq(a, f[e], bad);
+}
 
 constexpr int BULK_THREADS = 256;
 constexpr int BULK_QPIECE = 80;       // bytes between consecutive 64-k pieces of a quantised row
@@ -344,6 +374,92 @@ static __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, 
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
+// SRC_RMSNORM / SRC_SWIGLU: form, measure and quantise token row m.  The formed row is staged in shared
+// memory (h_s, K floats; every thread reads back only the groups it wrote) so that each transform exists
+// once, in a rolled loop: kept in registers and unrolled, the prologue was several thousand instructions that
+// a CTA executes exactly once, and fetching them cost more than executing them.
+// part_d / part_f / part_i: [NW][FUSED_MAX_M] partials of the warps; the caller synchronises after the last row.
+// put(q, gi, sum) packs a quantised group into the kernel's own layout.
+template <typename T, int SRC, int NW, typename Put>
+static __device__ __forceinline__ void src_quantise_row(const BulkParams &p, int m, float *h_s, double *part_d, float *part_f,
+                                                        int *part_i, Put put)
+{
+    constexpr int NTHR = NW * 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ngroups = (int)(p.K >> 4);
+    float mx = 0.0f;
+    FF a{0.0f, 0.0f};
+    bool bad = false;
+#pragma unroll 1
+    for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
+        float f[16];
+        src_load<T, SRC>(p, m, gi, f);
+        if (SRC == SRC_RMSNORM) ffsq16(a, f, bad); else mx = absmax16(f, mx);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) reinterpret_cast<float4 *>(h_s)[4 * gi + j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+    }
+    if (SRC == SRC_RMSNORM) {
+        a = ff_warp_sum(a, __any_sync(0xffffffffu, bad));
+        if (lane == 0) part_d[warp * FUSED_MAX_M + m] = (double)a.h + (double)a.l;
+        __syncthreads();
+        double tot = sum_partials<NW>(part_d + m, FUSED_MAX_M);
+        if (!(tot <= 3.5e38)) {                               // CTA-uniform: a row out of the fp32 path's range, f64 throughout
+            double sq = 0.0;
+#pragma unroll 1
+            for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 v = reinterpret_cast<const float4 *>(h_s)[4 * gi + j];
+                    sq += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            __syncthreads();
+            if (lane == 0) part_d[warp * FUSED_MAX_M + m] = sq;
+            __syncthreads();
+            tot = sum_partials<NW>(part_d + m, FUSED_MAX_M);
+        }
+        const RmsScale rs = rms_scale(tot, (double)p.K, p.inv_k, p.eps);
+#pragma unroll 1
+        for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float4 v = reinterpret_cast<const float4 *>(h_s)[4 * gi + j];
+                const float4 w = __ldg(reinterpret_cast<const float4 *>(p.norm_w) + 4 * gi + j);
+                v.x = norm_ff(v.x, w.x, rs); v.y = norm_ff(v.y, w.y, rs); v.z = norm_ff(v.z, w.z, rs); v.w = norm_ff(v.w, w.w, rs);
+                mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                reinterpret_cast<float4 *>(h_s)[4 * gi + j] = v;
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) part_f[warp * FUSED_MAX_M + m] = mx;
+    __syncthreads();
+    float scale = 0.0f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) scale = fmaxf(scale, part_f[w * FUSED_MAX_M + m]);
+    const float inv = __fdiv_rn(127.0f, scale);
+    const bool fast = inv < INFINITY;                         // CTA-uniform; false for inf and NaN
+    int sum = 0;
+#pragma unroll 1
+    for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
+        float f[16];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float4 v = reinterpret_cast<const float4 *>(h_s)[4 * gi + j];
+            f[4 * j] = v.x; f[4 * j + 1] = v.y; f[4 * j + 2] = v.z; f[4 * j + 3] = v.w;
+        }
+        int q[16];
+        if (fast) quant16<true>(f, inv, q); else quant16<false>(f, inv, q);
+        put(q, gi, sum);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) part_i[warp * FUSED_MAX_M + m] = sum;
+}
+
 // The same CTA with the products on the integer ALUs (dp4a) instead of mma.sync: the form used for
 // one and two tokens.  Measured on this part: with eight warps and at most sixteen accumulator
 // chains per warp the mma.sync form spends 1.5-2 us multiplying a 64-row slab (one sub-step of
@@ -356,7 +472,7 @@ static __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, 
 // and then, per row, one 4-byte word of weights -- a warp reads 128 consecutive bytes of a row, so
 // the unpadded slab is conflict-free -- and per class one AND (w & (0x03030303 << 2i) = the four
 // codes of the class, scaled by 4^i) and one dp4a.u32.s32.  Row sums are reduced by shuffles.
-template <typename T, int ROWS, int MT>
+template <typename T, int ROWS, int MT, int SRC>
 __global__ void __launch_bounds__(BULK_THREADS, 3)
 ternary_gemv_bulk_dp4a_kernel(const BulkParams p)
 {
@@ -375,6 +491,7 @@ ternary_gemv_bulk_dp4a_kernel(const BulkParams p)
     float *part_f = reinterpret_cast<float *>(red + 8 * 32 * 4);          // [8][FUSED_MAX_M]
     int *part_i = reinterpret_cast<int *>(part_f + 8 * FUSED_MAX_M);      // [8][FUSED_MAX_M]
     uint64_t *bars = reinterpret_cast<uint64_t *>(part_i + 8 * FUSED_MAX_M);   // [RT]
+    double *part_d = reinterpret_cast<double *>(bars + 4);                // [8][FUSED_MAX_M]
     const int64_t n0 = (int64_t)blockIdx.x * ROWS;
 
     if (threadIdx.x == 0) {
@@ -399,62 +516,78 @@ ternary_gemv_bulk_dp4a_kernel(const BulkParams p)
     // this grid's own -- while a late one still hides their launch and prefetch under this grid's tail.)
     pdl_wait();
 
-    // ---- quantise the token rows (registers hold a thread's groups between the two passes)
-    const T *x = reinterpret_cast<const T *>(p.x);
+    // ---- quantise the token rows
     const int ngroups = (int)(p.K >> 4);
-    constexpr int XG = MT == 1 ? 2 : 1;                       // groups per thread and token kept in registers
-    float xv[MT][XG][16];
-#pragma unroll
-    for (int m = 0; m < MT; ++m) {
-        float mx = 0.0f;
-        if (m < p.M) {
-#pragma unroll
-            for (int i = 0; i < XG; ++i) {
-                const int gi = i * BULK_THREADS + threadIdx.x;
-                if (gi < ngroups) { Group16<T>::load(x + (int64_t)m * p.K, gi, xv[m][i]); mx = absmax16(xv[m][i], mx); }
-            }
-            for (int gi = XG * BULK_THREADS + threadIdx.x; gi < ngroups; gi += BULK_THREADS) {
-                float f[16];
-                Group16<T>::load(x + (int64_t)m * p.K, gi, f);
-                mx = absmax16(f, mx);
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) part_f[warp * FUSED_MAX_M + m] = mx;
-    }
-    __syncthreads();                                          // also publishes the barrier initialisation
     float scale[MT];
+    if (SRC == SRC_PLAIN) {                                   // registers hold a thread's groups between the two passes
+        const T *x = reinterpret_cast<const T *>(p.x);
+        constexpr int XG = MT == 1 ? 2 : 1;                   // groups per thread and token kept in registers
+        float xv[MT][XG][16];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-        scale[m] = 0.0f;
+        for (int m = 0; m < MT; ++m) {
+            float mx = 0.0f;
+            if (m < p.M) {
 #pragma unroll
-        for (int w = 0; w < 8; ++w) scale[m] = fmaxf(scale[m], part_f[w * FUSED_MAX_M + m]);
-        int sum = 0;
-        if (m < p.M) {
-            const float inv = __fdiv_rn(127.0f, scale[m]);
-            const bool fast = inv < INFINITY;                 // CTA-uniform; false for inf and NaN
-            auto put = [&](const float (&f)[16], int gi) {
-                int q[16];
-                if (fast) quant16<true>(f, inv, q); else quant16<false>(f, inv, q);
-                *reinterpret_cast<uint4 *>(q_s + (size_t)m * qrow + (size_t)gi * 16) = pack_perm16(q, sum);
-            };
-#pragma unroll
-            for (int i = 0; i < XG; ++i) {
-                const int gi = i * BULK_THREADS + threadIdx.x;
-                if (gi < ngroups) put(xv[m][i], gi);
+                for (int i = 0; i < XG; ++i) {
+                    const int gi = i * BULK_THREADS + threadIdx.x;
+                    if (gi < ngroups) { Group16<T>::load(x + (int64_t)m * p.K, gi, xv[m][i]); mx = absmax16(xv[m][i], mx); }
+                }
+                for (int gi = XG * BULK_THREADS + threadIdx.x; gi < ngroups; gi += BULK_THREADS) {
+                    float f[16];
+                    Group16<T>::load(x + (int64_t)m * p.K, gi, f);
+                    mx = absmax16(f, mx);
+                }
             }
-            for (int gi = XG * BULK_THREADS + threadIdx.x; gi < ngroups; gi += BULK_THREADS) {
-                float f[16];
-                Group16<T>::load(x + (int64_t)m * p.K, gi, f);
-                put(f, gi);
-            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            if (lane == 0) part_f[warp * FUSED_MAX_M + m] = mx;
         }
+        __syncthreads();                                      // also publishes the barrier initialisation
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if (lane == 0) part_i[warp * FUSED_MAX_M + m] = sum;
+        for (int m = 0; m < MT; ++m) {
+            scale[m] = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) scale[m] = fmaxf(scale[m], part_f[w * FUSED_MAX_M + m]);
+            int sum = 0;
+            if (m < p.M) {
+                const float inv = __fdiv_rn(127.0f, scale[m]);
+                const bool fast = inv < INFINITY;             // CTA-uniform; false for inf and NaN
+                auto put = [&](const float (&f)[16], int gi) {
+                    int q[16];
+                    if (fast) quant16<true>(f, inv, q); else quant16<false>(f, inv, q);
+                    *reinterpret_cast<uint4 *>(q_s + (size_t)m * qrow + (size_t)gi * 16) = pack_perm16(q, sum);
+                };
+#pragma unroll
+                for (int i = 0; i < XG; ++i) {
+                    const int gi = i * BULK_THREADS + threadIdx.x;
+                    if (gi < ngroups) put(xv[m][i], gi);
+                }
+                for (int gi = XG * BULK_THREADS + threadIdx.x; gi < ngroups; gi += BULK_THREADS) {
+                    float f[16];
+                    Group16<T>::load(x + (int64_t)m * p.K, gi, f);
+                    put(f, gi);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) part_i[warp * FUSED_MAX_M + m] = sum;
+        }
+        __syncthreads();
+    } else {
+        float *h_s = reinterpret_cast<float *>(part_d + 8 * FUSED_MAX_M);
+#pragma unroll 1
+        for (int m = 0; m < p.M; ++m)
+            src_quantise_row<T, SRC, 8>(p, m, h_s, part_d, part_f, part_i, [&](const int (&q)[16], int gi, int &sum) {
+                *reinterpret_cast<uint4 *>(q_s + (size_t)m * qrow + (size_t)gi * 16) = pack_perm16(q, sum);
+            });
+        __syncthreads();                                      // (the first one inside also published the barrier initialisation)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            scale[m] = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) scale[m] = fmaxf(scale[m], part_f[w * FUSED_MAX_M + m]);
+        }
     }
-    __syncthreads();
 
     // ---- multiply: warp -> rows 8*(warp / KW) .. +7, passes warp % KW, + KW, ... (32 words per pass)
     const int rset = warp / KW, kw = warp % KW;
@@ -560,7 +693,7 @@ ternary_gemv_bulk_dp4a_kernel(const BulkParams p)
 // integer work (proportional to the token count) exceeds this form's.  Measured at one token on a
 // 64-row slab of K = 3200: 2.1 us for this phase with eight warps, more with sixteen (64 registers
 // per thread then, with spills); the tensor pipe itself is busy for under half a microsecond.
-template <typename T, int ROWS, int NW>
+template <typename T, int ROWS, int NW, int SRC>
 __global__ void __launch_bounds__(NW * 32, (NW <= 8) ? 3 : 2)
 ternary_gemv_bulk_kernel(const BulkParams p)
 {
@@ -580,6 +713,7 @@ ternary_gemv_bulk_kernel(const BulkParams p)
     float *part_f = reinterpret_cast<float *>(red + NW * 32 * 4);         // [NW][FUSED_MAX_M]
     int *part_i = reinterpret_cast<int *>(part_f + NW * FUSED_MAX_M);     // [NW][FUSED_MAX_M]
     uint64_t *bars = reinterpret_cast<uint64_t *>(part_i + NW * FUSED_MAX_M);  // [RT]
+    double *part_d = reinterpret_cast<double *>(bars + 4);                // [NW][FUSED_MAX_M]
     const int64_t n0 = (int64_t)blockIdx.x * ROWS;
 
     if (threadIdx.x == 0) {
@@ -607,37 +741,46 @@ ternary_gemv_bulk_kernel(const BulkParams p)
     // owns whole groups of 16 consecutive elements: they become the four words of the consumption order
     // with no exchange between threads.  The row is read twice (maximum, then rounding); the second
     // read hits the L1 cache.
-    const T *x = reinterpret_cast<const T *>(p.x);
-    const int ngroups = (int)(p.K >> 4);
-    for (int m = 0; m < p.M; ++m) {
-        float mx = 0.0f;
-        for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
-            float f[16];
-            Group16<T>::load(x + (int64_t)m * p.K, gi, f);
-            mx = absmax16(f, mx);
+    if (SRC == SRC_PLAIN) {
+        const T *x = reinterpret_cast<const T *>(p.x);
+        const int ngroups = (int)(p.K >> 4);
+        for (int m = 0; m < p.M; ++m) {
+            float mx = 0.0f;
+            for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
+                float f[16];
+                Group16<T>::load(x + (int64_t)m * p.K, gi, f);
+                mx = absmax16(f, mx);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            if (lane == 0) part_f[warp * FUSED_MAX_M + m] = mx;
         }
+        __syncthreads();                                      // also publishes the barrier initialisation
+        for (int m = 0; m < p.M; ++m) {
+            float scale = 0.0f;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) part_f[warp * FUSED_MAX_M + m] = mx;
-    }
-    __syncthreads();                                          // also publishes the barrier initialisation
-    for (int m = 0; m < p.M; ++m) {
-        float scale = 0.0f;
+            for (int w = 0; w < NW; ++w) scale = fmaxf(scale, part_f[w * FUSED_MAX_M + m]);
+            const float inv = __fdiv_rn(127.0f, scale);
+            const bool fast = inv < INFINITY;                 // CTA-uniform; false for inf and NaN
+            int sum = 0;
+            for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
+                float f[16];
+                Group16<T>::load(x + (int64_t)m * p.K, gi, f);
+                int q[16];
+                if (fast) quant16<true>(f, inv, q); else quant16<false>(f, inv, q);
+                *reinterpret_cast<uint4 *>(q_s + (size_t)m * qrow + (gi >> 2) * BULK_QPIECE + (gi & 3) * 16) = pack_perm16(q, sum);
+            }
 #pragma unroll
-        for (int w = 0; w < NW; ++w) scale = fmaxf(scale, part_f[w * FUSED_MAX_M + m]);
-        const float inv = __fdiv_rn(127.0f, scale);
-        const bool fast = inv < INFINITY;                     // CTA-uniform; false for inf and NaN
-        int sum = 0;
-        for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
-            float f[16];
-            Group16<T>::load(x + (int64_t)m * p.K, gi, f);
-            int q[16];
-            if (fast) quant16<true>(f, inv, q); else quant16<false>(f, inv, q);
-            *reinterpret_cast<uint4 *>(q_s + (size_t)m * qrow + (gi >> 2) * BULK_QPIECE + (gi & 3) * 16) = pack_perm16(q, sum);
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) part_i[warp * FUSED_MAX_M + m] = sum;
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if (lane == 0) part_i[warp * FUSED_MAX_M + m] = sum;
+    } else {
+        float *h_s = reinterpret_cast<float *>(part_d + NW * FUSED_MAX_M);
+#pragma unroll 1
+        for (int m = 0; m < p.M; ++m)
+            src_quantise_row<T, SRC, NW>(p, m, h_s, part_d, part_f, part_i, [&](const int (&q)[16], int gi, int &sum) {
+                *reinterpret_cast<uint4 *>(q_s + (size_t)m * qrow + (gi >> 2) * BULK_QPIECE + (gi & 3) * 16) = pack_perm16(q, sum);
+            });
     }
     __syncthreads();
 
@@ -811,66 +954,75 @@ static int bulk_rows(int64_t K)
 
 constexpr int BULK_MMA_WARPS = 8;
 
-static size_t bulk_smem(int rows, int M, int64_t K, int nw = 8)
+static size_t bulk_smem(int rows, int M, int64_t K, int nw = 8, bool staged_row = false)
 {
     const size_t qrow = (size_t)(K / 64) * BULK_QPIECE;
-    return (size_t)rows * (K / 4) + (((size_t)M * qrow + 15) & ~(size_t)15) + (size_t)nw * 32 * 4 * 4 + (size_t)nw * FUSED_MAX_M * 8 + 4 * 8 + 64;
+    return (size_t)rows * (K / 4) + (((size_t)M * qrow + 15) & ~(size_t)15) + (size_t)nw * 32 * 4 * 4 + (size_t)nw * FUSED_MAX_M * 8 + 4 * 8 +
+           (size_t)nw * FUSED_MAX_M * 8 + (staged_row ? (size_t)K * 4 : 0) + 64;
 }
 
-template <typename T, int ROWS>
+template <typename T, int ROWS, int SRC>
 static int launch_bulk(const BulkParams &p, cudaStream_t st)
 {
     constexpr int NW = BULK_MMA_WARPS;
-    const size_t smem = bulk_smem(ROWS, p.M, p.K, NW);
+    const size_t smem = bulk_smem(ROWS, p.M, p.K, NW, SRC != SRC_PLAIN);
     static std::atomic<size_t> reserved[kMaxDevices];
     static std::atomic<int> carved[kMaxDevices];
     if (!carved[device_index()].load(std::memory_order_acquire)) {
         // Several CTAs of this kernel (and of the next call) must fit an SM side by side, each with its slab in
         // shared memory: ask for the largest shared-memory carve-out instead of the one sized for a single CTA.
-        cudaFuncSetAttribute(ternary_gemv_bulk_kernel<T, ROWS, NW>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(ternary_gemv_bulk_kernel<T, ROWS, NW, SRC>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         carved[device_index()].store(1, std::memory_order_release);
     }
-    if (reserve_smem(ternary_gemv_bulk_kernel<T, ROWS, NW>, reserved, smem) != cudaSuccess)
+    if (reserve_smem(ternary_gemv_bulk_kernel<T, ROWS, NW, SRC>, reserved, smem) != cudaSuccess)
         return fail(NSLQ_ERR_CUDA, "ternary_gemv_bulk_kernel: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(cudaGetLastError()));
     const unsigned ctas = (unsigned)((p.N + ROWS - 1) / ROWS);
-    cudaError_t e = launch_kernel(ternary_gemv_bulk_kernel<T, ROWS, NW>, dim3(ctas), dim3(NW * 32), smem, st, p);
+    cudaError_t e = launch_kernel(ternary_gemv_bulk_kernel<T, ROWS, NW, SRC>, dim3(ctas), dim3(NW * 32), smem, st, p);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "ternary_gemv_bulk_kernel: %s", cudaGetErrorString(e));
     return check_launch("ternary_gemv_bulk_kernel");
 }
 
-template <typename T, int ROWS, int MT>
+template <typename T, int ROWS, int MT, int SRC>
 static int launch_bulk_dp4a(const BulkParams &p, cudaStream_t st)
 {
-    const size_t smem = bulk_smem(ROWS, p.M, p.K);
+    const size_t smem = bulk_smem(ROWS, p.M, p.K, 8, SRC != SRC_PLAIN);
     static std::atomic<size_t> reserved[kMaxDevices];
     static std::atomic<int> carved[kMaxDevices];
     if (!carved[device_index()].load(std::memory_order_acquire)) {
-        cudaFuncSetAttribute(ternary_gemv_bulk_dp4a_kernel<T, ROWS, MT>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(ternary_gemv_bulk_dp4a_kernel<T, ROWS, MT, SRC>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         carved[device_index()].store(1, std::memory_order_release);
     }
-    if (reserve_smem(ternary_gemv_bulk_dp4a_kernel<T, ROWS, MT>, reserved, smem) != cudaSuccess)
+    if (reserve_smem(ternary_gemv_bulk_dp4a_kernel<T, ROWS, MT, SRC>, reserved, smem) != cudaSuccess)
         return fail(NSLQ_ERR_CUDA, "ternary_gemv_bulk_dp4a_kernel: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(cudaGetLastError()));
     const unsigned ctas = (unsigned)((p.N + ROWS - 1) / ROWS);
-    cudaError_t e = launch_kernel(ternary_gemv_bulk_dp4a_kernel<T, ROWS, MT>, dim3(ctas), dim3(BULK_THREADS), smem, st, p);
+    cudaError_t e = launch_kernel(ternary_gemv_bulk_dp4a_kernel<T, ROWS, MT, SRC>, dim3(ctas), dim3(BULK_THREADS), smem, st, p);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "ternary_gemv_bulk_dp4a_kernel: %s", cudaGetErrorString(e));
     return check_launch("ternary_gemv_bulk_dp4a_kernel");
+}
+
+template <typename T, int SRC>
+static int pick_bulk_src(const BulkParams &p, cudaStream_t st)
+{
+    if (p.M <= 2) {                      // one or two tokens: integer ALUs (see the kernel's comment)
+        if (bulk_rows(p.K) == 64) return p.M == 1 ? launch_bulk_dp4a<T, 64, 1, SRC>(p, st) : launch_bulk_dp4a<T, 64, 2, SRC>(p, st);
+        return p.M == 1 ? launch_bulk_dp4a<T, 32, 1, SRC>(p, st) : launch_bulk_dp4a<T, 32, 2, SRC>(p, st);
+    }
+    return bulk_rows(p.K) == 64 ? launch_bulk<T, 64, SRC>(p, st) : launch_bulk<T, 32, SRC>(p, st);
 }
 
 template <typename T>
 static int pick_bulk(const BulkParams &p, cudaStream_t st)
 {
-    if (p.M <= 2) {                      // one or two tokens: integer ALUs (see the kernel's comment)
-        if (bulk_rows(p.K) == 64) return p.M == 1 ? launch_bulk_dp4a<T, 64, 1>(p, st) : launch_bulk_dp4a<T, 64, 2>(p, st);
-        return p.M == 1 ? launch_bulk_dp4a<T, 32, 1>(p, st) : launch_bulk_dp4a<T, 32, 2>(p, st);
-    }
-    return bulk_rows(p.K) == 64 ? launch_bulk<T, 64>(p, st) : launch_bulk<T, 32>(p, st);
+    if (p.src == SRC_RMSNORM) return pick_bulk_src<T, SRC_RMSNORM>(p, st);
+    if (p.src == SRC_SWIGLU) return pick_bulk_src<T, SRC_SWIGLU>(p, st);
+    return pick_bulk_src<T, SRC_PLAIN>(p, st);
 }
 
 // The bulk-copy kernel takes the call when the slab of its CTA and the quantised rows fit shared memory.
-static bool bulk_supported(int M, int64_t K)
+static bool bulk_supported(int M, int64_t K, bool staged_row = false)
 {
     const int rows = bulk_rows(K);
-    return rows != 0 && bulk_smem(rows, M, K, BULK_MMA_WARPS) <= 160 * 1024;
+    return rows != 0 && bulk_smem(rows, M, K, BULK_MMA_WARPS, staged_row) <= 160 * 1024;
 }
 
 int ternary_gemv_status(int *out) { return sm100::read_wait_status(out); }
@@ -881,18 +1033,39 @@ bool ternary_gemv_fused_supported(const void *w, const void *x, int64_t M, int64
     return M >= 1 && M <= FUSED_MAX_M && (K % 64 == 0) && aligned16(w) && aligned16(x) && M * K <= 160 * 1024;
 }
 
+static int bulk_by_dtype(const BulkParams &b, int x_dtype, cudaStream_t st)
+{
+    switch (x_dtype) {
+    case NSLQ_DTYPE_F32: return pick_bulk<float>(b, st);
+    case NSLQ_DTYPE_FP16: return pick_bulk<__half>(b, st);
+    case NSLQ_DTYPE_BF16: return pick_bulk<__nv_bfloat16>(b, st);
+    default: return fail(NSLQ_ERR_ARG, "BitLinear: x_dtype %d not in {F32,FP16,BF16}", x_dtype);
+    }
+}
+
+// Up to four token rows whose RMSNorm (norm_w != null) or SiLU(x) * x2 (x2 != null) the CTAs form for themselves.
+bool ternary_gemv_src_supported(const void *w, const void *x, const void *x2, const float *norm_w, int64_t M, int64_t K)
+{
+    return M >= 1 && M <= FUSED_MAX_M && (K % 64 == 0) && aligned16(w) && aligned16(x) && (!x2 || aligned16(x2)) &&
+           (!norm_w || aligned16(norm_w)) && bulk_supported((int)M, K, true);
+}
+
+int ternary_gemv_src_dispatch(const uint8_t *w, const void *x, const void *x2, const float *norm_w, double eps, int x_dtype,
+                              int M, int64_t N, int64_t K, float weight_scale, void *y, int y_dtype, int32_t *acc_out,
+                              const float *bias, const float *residual, cudaStream_t st)
+{
+    BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale, bulk_pattern(K / 4),
+                 norm_w ? SRC_RMSNORM : (x2 ? SRC_SWIGLU : SRC_PLAIN), x2, norm_w, eps, 1.0 / (double)K};
+    return bulk_by_dtype(b, x_dtype, st);
+}
+
 int ternary_gemv_fused_dispatch(const uint8_t *w, const void *x, int x_dtype, int M, int64_t N, int64_t K,
                                 float weight_scale, void *y, int y_dtype, int32_t *acc_out, const float *bias,
                                 const float *residual, cudaStream_t st)
 {
     if (bulk_supported(M, K)) {
-        BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale, bulk_pattern(K / 4)};
-        switch (x_dtype) {
-        case NSLQ_DTYPE_F32: return pick_bulk<float>(b, st);
-        case NSLQ_DTYPE_FP16: return pick_bulk<__half>(b, st);
-        case NSLQ_DTYPE_BF16: return pick_bulk<__nv_bfloat16>(b, st);
-        default: return fail(NSLQ_ERR_ARG, "BitLinear: x_dtype %d not in {F32,FP16,BF16}", x_dtype);
-        }
+        BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale, bulk_pattern(K / 4), SRC_PLAIN, nullptr, nullptr, 0.0, 0.0};
+        return bulk_by_dtype(b, x_dtype, st);
     }
     FusedParams p{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale};
     switch (x_dtype) {

@@ -1,12 +1,15 @@
 """Decoder harness for the model-shaped workloads of the benchmark (BitNet b1.58-3B shape).
 
-Everything that is NOT a quantized linear -- embedding, RMSNorm, RoPE, attention over the KV
-cache at prefill, greedy sampling, the bf16 lm_head -- is plain PyTorch, on purpose: those pieces are outside
-the quantized-linear path this library replaces (NSL has them in stdlib/nsl/nn/{norms,rope,gqa}.nsl
-and stdlib/nsl/inference/generate.nsl).  Every projection of every layer (q, k, v, o, gate, up,
-down) runs through nsl_b200.ops.BitLinear, i.e. the C ABI; in a decode step the RMSNorms in front of
-them and the attention of the new token (RoPE, cache append, softmax(qK)V) are library launches too
-(nslq_rmsnorm_act_quant_i8, nslq_decode_attention).  Weights are random ternary (no
+At prefill, everything that is NOT a quantized linear -- embedding, RoPE, attention over the prompt, the
+bf16 lm_head -- is plain PyTorch, on purpose: those pieces are outside the quantized-linear path this
+library replaces (NSL has them in stdlib/nsl/nn/{norms,rope,gqa}.nsl and
+stdlib/nsl/inference/generate.nsl).  Every projection of every layer (q, k, v, o, gate, up, down) runs
+through nsl_b200.ops.BitLinear, i.e. the C ABI.  A decode step is library launches throughout, the
+lm_head's bf16 GEMM aside: the embedding rows (nslq_embed_gather), the RMSNorms (inside the projections'
+launches up to four tokens, nslq_rmsnorm_act_quant_i8 above), the attention of the new token (RoPE, cache
+append, softmax(qK)V: nslq_decode_attention), SiLU(gate)*up (inside the down projection's launch up to
+four tokens), the final norm (nslq_rmsnorm_rows) and the greedy choice (nslq_argmax_rows, which also
+advances the position).  Weights are random ternary (no
 checkpoint is available offline), so the numbers are throughput numbers, not quality numbers.
 
 The residual stream is kept in fp32: the norms then need no casts, and the residual additions ride
@@ -115,17 +118,20 @@ class BitNetDecoder:
 
     def _swiglu_down(self, layer, g, u, residual):
         """down(silu(gate) * up) + residual: one launch forms and quantises the product, one multiplies."""
+        if g.shape[0] <= 4:               # a decode step of a few tokens: the product is formed inside the projection's launch
+            return layer.forward_swiglu(g, u, out_dtype=torch.float32, residual=residual)
         qa = ops.swiglu_act_quant_i8(g, u, plain=False, perm=True)
         return layer.forward_quantized(qa, out_dtype=torch.float32, residual=residual)
 
     def _norm_lin_shared(self, layers, x2d, norm_w):
         """RMSNorm, then several projections of the normalised rows.  More than four rows: one
         launch normalises and quantises (the normalised rows never reach memory) and the
-        projections share the result; four or fewer: the decode kernel quantises for itself."""
+        projections share the result; four or fewer: every projection's launch normalises and
+        quantises for itself (nslq_bitlinear_forward_rmsnorm), so the norm is no launch at all."""
         M = x2d.shape[0]
         if M <= 4:
-            hn = _rms_norm(x2d, norm_w, self.cfg.eps)
-            return self._siblings([lambda l=l: l.forward(hn, out_dtype=torch.bfloat16) for l in layers])
+            eps = self.cfg.eps
+            return self._siblings([lambda l=l: l.forward_rmsnorm(x2d, norm_w, eps, out_dtype=torch.bfloat16) for l in layers])
         qa = ops.rmsnorm_act_quant_i8(x2d, norm_w, self.cfg.eps, plain=False, perm=True)
         return self._siblings([lambda l=l: l.forward_quantized(qa, out_dtype=torch.bfloat16) for l in layers])
 
@@ -156,12 +162,11 @@ class BitNetDecoder:
     def _step(self):
         cfg, B = self.cfg, self.B
         self.fork = bool(self.side)
-        x = self.embed[self.tokens].float()                               # [B, h] residual stream, fp32
+        x = ops.embed_gather(self.embed, self.tokens)                     # [B, h] residual stream, fp32
         for li in range(len(self.layers)):
             x = self.decode_layer(li, x)
-        logits = _rms_norm(x, self.final_norm, cfg.eps).to(torch.bfloat16) @ self.lm_head.t()
-        self.tokens.copy_(logits.argmax(-1))
-        self.pos.add_(1)
+        logits = ops.rmsnorm_rows(x, self.final_norm, cfg.eps, out_dtype=torch.bfloat16) @ self.lm_head.t()
+        ops.argmax_rows(logits, out=self.tokens, counter=self.pos)       # next tokens, and the position moves on
         self.fork = False
 
     def decode_layer(self, li, x):

@@ -123,6 +123,35 @@ def decode_attention(q, k_new, v_new, k_cache, v_cache, cos_table, sin_table, po
     return out
 
 
+def embed_gather(table, tokens, out=None):
+    """fp32 rows of `table` [V, H] for int64 `tokens` [B] (nslq_embed_gather)."""
+    if not (table.is_cuda and table.is_contiguous() and table.dim() == 2 and tokens.dtype == torch.int64 and tokens.is_contiguous()):
+        raise ValueError("table: contiguous CUDA [V, H]; tokens: contiguous int64")
+    B = tokens.numel()
+    out = out if out is not None else torch.empty(B, table.shape[1], dtype=torch.float32, device=table.device)
+    check(lib().nslq_embed_gather(_ptr(table), _tag(table.dtype), table.shape[0], table.shape[1], _ptr(tokens), B, _ptr(out), _stream()))
+    return out
+
+
+def rmsnorm_rows(x, weight, eps=1e-5, out_dtype=torch.float32, out=None):
+    """RMSNorm of fp32 rows with NSL's arithmetic, rounded to out_dtype (nslq_rmsnorm_rows)."""
+    _cuda2d(x, "x")
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or weight.numel() != x.shape[1]:
+        raise ValueError("x fp32 [M, K] and an fp32 weight of K elements expected")
+    out = out if out is not None else torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    check(lib().nslq_rmsnorm_rows(_ptr(x), _ptr(weight), float(eps), x.shape[0], x.shape[1], _ptr(out), _tag(out.dtype), _stream()))
+    return out
+
+
+def argmax_rows(x, out=None, counter=None):
+    """Lowest index of each row's maximum as int64 (nslq_argmax_rows); `counter` (int64 tensor) is incremented."""
+    if not x.is_cuda or x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be a CUDA [M, V] tensor with unit column stride")
+    out = out if out is not None else torch.empty(x.shape[0], dtype=torch.int64, device=x.device)
+    check(lib().nslq_argmax_rows(_ptr(x), _tag(x.dtype), x.shape[0], x.shape[1], x.stride(0), _ptr(out), _ptr(counter), _stream()))
+    return out
+
+
 class BitLinear:
     """A ternary weight in NSL's packed layout ([out_dim, hidden_dim/4] uint8) on the GPU."""
 
@@ -169,6 +198,36 @@ class BitLinear:
         ws = workspace if workspace is not None else self.workspace(M)
         check(lib().nslq_bitlinear_forward(self._h, _ptr(x), _tag(x.dtype), M, _ptr(y), _tag(y.dtype), _ptr(acc),
                                            _ptr(bias), _ptr(residual), _ptr(ws), ws.numel(), _stream()))
+        return (y, acc) if return_acc else y
+
+    def forward_rmsnorm(self, x, norm_weight, eps=1e-5, out_dtype=torch.float32, return_acc=False, bias=None, residual=None,
+                        out=None):
+        """BitLinear(RMSNorm(x)): one launch up to four tokens (nslq_bitlinear_forward_rmsnorm)."""
+        _cuda2d(x, "x")
+        M = x.shape[0]
+        if x.shape[1] != self.K or norm_weight.numel() != self.K or norm_weight.dtype != torch.float32:
+            raise ValueError("x [M, %d] and an fp32 norm weight of %d elements expected" % (self.K, self.K))
+        y = out if out is not None else torch.empty(M, self.N, dtype=out_dtype, device=x.device)
+        acc = torch.empty(M, self.N, dtype=torch.int32, device=x.device) if return_acc else None
+        ws = self.workspace(M)            # used when the one-launch form does not take the call (more than four tokens, very wide rows)
+        check(lib().nslq_bitlinear_forward_rmsnorm(self._h, _ptr(x), _tag(x.dtype), M, _ptr(norm_weight), float(eps), _ptr(y),
+                                                   _tag(y.dtype), _ptr(acc), _ptr(bias), _ptr(residual), _ptr(ws),
+                                                   ws.numel(), _stream()))
+        return (y, acc) if return_acc else y
+
+    def forward_swiglu(self, gate, up, out_dtype=torch.float32, return_acc=False, bias=None, residual=None, out=None):
+        """BitLinear(SiLU(gate) * up): one launch up to four tokens (nslq_bitlinear_forward_swiglu)."""
+        _cuda2d(gate, "gate")
+        _cuda2d(up, "up")
+        M = gate.shape[0]
+        if gate.shape != up.shape or gate.dtype != up.dtype or gate.shape[1] != self.K:
+            raise ValueError("gate and up must both be [M, %d] of one dtype" % self.K)
+        y = out if out is not None else torch.empty(M, self.N, dtype=out_dtype, device=gate.device)
+        acc = torch.empty(M, self.N, dtype=torch.int32, device=gate.device) if return_acc else None
+        ws = self.workspace(M)            # used when the one-launch form does not take the call (more than four tokens, very wide rows)
+        check(lib().nslq_bitlinear_forward_swiglu(self._h, _ptr(gate), _ptr(up), _tag(gate.dtype), M, _ptr(y), _tag(y.dtype),
+                                                  _ptr(acc), _ptr(bias), _ptr(residual), _ptr(ws),
+                                                  ws.numel(), _stream()))
         return (y, acc) if return_acc else y
 
     def forward_noalloc(self, x, out):
@@ -300,6 +359,31 @@ def int4_quantize_nk(w, group_size):
     check(lib().nslq_int4_quantize_nk(_ptr(w), _tag(w.dtype), N, K, group_size, _ptr(codes), _ptr(scale), _ptr(zp),
                                       _stream()))
     return codes, scale, zp
+
+
+def qtensor_quantize(src, dtype, gran, axis=0, group_size=0):
+    """nsl_qtensor_quantize on the GPU: src f32/f64 CUDA tensor -> (data u8, scale f32, zero_point u8) flat tensors."""
+    if not src.is_cuda or not src.is_contiguous():
+        raise ValueError("src must be a contiguous CUDA tensor")
+    shape = (C.c_int64 * src.dim())(*src.shape)
+    ns = int(lib().nslq_qtensor_num_scales(shape, src.dim(), gran, axis, group_size))
+    if ns < 0:
+        raise ValueError(lib().nslq_last_error().decode())
+    total = src.numel()
+    data = torch.empty((total + 1) // 2 if dtype == 1 else total, dtype=torch.uint8, device=src.device)
+    scale = torch.empty(ns, dtype=torch.float32, device=src.device)
+    zp = torch.empty(ns, dtype=torch.uint8, device=src.device)
+    check(lib().nslq_qtensor_quantize(_ptr(src), _tag(src.dtype), shape, src.dim(), dtype, gran, axis, group_size,
+                                      _ptr(data), _ptr(scale), _ptr(zp), _stream()))
+    return data, scale, zp
+
+
+def qtensor_dequantize(data, scale, zp, shape, dtype, gran, axis=0, group_size=0, out_dtype=torch.float64):
+    sh = (C.c_int64 * len(shape))(*shape)
+    out = torch.empty(*shape, dtype=out_dtype, device=data.device)
+    check(lib().nslq_qtensor_dequantize(_ptr(data), _ptr(scale), _ptr(zp), sh, len(shape), dtype, gran, axis, group_size,
+                                        _ptr(out), _tag(out_dtype), _stream()))
+    return out
 
 
 def awq_quantize_kn(w, group_size):
