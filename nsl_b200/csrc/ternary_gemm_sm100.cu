@@ -69,7 +69,8 @@ template <int BT> struct Cfg {
     static constexpr int HALF_T = BT / 2;                             // tokens per epilogue warp
     static constexpr int SCALE_BYTES = 8 * HALF_T * 8;                // per epilogue warp: scale/127 and row sum per token
     static constexpr int BAR_BYTES = 512;
-    static constexpr int SMEM = TS * T_BYTES + SCALE_BYTES + BAR_BYTES + 1024;   // + alignment slack
+    static constexpr int STAGE_BYTES = 2 * 16 * 128 * 4;              // per token half: 16 tokens x 128 features of output, up to 4 bytes each
+    static constexpr int SMEM = TS * T_BYTES + SCALE_BYTES + BAR_BYTES + STAGE_BYTES + 1024;   // + alignment slack
     static_assert(SMEM <= 232448, "over the 227 KiB a CTA may use");
     static constexpr uint32_t IDESC = (2u << 4)        // D format: s32
                                       | (0u << 7)      // A format: unsigned 8-bit (codes)
@@ -100,18 +101,30 @@ struct Params {
     int64_t ldy;             // elements between consecutive token rows of y (N when y is [M][N])
     int npeer;               // copies of y in other GPUs' memory that receive the same stores
     void *y_peer[NSLQ_MAX_RANKS - 1];
+    int wide;                // y, its copies and ldy allow 16-byte stores
 };
 
 template <typename T> struct OutStore;
 template <> struct OutStore<float> {
+    static __device__ __forceinline__ float cvt(float v) { return v; }
     static __device__ __forceinline__ void put(void *y, int64_t o, float v) { reinterpret_cast<float *>(y)[o] = v; }
 };
 template <> struct OutStore<__nv_bfloat16> {
+    static __device__ __forceinline__ __nv_bfloat16 cvt(float v) { return __float2bfloat16_rn(v); }
     static __device__ __forceinline__ void put(void *y, int64_t o, float v) { reinterpret_cast<__nv_bfloat16 *>(y)[o] = __float2bfloat16_rn(v); }
 };
 template <> struct OutStore<__half> {
+    static __device__ __forceinline__ __half cvt(float v) { return __float2half_rn(v); }
     static __device__ __forceinline__ void put(void *y, int64_t o, float v) { reinterpret_cast<__half *>(y)[o] = __float2half_rn(v); }
 };
+
+// Barrier of the four epilogue warps that share a token half (ids 1 and 2; id 0 is __syncthreads).  Every one of
+// the four executes the same sequence of these: they are reached only between the wait for a finished
+// accumulator, which the four pass or give up together, and the end of that tile's groups, with no exit between.
+static __device__ __forceinline__ void half_sync(int half)
+{
+    asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+}
 
 // Sixteen tokens of one accumulator lane (output feature n): finalise and store.  Kept small and
 // called from a rolled loop on purpose: the epilogue as straight-line code for a whole tile does
@@ -119,10 +132,17 @@ template <> struct OutStore<__half> {
 constexpr int EG = 16;                   // tokens per epilogue step
 // `valid` (tokens of the group inside M) is warp-uniform.  The arithmetic is branch-free so the 16
 // independent chains overlap; only the stores are guarded, by one test per group on the common path.
+//
+// Full tiles of a result that allows 16-byte stores go out through shared memory (`stage`, [16 tokens][128
+// features] of the four warps of a token half): a lane owns one feature, so direct stores are 2 or 4 bytes per
+// lane and 64 or 128 contiguous bytes per instruction -- over NVLink, into the other ranks' copies, such
+// stores reached 340 GB/s where 16 bytes per lane in whole 256- or 512-byte rows reach 560.
 template <typename T>
 static __device__ __forceinline__ void store_group(const Params &p, const uint32_t (&r)[EG], const float *s127, const int *rs,
-                                                   int64_t mt, int64_t n, bool n_ok, float bias)
+                                                   int64_t mt, int64_t n0, int q, int lane, int half, bool wide, T *stage, float bias)
 {
+    const int64_t n = n0 + q * 32 + lane;
+    const bool n_ok = n < p.N;
     int acc[EG];
     float v[EG];
 #pragma unroll
@@ -142,46 +162,47 @@ static __device__ __forceinline__ void store_group(const Params &p, const uint32
 #pragma unroll
         for (int j = 0; j < EG; ++j) v[j] = __fadd_rn(v[j], bias);
     }
+    const int64_t o = mt * p.N + n;
+    const int64_t left = p.M - mt;
     // no early return for lanes past N: the caller's next instruction is a warp-wide
     // tcgen05.ld, which every lane must reach together
-    if (n_ok) {
-    const int64_t o = mt * p.N + n;
-    const int64_t oy = mt * p.ldy + n;
-    const int64_t left = p.M - mt;
-    if (left >= EG) {
-        if (p.acc_out) {
-#pragma unroll
-            for (int j = 0; j < EG; ++j) p.acc_out[o + j * p.N] = acc[j];
-        }
-        if (p.residual) {
-            float res[EG];
-#pragma unroll
-            for (int j = 0; j < EG; ++j) res[j] = p.residual[o + j * p.N];
-#pragma unroll
-            for (int j = 0; j < EG; ++j) v[j] = __fadd_rn(v[j], res[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < EG; ++j) OutStore<T>::put(p.y, oy + j * p.ldy, v[j]);
-        // column-sharded run: the same tile goes straight into every other rank's copy of the
-        // gathered output (plain stores over NVLink; the all-gather rides in the epilogue)
-        for (int pi = 0; pi < p.npeer; ++pi) {
-            void *yp = p.y_peer[pi];
-#pragma unroll
-            for (int j = 0; j < EG; ++j) OutStore<T>::put(yp, oy + j * p.ldy, v[j]);
-        }
-    } else {
+    if (n_ok && (p.acc_out || p.residual)) {
 #pragma unroll
         for (int j = 0; j < EG; ++j) {
             if (j < left) {
-                const int64_t oj = o + j * p.N;
-                if (p.acc_out) p.acc_out[oj] = acc[j];
-                float vj = v[j];
-                if (p.residual) vj = __fadd_rn(vj, p.residual[oj]);
-                OutStore<T>::put(p.y, oy + j * p.ldy, vj);
-                for (int pi = 0; pi < p.npeer; ++pi) OutStore<T>::put(p.y_peer[pi], oy + j * p.ldy, vj);
+                if (p.acc_out) p.acc_out[o + j * p.N] = acc[j];
+                if (p.residual) v[j] = __fadd_rn(v[j], p.residual[o + j * p.N]);
             }
         }
     }
+    if (wide) {                                        // uniform over the four warps of the half
+#pragma unroll
+        for (int j = 0; j < EG; ++j) stage[j * BW + q * 32 + lane] = OutStore<T>::cvt(v[j]);
+        half_sync(half);
+        constexpr int VR = BW * (int)sizeof(T) / 16;   // 16-byte vectors per row of the tile
+        constexpr int RPI = 32 / VR;                   // rows per warp instruction
+#pragma unroll
+        for (int i = 0; i < 4 / RPI; ++i) {
+            const int row = 4 * q + i * RPI + lane / VR, c = lane % VR;
+            if (row < left) {
+                const uint4 val = reinterpret_cast<const uint4 *>(stage)[row * VR + c];
+                const int64_t off = ((mt + row) * p.ldy + n0) * (int64_t)sizeof(T) + 16 * c;
+                *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(p.y) + off) = val;
+                // column-sharded run: the same rows go straight into every other rank's copy of the
+                // gathered output (plain stores over NVLink; the all-gather rides in the epilogue)
+                for (int pi = 0; pi < p.npeer; ++pi) *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(p.y_peer[pi]) + off) = val;
+            }
+        }
+        half_sync(half);                               // the stage is free for the next group
+    } else if (n_ok) {
+        const int64_t oy = mt * p.ldy + n;
+#pragma unroll
+        for (int j = 0; j < EG; ++j) {
+            if (j < left) {
+                OutStore<T>::put(p.y, oy + j * p.ldy, v[j]);
+                for (int pi = 0; pi < p.npeer; ++pi) OutStore<T>::put(p.y_peer[pi], oy + j * p.ldy, v[j]);
+            }
+        }
     }
 }
 
@@ -220,6 +241,8 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     volatile uint32_t *slot_ptr = reinterpret_cast<volatile uint32_t *>(base_ptr + C::TS * C::T_BYTES + C::SCALE_BYTES + 8 * NBAR);
     // CTA-wide "a wait gave up" flag: raised by the role whose wait expired, seen by every other wait
     volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + C::TS * C::T_BYTES + C::SCALE_BYTES + 8 * NBAR + 8);
+
+    uint8_t *stage_ptr = base_ptr + C::TS * C::T_BYTES + C::SCALE_BYTES + C::BAR_BYTES;   // output staging of the epilogue
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nkb = (int)((p.K + BK * C::KS - 1) / (BK * C::KS));   // pipeline steps per tile
@@ -375,8 +398,9 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             const uint32_t buf = t & 1u, cph = (t >> 1) & 1u;
             const int64_t m0 = (int64_t)(tile % p.tiles_t) * BT + half * C::HALF_T, n0 = (int64_t)(tile / p.tiles_t) * BW;
             const int64_t n = n0 + q * 32 + lane;
-            const bool n_ok = n < p.N;
-            const float bias = (p.bias && n_ok) ? p.bias[n] : 0.0f;
+            const float bias = (p.bias && n < p.N) ? p.bias[n] : 0.0f;
+            const bool wide = p.wide && n0 + BW <= p.N;
+            uint8_t *stage = stage_ptr + half * (C::STAGE_BYTES / 2);
             __syncwarp();                             // the previous tile's reads of the factors are done
             for (int i = lane; i < C::HALF_T; i += 32) {
                 const int64_t m = m0 + i;
@@ -398,9 +422,12 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 }
                 const int64_t mt = m0 + g * EG;
                 if (mt >= p.M) continue;             // warp-uniform
-                if (p.y_dtype == NSLQ_DTYPE_F32) store_group<float>(p, r, s127 + g * EG, rs + g * EG, mt, n, n_ok, bias);
-                else if (p.y_dtype == NSLQ_DTYPE_BF16) store_group<__nv_bfloat16>(p, r, s127 + g * EG, rs + g * EG, mt, n, n_ok, bias);
-                else store_group<__half>(p, r, s127 + g * EG, rs + g * EG, mt, n, n_ok, bias);
+                if (p.y_dtype == NSLQ_DTYPE_F32)
+                    store_group<float>(p, r, s127 + g * EG, rs + g * EG, mt, n0, q, lane, half, wide, reinterpret_cast<float *>(stage), bias);
+                else if (p.y_dtype == NSLQ_DTYPE_BF16)
+                    store_group<__nv_bfloat16>(p, r, s127 + g * EG, rs + g * EG, mt, n0, q, lane, half, wide, reinterpret_cast<__nv_bfloat16 *>(stage), bias);
+                else
+                    store_group<__half>(p, r, s127 + g * EG, rs + g * EG, mt, n0, q, lane, half, wide, reinterpret_cast<__half *>(stage), bias);
             }
         }
     }
@@ -451,13 +478,18 @@ static int gemm_one_launch(const uint8_t *w, const int8_t *q_perm, const float *
                            int64_t N, int64_t K, float weight_scale, void *y, int y_dtype, int32_t *acc_out,
                            const float *bias, const float *residual, const OutSpec *os, int64_t row_off, cudaStream_t st)
 {
-    gemm::Params p{w, scale, rowsum, y, acc_out, bias, residual, M, N, K, y_dtype, weight_scale, 0, 0, N, 0, {}};
+    gemm::Params p{w, scale, rowsum, y, acc_out, bias, residual, M, N, K, y_dtype, weight_scale, 0, 0, N, 0, {}, 0};
+    const int es = y_dtype == NSLQ_DTYPE_F32 ? 4 : 2;
     if (os) {
-        const int es = y_dtype == NSLQ_DTYPE_F32 ? 4 : 2;
         p.ldy = os->ldy;
         p.npeer = os->npeer;
         for (int i = 0; i < os->npeer; ++i) p.y_peer[i] = (char *)os->peer[i] + row_off * os->ldy * es;
     }
+    // Whole rows of a tile as 16-byte vectors, for results that also go to other GPUs (a local-only result is
+    // stored directly: measured, the staging costs the single-GPU prefill GEMM 6 us of 47).  Every row start of y
+    // and of its copies must be 16-byte aligned.
+    p.wide = p.npeer > 0 && aligned16(p.y) && (p.ldy * es) % 16 == 0;
+    for (int i = 0; i < p.npeer; ++i) p.wide = p.wide && aligned16(p.y_peer[i]);
     // Token-tile width: the one that wastes fewer SM-rounds on this shape (ties go to the wider
     // tile, which moves fewer shared-memory bytes per MAC).
     const int sms = sm100::sm_count();

@@ -394,7 +394,13 @@ static __device__ __forceinline__ void src_quantise_row(const BulkParams &p, int
     for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
         float f[16];
         src_load<T, SRC>(p, m, gi, f);
-        if (SRC == SRC_RMSNORM) ffsq16(a, f, bad); else mx = absmax16(f, mx);
+        if (SRC == SRC_RMSNORM) {
+            // the norm weights of this group are needed behind two reductions: have them fetched meanwhile
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(p.norm_w + 16 * (int64_t)gi));
+            ffsq16(a, f, bad);
+        } else {
+            mx = absmax16(f, mx);
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) reinterpret_cast<float4 *>(h_s)[4 * gi + j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
     }
