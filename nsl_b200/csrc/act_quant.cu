@@ -13,7 +13,6 @@
 
 #include "common.cuh"
 #include "quant_core.cuh"
-#include "rmsnorm_core.cuh"
 
 namespace nslq {
 
@@ -189,14 +188,13 @@ static __device__ __forceinline__ double block_sum_f64(double v, double *smem)
 // `fused_rmsnorm` but never emits, crates/nsl-codegen/src/bitnet/config.rs:23-31): one CTA per row,
 //   rms = sqrt(sum_k x^2 / K + eps)                 in f64
 //   h   = (f32)(x / rms * weight)                   in f64, rounded once
-// the arithmetic of nsl_tensor_rmsnorm (crates/nsl-runtime/src/tensor/mod.rs:3016-3035), carried out mostly
-// in fp32 pairs with the f64 expression as the fallback (rmsnorm_core.cuh says how and why the results are
-// the same); the sum of squares is a tree of partial sums instead of a sequential loop and can differ from
-// the reference's in its last bits.  h never goes to memory unless h_out is given.  Then the row is
+// exactly the arithmetic of nsl_tensor_rmsnorm (crates/nsl-runtime/src/tensor/mod.rs:3016-3035),
+// except that the sum of squares is a tree reduction instead of a sequential loop (it can differ
+// in the last bits of the f64); h never goes to memory unless h_out is given.  Then the row is
 // quantised from registers like act_quant_kernel.
 template <typename T, int XV>
 __global__ void __launch_bounds__(AQ_THREADS)
-rmsnorm_act_quant_kernel(const T *__restrict__ x, const float *__restrict__ weight, double eps, double inv_k, int64_t K,
+rmsnorm_act_quant_kernel(const T *__restrict__ x, const float *__restrict__ weight, double eps, int64_t K,
                          float *__restrict__ h_out, int8_t *__restrict__ q_plain, int8_t *__restrict__ q_perm,
                          float *__restrict__ scale_out, int32_t *__restrict__ rowsum_out)
 {
@@ -225,23 +223,11 @@ rmsnorm_act_quant_kernel(const T *__restrict__ x, const float *__restrict__ weig
             wv[i] = (v < nvec) ? __ldg(reinterpret_cast<const float4 *>(weight) + v) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
-    // sum of squares: float-float per thread, f64 across the CTA; f64 throughout for a row out of range
-    FF a{0.0f, 0.0f};
-    bool bad = false;
 #pragma unroll
-    for (int i = 0; i < XV; ++i) { ff_add_sq(a, xv[i].x, bad); ff_add_sq(a, xv[i].y, bad); ff_add_sq(a, xv[i].z, bad); ff_add_sq(a, xv[i].w, bad); }
-    a = ff_warp_sum(a, __any_sync(0xffffffffu, bad));
-    if ((threadIdx.x & 31) == 0) ssq[threadIdx.x >> 5] = (double)a.h + (double)a.l;
-    __syncthreads();
-    double tot = sum_partials<AQ_THREADS / 32>(ssq, 1);
-    if (!(tot <= 3.5e38)) {                                   // CTA-uniform
-#pragma unroll
-        for (int i = 0; i < XV; ++i)
-            sq += (double)xv[i].x * xv[i].x + (double)xv[i].y * xv[i].y + (double)xv[i].z * xv[i].z + (double)xv[i].w * xv[i].w;
-        __syncthreads();
-        tot = block_sum_f64(sq, ssq);
-    }
-    const RmsScale rs = rms_scale(tot, (double)K, inv_k, eps);
+    for (int i = 0; i < XV; ++i)
+        sq += (double)xv[i].x * xv[i].x + (double)xv[i].y * xv[i].y + (double)xv[i].z * xv[i].z + (double)xv[i].w * xv[i].w;
+    const double rms = sqrt(block_sum_f64(sq, ssq) / (double)K + eps);
+    const double rinv = __drcp_rn(rms);
     float m = 0.0f;
 #pragma unroll
     for (int i = 0; i < XV; ++i) {
@@ -249,8 +235,8 @@ rmsnorm_act_quant_kernel(const T *__restrict__ x, const float *__restrict__ weig
         if (v < nvec) {
             const float4 w = WPRE ? wv[WPRE ? i : 0] : reinterpret_cast<const float4 *>(weight)[v];
             float4 h;
-            h.x = norm_ff(xv[i].x, w.x, rs); h.y = norm_ff(xv[i].y, w.y, rs);
-            h.z = norm_ff(xv[i].z, w.z, rs); h.w = norm_ff(xv[i].w, w.w, rs);
+            h.x = norm_one(xv[i].x, rms, rinv, w.x); h.y = norm_one(xv[i].y, rms, rinv, w.y);
+            h.z = norm_one(xv[i].z, rms, rinv, w.z); h.w = norm_one(xv[i].w, rms, rinv, w.w);
             xv[i] = h;
             if (h_out) reinterpret_cast<float4 *>(h_out + r * K)[v] = h;
             m = fmaxf(m, fmaxf(fmaxf(fabsf(h.x), fabsf(h.y)), fmaxf(fabsf(h.z), fabsf(h.w))));
@@ -287,9 +273,9 @@ static int launch_rmsnorm_quant(const void *x, const float *weight, double eps, 
     dim3 grid((unsigned)M), block(AQ_THREADS);
     cudaError_t e;
     if (K <= 4 * 4 * AQ_THREADS)
-        e = launch_kernel(rmsnorm_act_quant_kernel<T, 4>, grid, block, 0, st, (const T *)x, weight, eps, 1.0 / (double)K, K, h_out, q_plain, q_perm, scale, rowsum);
+        e = launch_kernel(rmsnorm_act_quant_kernel<T, 4>, grid, block, 0, st, (const T *)x, weight, eps, K, h_out, q_plain, q_perm, scale, rowsum);
     else
-        e = launch_kernel(rmsnorm_act_quant_kernel<T, 12>, grid, block, 0, st, (const T *)x, weight, eps, 1.0 / (double)K, K, h_out, q_plain, q_perm, scale, rowsum);
+        e = launch_kernel(rmsnorm_act_quant_kernel<T, 12>, grid, block, 0, st, (const T *)x, weight, eps, K, h_out, q_plain, q_perm, scale, rowsum);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "rmsnorm_act_quant_kernel: %s", cudaGetErrorString(e));
     return check_launch("rmsnorm_act_quant_kernel");
 }

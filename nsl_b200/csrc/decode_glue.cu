@@ -15,7 +15,6 @@
 
 #include "common.cuh"
 #include "quant_core.cuh"
-#include "rmsnorm_core.cuh"
 
 namespace nslq {
 
@@ -44,33 +43,23 @@ __global__ void __launch_bounds__(256) embed_gather_kernel(const T *__restrict__
 }
 
 // y[r, k] = (out dtype)(f32)(x[r,k] / rms * w[k]), rms = sqrt(mean x^2 + eps) in f64: the arithmetic of
-// nslq_rmsnorm_act_quant_i8's normalisation (rmsnorm_core.cuh), rounded once more when y is 16-bit.
+// nslq_rmsnorm_act_quant_i8's normalisation (tree sum of squares), rounded once more when y is 16-bit.
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float *__restrict__ x, const float *__restrict__ w, double eps,
-                                                           double inv_k, int64_t K, void *__restrict__ y, int y_dtype)
+                                                           int64_t K, void *__restrict__ y, int y_dtype)
 {
     __shared__ double part[8];
     pdl_wait();
     const int64_t r = blockIdx.x;
     const float *row = x + r * K;
-    FF a{0.0f, 0.0f};
-    bool bad = false;
-    for (int64_t i = threadIdx.x; i < K; i += 256) ff_add_sq(a, row[i], bad);
-    a = ff_warp_sum(a, __any_sync(0xffffffffu, bad));
-    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = (double)a.h + (double)a.l;
-    __syncthreads();
-    double tot = sum_partials<8>(part, 1);
-    if (!(tot <= 3.5e38)) {                                   // CTA-uniform: a row out of the fp32 path's range
-        double sq = 0.0;
-        for (int64_t i = threadIdx.x; i < K; i += 256) sq += (double)row[i] * (double)row[i];
+    double sq = 0.0;
+    for (int64_t i = threadIdx.x; i < K; i += 256) sq += (double)row[i] * (double)row[i];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-        __syncthreads();
-        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = sq;
-        __syncthreads();
-        tot = sum_partials<8>(part, 1);
-    }
-    const RmsScale rs = rms_scale(tot, (double)K, inv_k, eps);
-    for (int64_t i = threadIdx.x; i < K; i += 256) store_out(y, y_dtype, r * K + i, norm_ff(row[i], w[i], rs));
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    const double tot = sum_partials<8>(part, 1);
+    const double rms = sqrt(tot / (double)K + eps), rinv = __drcp_rn(rms);
+    for (int64_t i = threadIdx.x; i < K; i += 256) store_out(y, y_dtype, r * K + i, norm_one(row[i], rms, rinv, w[i]));
     pdl_launch_dependents();
 }
 
@@ -162,7 +151,7 @@ int nslq_rmsnorm_rows(const float *x, const float *weight, double eps, int64_t M
     if (y_dtype != NSLQ_DTYPE_F32 && y_dtype != NSLQ_DTYPE_FP16 && y_dtype != NSLQ_DTYPE_BF16)
         return fail(NSLQ_ERR_ARG, "nslq_rmsnorm_rows: y dtype %d not in {F32,FP16,BF16}", y_dtype);
     if (M == 0) return NSLQ_OK;
-    const cudaError_t e = launch_kernel(rmsnorm_rows_kernel, dim3((unsigned)M), dim3(256), 0, (cudaStream_t)stream, x, weight, eps, 1.0 / (double)K, K, y, y_dtype);
+    const cudaError_t e = launch_kernel(rmsnorm_rows_kernel, dim3((unsigned)M), dim3(256), 0, (cudaStream_t)stream, x, weight, eps, K, y, y_dtype);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "rmsnorm_rows_kernel: %s", cudaGetErrorString(e));
     return check_launch("rmsnorm_rows_kernel");
 }

@@ -28,7 +28,6 @@
 // Also here: a scalar kernel for shapes the streaming kernel cannot take
 // (K % 64 != 0 or unaligned rows); same arithmetic, natural-order activations.
 #include "quant_core.cuh"
-#include "rmsnorm_core.cuh"
 #include "sm100_common.cuh"
 #include "ternary_mma.cuh"
 
@@ -334,7 +333,7 @@ struct BulkParams {
     int src;               // (a template argument of the kernels; kept here for the dispatch)
     const void *x2;        // [M][K], SRC_SWIGLU
     const float *norm_w;   // [K], SRC_RMSNORM
-    double eps, inv_k;     // inv_k = 1.0 / K
+    double eps;
 };
 enum { SRC_PLAIN = 0, SRC_RMSNORM = 1, SRC_SWIGLU = 2 };
 
@@ -349,12 +348,6 @@ static __device__ __forceinline__ void src_load(const BulkParams &p, int m, int 
 #pragma unroll
         for (int e = 0; e < 16; ++e) f[e] = swiglu_one(f[e], u[e]);
     }
-}
-
-static __device__ __forceinline__ void ffsq16(FF &a, const float (&f)[16], bool &bad)
-{
-#pragma unroll
-    for (int e = 0; e < 16; ++e) ff_add_sq(a, f[e], bad);
 }
 
 constexpr int BULK_THREADS = 256;
@@ -388,8 +381,7 @@ static __device__ __forceinline__ void src_quantise_row(const BulkParams &p, int
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ngroups = (int)(p.K >> 4);
     float mx = 0.0f;
-    FF a{0.0f, 0.0f};
-    bool bad = false;
+    double sq = 0.0;
 #pragma unroll 1
     for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
         float f[16];
@@ -397,7 +389,8 @@ static __device__ __forceinline__ void src_quantise_row(const BulkParams &p, int
         if (SRC == SRC_RMSNORM) {
             // the norm weights of this group are needed behind two reductions: have them fetched meanwhile
             asm volatile("prefetch.global.L1 [%0];" ::"l"(p.norm_w + 16 * (int64_t)gi));
-            ffsq16(a, f, bad);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) sq += (double)f[e] * (double)f[e];
         } else {
             mx = absmax16(f, mx);
         }
@@ -405,35 +398,19 @@ static __device__ __forceinline__ void src_quantise_row(const BulkParams &p, int
         for (int j = 0; j < 4; ++j) reinterpret_cast<float4 *>(h_s)[4 * gi + j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
     }
     if (SRC == SRC_RMSNORM) {
-        a = ff_warp_sum(a, __any_sync(0xffffffffu, bad));
-        if (lane == 0) part_d[warp * FUSED_MAX_M + m] = (double)a.h + (double)a.l;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (lane == 0) part_d[warp * FUSED_MAX_M + m] = sq;
         __syncthreads();
-        double tot = sum_partials<NW>(part_d + m, FUSED_MAX_M);
-        if (!(tot <= 3.5e38)) {                               // CTA-uniform: a row out of the fp32 path's range, f64 throughout
-            double sq = 0.0;
-#pragma unroll 1
-            for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float4 v = reinterpret_cast<const float4 *>(h_s)[4 * gi + j];
-                    sq += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
-                }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            __syncthreads();
-            if (lane == 0) part_d[warp * FUSED_MAX_M + m] = sq;
-            __syncthreads();
-            tot = sum_partials<NW>(part_d + m, FUSED_MAX_M);
-        }
-        const RmsScale rs = rms_scale(tot, (double)p.K, p.inv_k, p.eps);
+        const double tot = sum_partials<NW>(part_d + m, FUSED_MAX_M);
+        const double rms = sqrt(tot / (double)p.K + p.eps), rinv = __drcp_rn(rms);
 #pragma unroll 1
         for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 float4 v = reinterpret_cast<const float4 *>(h_s)[4 * gi + j];
                 const float4 w = __ldg(reinterpret_cast<const float4 *>(p.norm_w) + 4 * gi + j);
-                v.x = norm_ff(v.x, w.x, rs); v.y = norm_ff(v.y, w.y, rs); v.z = norm_ff(v.z, w.z, rs); v.w = norm_ff(v.w, w.w, rs);
+                v.x = norm_one(v.x, rms, rinv, w.x); v.y = norm_one(v.y, rms, rinv, w.y); v.z = norm_one(v.z, rms, rinv, w.z); v.w = norm_one(v.w, rms, rinv, w.w);
                 mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
                 reinterpret_cast<float4 *>(h_s)[4 * gi + j] = v;
             }
@@ -1061,7 +1038,7 @@ int ternary_gemv_src_dispatch(const uint8_t *w, const void *x, const void *x2, c
                               const float *bias, const float *residual, cudaStream_t st)
 {
     BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale, bulk_pattern(K / 4),
-                 norm_w ? SRC_RMSNORM : (x2 ? SRC_SWIGLU : SRC_PLAIN), x2, norm_w, eps, 1.0 / (double)K};
+                 norm_w ? SRC_RMSNORM : (x2 ? SRC_SWIGLU : SRC_PLAIN), x2, norm_w, eps};
     return bulk_by_dtype(b, x_dtype, st);
 }
 
@@ -1070,7 +1047,7 @@ int ternary_gemv_fused_dispatch(const uint8_t *w, const void *x, int x_dtype, in
                                 const float *residual, cudaStream_t st)
 {
     if (bulk_supported(M, K)) {
-        BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale, bulk_pattern(K / 4), SRC_PLAIN, nullptr, nullptr, 0.0, 0.0};
+        BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale, bulk_pattern(K / 4), SRC_PLAIN, nullptr, nullptr, 0.0};
         return bulk_by_dtype(b, x_dtype, st);
     }
     FusedParams p{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale};
