@@ -234,9 +234,7 @@ rmsnorm_act_quant_kernel(const T *__restrict__ x, const float *__restrict__ weig
         const int v = i * AQ_THREADS + threadIdx.x;
         if (v < nvec) {
             const float4 w = WPRE ? wv[WPRE ? i : 0] : reinterpret_cast<const float4 *>(weight)[v];
-            float4 h;
-            h.x = norm_one(xv[i].x, rms, rinv, w.x); h.y = norm_one(xv[i].y, rms, rinv, w.y);
-            h.z = norm_one(xv[i].z, rms, rinv, w.z); h.w = norm_one(xv[i].w, rms, rinv, w.w);
+            const float4 h = norm_four(xv[i], rms, rinv, w);
             xv[i] = h;
             if (h_out) reinterpret_cast<float4 *>(h_out + r * K)[v] = h;
             m = fmaxf(m, fmaxf(fmaxf(fabsf(h.x), fabsf(h.y)), fmaxf(fabsf(h.z), fabsf(h.w))));
@@ -300,7 +298,7 @@ int rmsnorm_act_quant_dispatch(const void *x, int x_dtype, const float *weight, 
 
 // SiLU(gate) * up fused in front of the quantisation of the down projection's input (the other
 // "fused neighbour" of the linear: gate and up never make a round trip as an activation tensor):
-//   h = (f32)( g / (1 + exp(-g)) * u )    computed in fp32 from the f32/fp16/bf16 inputs,
+//   h = (f32)( g / (1 + exp(-g)) * u )    computed in fp32 from the f32/fp16/bf16 inputs (swiglu_one),
 // then quantised from registers like act_quant_kernel.  One CTA per row.
 template <typename T, int XV>
 __global__ void __launch_bounds__(AQ_THREADS)
@@ -323,8 +321,8 @@ swiglu_act_quant_kernel(const T *__restrict__ gate, const T *__restrict__ up, in
         if (v < nvec) {
             const float4 g = Vec4<T>::load(gate + r * ld_g, v), u = Vec4<T>::load(up + r * ld_u, v);
             float4 h;
-            h.x = __fdiv_rn(g.x, 1.0f + expf(-g.x)) * u.x; h.y = __fdiv_rn(g.y, 1.0f + expf(-g.y)) * u.y;
-            h.z = __fdiv_rn(g.z, 1.0f + expf(-g.z)) * u.z; h.w = __fdiv_rn(g.w, 1.0f + expf(-g.w)) * u.w;
+            h.x = swiglu_one(g.x, u.x); h.y = swiglu_one(g.y, u.y);
+            h.z = swiglu_one(g.z, u.z); h.w = swiglu_one(g.w, u.w);
             hv[i] = h;
             if (h_out) reinterpret_cast<float4 *>(h_out + r * K)[v] = h;
             m = fmaxf(m, fmaxf(fmaxf(fabsf(h.x), fabsf(h.y)), fmaxf(fabsf(h.z), fabsf(h.w))));
@@ -383,7 +381,7 @@ swiglu_act_quant_cluster_kernel(const T *__restrict__ gate, const T *__restrict_
         Group16<T>::load(gate + r * ld_g, g, gv);
         Group16<T>::load(up + r * ld_u, g, uv);
 #pragma unroll
-        for (int e = 0; e < 16; ++e) h[e] = __fdiv_rn(gv[e], 1.0f + expf(-gv[e])) * uv[e];
+        for (int e = 0; e < 16; ++e) h[e] = swiglu_one(gv[e], uv[e]);
         if (h_out) {
 #pragma unroll
             for (int j = 0; j < 4; ++j)

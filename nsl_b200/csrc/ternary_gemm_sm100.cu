@@ -164,18 +164,16 @@ static __device__ __forceinline__ void store_group(const Params &p, const uint32
     }
     const int64_t o = mt * p.N + n;
     const int64_t left = p.M - mt;
-    // no early return for lanes past N: the caller's next instruction is a warp-wide
-    // tcgen05.ld, which every lane must reach together
-    if (n_ok && (p.acc_out || p.residual)) {
+    if (wide) {                                        // uniform over the four warps of the half; the tile lies inside N
+        if (p.acc_out || p.residual) {
 #pragma unroll
-        for (int j = 0; j < EG; ++j) {
-            if (j < left) {
-                if (p.acc_out) p.acc_out[o + j * p.N] = acc[j];
-                if (p.residual) v[j] = __fadd_rn(v[j], p.residual[o + j * p.N]);
+            for (int j = 0; j < EG; ++j) {
+                if (j < left) {
+                    if (p.acc_out) p.acc_out[o + j * p.N] = acc[j];
+                    if (p.residual) v[j] = __fadd_rn(v[j], p.residual[o + j * p.N]);
+                }
             }
         }
-    }
-    if (wide) {                                        // uniform over the four warps of the half
 #pragma unroll
         for (int j = 0; j < EG; ++j) stage[j * BW + q * 32 + lane] = OutStore<T>::cvt(v[j]);
         half_sync(half);
@@ -194,15 +192,44 @@ static __device__ __forceinline__ void store_group(const Params &p, const uint32
             }
         }
         half_sync(half);                               // the stage is free for the next group
-    } else if (n_ok) {
-        const int64_t oy = mt * p.ldy + n;
+        return;
+    }
+    // no early return for lanes past N: the caller's next instruction is a warp-wide
+    // tcgen05.ld, which every lane must reach together
+    if (n_ok) {
+    const int64_t oy = mt * p.ldy + n;
+    if (left >= EG) {
+        if (p.acc_out) {
+#pragma unroll
+            for (int j = 0; j < EG; ++j) p.acc_out[o + j * p.N] = acc[j];
+        }
+        if (p.residual) {
+            float res[EG];
+#pragma unroll
+            for (int j = 0; j < EG; ++j) res[j] = p.residual[o + j * p.N];
+#pragma unroll
+            for (int j = 0; j < EG; ++j) v[j] = __fadd_rn(v[j], res[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < EG; ++j) OutStore<T>::put(p.y, oy + j * p.ldy, v[j]);
+        for (int pi = 0; pi < p.npeer; ++pi) {
+            void *yp = p.y_peer[pi];
+#pragma unroll
+            for (int j = 0; j < EG; ++j) OutStore<T>::put(yp, oy + j * p.ldy, v[j]);
+        }
+    } else {
 #pragma unroll
         for (int j = 0; j < EG; ++j) {
             if (j < left) {
-                OutStore<T>::put(p.y, oy + j * p.ldy, v[j]);
-                for (int pi = 0; pi < p.npeer; ++pi) OutStore<T>::put(p.y_peer[pi], oy + j * p.ldy, v[j]);
+                const int64_t oj = o + j * p.N;
+                if (p.acc_out) p.acc_out[oj] = acc[j];
+                float vj = v[j];
+                if (p.residual) vj = __fadd_rn(vj, p.residual[oj]);
+                OutStore<T>::put(p.y, oy + j * p.ldy, vj);
+                for (int pi = 0; pi < p.npeer; ++pi) OutStore<T>::put(p.y_peer[pi], oy + j * p.ldy, vj);
             }
         }
+    }
     }
 }
 

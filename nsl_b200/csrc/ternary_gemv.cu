@@ -410,7 +410,7 @@ static __device__ __forceinline__ void src_quantise_row(const BulkParams &p, int
             for (int j = 0; j < 4; ++j) {
                 float4 v = reinterpret_cast<const float4 *>(h_s)[4 * gi + j];
                 const float4 w = __ldg(reinterpret_cast<const float4 *>(p.norm_w) + 4 * gi + j);
-                v.x = norm_one(v.x, rms, rinv, w.x); v.y = norm_one(v.y, rms, rinv, w.y); v.z = norm_one(v.z, rms, rinv, w.z); v.w = norm_one(v.w, rms, rinv, w.w);
+                v = norm_four(v, rms, rinv, w);
                 mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
                 reinterpret_cast<float4 *>(h_s)[4 * gi + j] = v;
             }
