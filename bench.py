@@ -651,11 +651,12 @@ META = {"prefill_gemm": PrefillGemm, **DECODE_CLASSES}
 
 
 # ----------------------------------------------------------------------------- decoder workload
-def run_decoder(torch, batch, peaks, prompt=512, steps=256, warm=8):
+def run_decoder(torch, batch, peaks, prompt=512, steps=256, warm=8, layers=None):
     """BitNet b1.58-3B-shaped decoder (configs[3]): random ternary weights, uniform-random prompt ids,
-    greedy decode.  Returns decode / prefill tokens per second and the HBM figures of a decode step."""
+    greedy decode.  Returns decode / prefill tokens per second and the HBM figures of a decode step.
+    `layers` / `steps` below the model's own are for profiler captures only (a few launches of each kernel)."""
     from nsl_b200 import decoder
-    cfg = decoder.BitNetConfig()
+    cfg = decoder.BitNetConfig() if not layers else decoder.BitNetConfig(layers=layers)
     model = decoder.BitNetDecoder(cfg, batch, prompt + steps + warm + 8)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(0)
@@ -861,7 +862,9 @@ def run_ours(args):
     use_graph = not args.no_graph            # NCCL collectives are captured into the graph as well
 
     if args.workload.startswith("bitnet3b_b"):
-        out = run_decoder(torch, int(args.workload[10:]), peaks)
+        out = run_decoder(torch, int(args.workload[10:]), peaks, steps=args.decode_steps, layers=args.decoder_layers)
+        if args.decoder_layers or args.decode_steps != 256:
+            out["workload"] += "_REDUCED_layers%s_not_a_benchmark" % (args.decoder_layers or 26)
         out.update({"metric": METRIC, "value": out["decode_tok_s"], "unit": "tok/s", "n_gpus": 1,
                     "higher_is_better": True, "data": "synthetic (seed 0)", "dtype": "int8 x int2 -> int32"})
         print(json.dumps(out))
@@ -997,6 +1000,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="issue launches directly instead of replaying a CUDA graph")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels without the programmatic-dependent-launch attribute")
     ap.add_argument("--no-also", action="store_true", help="skip the secondary workloads of the default run")
+    ap.add_argument("--decoder-layers", type=int, default=0, help="bitnet3b_*: build this many layers only (profiler captures; the result is not a benchmark figure)")
+    ap.add_argument("--decode-steps", type=int, default=256, help="bitnet3b_*: decode steps timed (256 is the workload's own)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -368,7 +368,8 @@ static __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, 
 }
 
 // SRC_RMSNORM / SRC_SWIGLU: form, measure and quantise token row m.  The formed row is staged in shared
-// memory (h_s, K floats; every thread reads back only the groups it wrote) so that each transform exists
+// memory (h_s, K floats, quarter j of group gi at float4 index j * ngroups + gi so that a warp's accesses are
+// consecutive; every thread reads back only the groups it wrote) so that each transform exists
 // once, in a rolled loop: kept in registers and unrolled, the prologue was several thousand instructions that
 // a CTA executes exactly once, and fetching them cost more than executing them.
 // part_d / part_f / part_i: [NW][FUSED_MAX_M] partials of the warps; the caller synchronises after the last row.
@@ -395,7 +396,7 @@ static __device__ __forceinline__ void src_quantise_row(const BulkParams &p, int
             mx = absmax16(f, mx);
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) reinterpret_cast<float4 *>(h_s)[4 * gi + j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+        for (int j = 0; j < 4; ++j) reinterpret_cast<float4 *>(h_s)[j * ngroups + gi] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
     }
     if (SRC == SRC_RMSNORM) {
 #pragma unroll
@@ -408,11 +409,11 @@ static __device__ __forceinline__ void src_quantise_row(const BulkParams &p, int
         for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                float4 v = reinterpret_cast<const float4 *>(h_s)[4 * gi + j];
+                float4 v = reinterpret_cast<const float4 *>(h_s)[j * ngroups + gi];
                 const float4 w = __ldg(reinterpret_cast<const float4 *>(p.norm_w) + 4 * gi + j);
                 v = norm_four(v, rms, rinv, w);
                 mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-                reinterpret_cast<float4 *>(h_s)[4 * gi + j] = v;
+                reinterpret_cast<float4 *>(h_s)[j * ngroups + gi] = v;
             }
         }
     }
@@ -431,7 +432,7 @@ static __device__ __forceinline__ void src_quantise_row(const BulkParams &p, int
         float f[16];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const float4 v = reinterpret_cast<const float4 *>(h_s)[4 * gi + j];
+            const float4 v = reinterpret_cast<const float4 *>(h_s)[j * ngroups + gi];
             f[4 * j] = v.x; f[4 * j + 1] = v.y; f[4 * j + 2] = v.z; f[4 * j + 3] = v.w;
         }
         int q[16];
