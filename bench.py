@@ -6,7 +6,9 @@
 Workloads (all synthetic, seed 0, shapes and distributions of the reference's benchmark
 configurations):
   prefill_gemm  (default) BitLinear prefill, M=2048: up/gate [8640,3200] and down [3200,8640]
-                projections (one step = both, 226.5 GOP); value in TOPS.
+                projections (one step = both, 226.5 GOP); value in TOPS.  The two projections are
+                independent calls and are issued on two streams (--streams 1: on one), so the second
+                one's CTAs fill the SMs that the first one's last round of tiles leaves idle.
   decode_gemv   BitLinear decode, x fp32 [1,3200], W ternary [8640,3200]; one step = 64 calls
                 over 64 distinct weights (442 MB > L2); value in GB/s of algorithmic bytes
                 (packed W + x + y per call).  --streams S issues the (independent) calls
@@ -213,8 +215,9 @@ class PrefillGemm(Workload):
     SHAPES = [(8640, 3200), (3200, 8640)]                      # (N, K): up/gate, down
     OPS_PER_PROJ = 2 * 2048 * 3200 * 8640
 
-    def __init__(self, torch, ops, rank, world, comm=None, gather="peer", out_dtype="bf16", **_):
+    def __init__(self, torch, ops, rank, world, comm=None, gather="peer", out_dtype="bf16", streams=1, **_):
         self.torch, self.ops, self.rank, self.world = torch, ops, rank, world
+        self.streams = 2 if (world == 1 and streams >= 2) else 1
         self.comm, self.mode = comm, (gather if world > 1 else "none")
         self.ydt = torch.bfloat16 if out_dtype == "bf16" else torch.float32
         self.out_dtype = out_dtype
@@ -243,7 +246,7 @@ class PrefillGemm(Workload):
             self.wss.append(torch.empty(int(ops.lib().nslq_bitlinear_workspace_bytes(self.M, k)), dtype=torch.uint8,
                                         device="cuda"))
         self.y_host = torch.empty(self.M * self.F, dtype=self.ydt).pin_memory()
-        self.side = torch.cuda.Stream() if world > 1 else None
+        self.side = torch.cuda.Stream() if (world > 1 or self.streams == 2) else None
         self.e2e_streams = None
         self.kernel_launches = 2                               # per kernel_only() pass
         # 2 x (act quant + GEMM); sharded: + 2 flag barriers (peer) or 2 NCCL all-gathers, not counted as ours
@@ -273,12 +276,25 @@ class PrefillGemm(Workload):
 
     def step(self, xs=None):
         xs = xs or self.xs
+        torch = self.torch
+        cur = torch.cuda.current_stream()
         if self.world == 1:
+            if self.streams == 2:
+                # the two projections are independent: on two streams the second one's CTAs take the SMs that the
+                # first one's last, partial round of tiles leaves idle
+                fork = torch.cuda.Event()
+                fork.record(cur)
+                self.side.wait_event(fork)
+                with torch.cuda.stream(self.side):
+                    self.one_call(1, xs[1])
+                    join = torch.cuda.Event()
+                    join.record(self.side)
+                self.one_call(0, xs[0])
+                cur.wait_event(join)
+                return
             for i in range(2):
                 self.one_call(i, xs[i])
             return
-        torch = self.torch
-        cur = torch.cuda.current_stream()
         if self.mode == "peer":
             # The peers may still be reading the previous step's result: nobody stores before everybody
             # has arrived.  Then the two projections (independent calls) run side by side on two streams,
@@ -627,7 +643,7 @@ class W4A16(Workload):
 
 def make_workload(key, torch, ops, rank, world, streams=1, comm=None, gather="peer", out_dtype="bf16"):
     if key == "prefill_gemm":
-        return PrefillGemm(torch, ops, rank, world, comm=comm, gather=gather, out_dtype=out_dtype)
+        return PrefillGemm(torch, ops, rank, world, comm=comm, gather=gather, out_dtype=out_dtype, streams=streams)
     if key in DECODE_CLASSES:
         return DECODE_CLASSES[key](torch, ops, rank, world, streams=streams, comm=comm)
     if key.startswith("w4a16_m"):
@@ -699,9 +715,10 @@ def run_decoder(torch, batch, peaks, prompt=512, steps=256, warm=8, layers=None)
            "e2e_tok_s": round(batch * (steps) / e2e_s, 1),
            "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                         "frac": round(ach / peaks["hbm_gbs"], 4), "bytes_per_step": step_bytes,
-                        "note": "ternary weights + bf16 lm_head + KV read at mid-run context; in a decode step the norms, "
-                                "RoPE + KV append + attention and SwiGLU are library launches; embedding, lm_head, sampling "
-                                "and the prefill glue are PyTorch"},
+                        "note": "ternary weights + bf16 lm_head + KV read at mid-run context; a decode step is library launches "
+                                "(embedding rows, RMSNorm and SiLU*up inside the projections' launches up to four tokens, RoPE + KV "
+                                "append + attention, final norm, argmax) except the lm_head's bf16 GEMM (cuBLAS); the prefill "
+                                "glue is PyTorch"},
            "ceiling_tok_s": round(batch / (step_bytes / (peaks["hbm_gbs"] * 1e9)), 1)}
     del model
     torch.cuda.empty_cache()
@@ -992,8 +1009,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=WORKLOAD_KEYS)
-    ap.add_argument("--streams", type=int, default=1,
-                    help="decode_gemv: issue the independent calls of a step round-robin on this many streams")
+    ap.add_argument("--streams", type=int, default=None,
+                    help="decode_gemv: issue the independent calls of a step round-robin on this many streams (default 1: a "
+                         "dependent chain); prefill_gemm: 2 (default) runs the step's two independent projections on two "
+                         "streams, 1 on one")
     ap.add_argument("--gather", default="peer", choices=["peer", "ce", "nccl"],
                     help="N > 1, prefill: shards stored into every rank's copy by the GEMM epilogue, or ncclAllGather")
     ap.add_argument("--out-dtype", default="bf16", choices=["bf16", "f32"], help="prefill: dtype of y")
@@ -1003,6 +1022,8 @@ def main():
     ap.add_argument("--decoder-layers", type=int, default=0, help="bitnet3b_*: build this many layers only (profiler captures; the result is not a benchmark figure)")
     ap.add_argument("--decode-steps", type=int, default=256, help="bitnet3b_*: decode steps timed (256 is the workload's own)")
     args = ap.parse_args()
+    if args.streams is None:
+        args.streams = 2 if args.workload == "prefill_gemm" else 1
     if args.impl == "reference":
         run_reference(args)
     else:
