@@ -463,7 +463,7 @@ class DecodeGemv(Workload):
         self.ws = torch.empty(int(ops.lib().nslq_bitlinear_workspace_bytes(self.M, self.K)), dtype=torch.uint8,
                               device="cuda")
         self.kernel_launches = self.LAYERS
-        # M <= 4 (<= 2 on the tensor-memory kernel): the quantisation is fused into the decode kernel
+        # M <= 2: the quantisation is fused into the decode kernel
         self.launches_per_step = self.LAYERS * (1 if self.M <= 2 else 2)
         self.h2d, self.d2h = self.M * self.K * 4, self.M * self.N * 4
         mb = self.N * self.K / 4e6
@@ -487,7 +487,7 @@ class DecodeGemv(Workload):
             for i, layer in enumerate(self.layers):
                 j = i % self.streams
                 with self.torch.cuda.stream(self.side[j]):
-                    layer.forward(self.x, out=self.y_side[j], workspace=self.ws)   # M <= 4: workspace unused
+                    layer.forward(self.x, out=self.y_side[j], workspace=self.ws)   # M <= 2: workspace unused
             for st in self.side:
                 cur.wait_stream(st)
             return
@@ -716,7 +716,7 @@ def run_decoder(torch, batch, peaks, prompt=512, steps=256, warm=8, layers=None)
            "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                         "frac": round(ach / peaks["hbm_gbs"], 4), "bytes_per_step": step_bytes,
                         "note": "ternary weights + bf16 lm_head + KV read at mid-run context; a decode step is library launches "
-                                "(embedding rows, RMSNorm and SiLU*up inside the projections' launches up to four tokens, RoPE + KV "
+                                "(embedding rows, RMSNorm and SiLU*up inside the projections' launches up to two tokens, RoPE + KV "
                                 "append + attention, final norm, argmax) except the lm_head's bf16 GEMM (cuBLAS); the prefill "
                                 "glue is PyTorch"},
            "ceiling_tok_s": round(batch / (step_bytes / (peaks["hbm_gbs"] * 1e9)), 1)}

@@ -243,9 +243,9 @@ int nslq_bitlinear_forward_quantized(const nslq_bitlinear_t *w, const int8_t *q_
  * nslq_bitlinear_forward with the launch in front of it folded in: the input rows are
  *   RMSNorm(x) with `norm_weight`, `eps`      (= nslq_rmsnorm_act_quant_i8, then forward_quantized), or
  *   SiLU(gate) * up                           (= nslq_swiglu_act_quant_i8,  then forward_quantized),
- * with the same bits as those two calls.  Up to four tokens (a decode step) every CTA of the one launch
+ * with the same bits as those two calls.  For one or two tokens (a decode step) every CTA of the one launch
  * forms and quantises the rows for itself -- NSL's BitNet kernel config names this prologue (`fused_rmsnorm`,
- * crates/nsl-codegen/src/bitnet/config.rs:23-31) and never emits it; above four tokens, or when a row
+ * crates/nsl-codegen/src/bitnet/config.rs:23-31) and never emits it; above two tokens (measured: the CTAs' repeated work then costs more than a launch), or when a row
  * does not fit the CTA's shared memory next to the weights, the call issues the two launches itself and
  * needs the workspace of nslq_bitlinear_forward (pass it always).  K % 64 == 0; gate, up: [M,K], packed.
  */

@@ -385,7 +385,10 @@ int nslq_bitlinear_forward(const nslq_bitlinear_t *w, const void *x, int x_dtype
     if (decode_pays(M, w->N, w->K) && ternary_decode_fused_supported(w->packed, x, x_dtype, M, w->N, w->K))
         return ternary_decode_fused_dispatch(w->packed, x, x_dtype, (int)M, w->N, w->K, w->weight_scale, y, y_dtype, acc_out,
                                              bias, residual, st);
-    if (!decode_pays(M, w->N, w->K) && ternary_gemv_fused_supported(w->packed, x, M, w->K) &&
+    // One launch that also quantises the tokens pays for one or two of them: every CTA repeats the quantisation, and
+    // measured at four tokens ([3200, 3200]) it took 7.3 us against 1.7 + 2.9 for the quantiser and the
+    // pre-quantised kernel as two launches.
+    if (M <= 2 && !decode_pays(M, w->N, w->K) && ternary_gemv_fused_supported(w->packed, x, M, w->K) &&
         (x_dtype == NSLQ_DTYPE_F32 || aligned16(x)))
         return ternary_gemv_fused_dispatch(w->packed, x, x_dtype, (int)M, w->N, w->K, w->weight_scale, y, y_dtype, acc_out,
                                            bias, residual, st);
@@ -402,7 +405,7 @@ int nslq_bitlinear_forward(const nslq_bitlinear_t *w, const void *x, int x_dtype
 }
 
 // The RMSNorm or the SiLU(gate) * up in front of a projection, formed inside the projection's own launch for
-// up to four tokens; the same two launches as the separate entry points (bit-equal results) above that.
+// one or two tokens; the same two launches as the separate entry points (bit-equal results) above that.
 static int forward_src(const char *who, const nslq_bitlinear_t *w, const void *x, const void *x2, const float *norm_w, double eps,
                        int x_dtype, int64_t M, void *y, int y_dtype, int32_t *acc_out, const float *bias, const float *residual,
                        void *workspace, int64_t workspace_bytes, void *stream)
@@ -414,7 +417,7 @@ static int forward_src(const char *who, const nslq_bitlinear_t *w, const void *x
     if (w->K % 64 != 0 || !aligned16(w->packed))
         return fail(NSLQ_ERR_UNSUPPORTED, "%s: K=%lld must be a multiple of 64 and the weight 16-byte aligned", who, (long long)w->K);
     cudaStream_t st = (cudaStream_t)stream;
-    if (ternary_gemv_src_supported(w->packed, x, x2, norm_w, M, w->K))
+    if (M <= 2 && ternary_gemv_src_supported(w->packed, x, x2, norm_w, M, w->K))
         return ternary_gemv_src_dispatch(w->packed, x, x2, norm_w, eps, x_dtype, (int)M, w->N, w->K, w->weight_scale, y, y_dtype,
                                          acc_out, bias, residual, st);
     const int64_t need = nslq_bitlinear_workspace_bytes(M, w->K);

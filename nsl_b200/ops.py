@@ -202,21 +202,21 @@ class BitLinear:
 
     def forward_rmsnorm(self, x, norm_weight, eps=1e-5, out_dtype=torch.float32, return_acc=False, bias=None, residual=None,
                         out=None):
-        """BitLinear(RMSNorm(x)): one launch up to four tokens (nslq_bitlinear_forward_rmsnorm)."""
+        """BitLinear(RMSNorm(x)): one launch for one or two tokens (nslq_bitlinear_forward_rmsnorm)."""
         _cuda2d(x, "x")
         M = x.shape[0]
         if x.shape[1] != self.K or norm_weight.numel() != self.K or norm_weight.dtype != torch.float32:
             raise ValueError("x [M, %d] and an fp32 norm weight of %d elements expected" % (self.K, self.K))
         y = out if out is not None else torch.empty(M, self.N, dtype=out_dtype, device=x.device)
         acc = torch.empty(M, self.N, dtype=torch.int32, device=x.device) if return_acc else None
-        ws = self.workspace(M)            # used when the one-launch form does not take the call (more than four tokens, very wide rows)
+        ws = self.workspace(M)            # used when the one-launch form does not take the call (more than two tokens, very wide rows)
         check(lib().nslq_bitlinear_forward_rmsnorm(self._h, _ptr(x), _tag(x.dtype), M, _ptr(norm_weight), float(eps), _ptr(y),
                                                    _tag(y.dtype), _ptr(acc), _ptr(bias), _ptr(residual), _ptr(ws),
                                                    ws.numel(), _stream()))
         return (y, acc) if return_acc else y
 
     def forward_swiglu(self, gate, up, out_dtype=torch.float32, return_acc=False, bias=None, residual=None, out=None):
-        """BitLinear(SiLU(gate) * up): one launch up to four tokens (nslq_bitlinear_forward_swiglu)."""
+        """BitLinear(SiLU(gate) * up): one launch for one or two tokens (nslq_bitlinear_forward_swiglu)."""
         _cuda2d(gate, "gate")
         _cuda2d(up, "up")
         M = gate.shape[0]
@@ -224,7 +224,7 @@ class BitLinear:
             raise ValueError("gate and up must both be [M, %d] of one dtype" % self.K)
         y = out if out is not None else torch.empty(M, self.N, dtype=out_dtype, device=gate.device)
         acc = torch.empty(M, self.N, dtype=torch.int32, device=gate.device) if return_acc else None
-        ws = self.workspace(M)            # used when the one-launch form does not take the call (more than four tokens, very wide rows)
+        ws = self.workspace(M)            # used when the one-launch form does not take the call (more than two tokens, very wide rows)
         check(lib().nslq_bitlinear_forward_swiglu(self._h, _ptr(gate), _ptr(up), _tag(gate.dtype), M, _ptr(y), _tag(y.dtype),
                                                   _ptr(acc), _ptr(bias), _ptr(residual), _ptr(ws),
                                                   ws.numel(), _stream()))
