@@ -296,7 +296,7 @@ ternary_gemv_fused_kernel(const FusedParams p)
     }
 }
 
-// ---------------------------------------------------------------- bulk-copy decode kernel (M <= 4)
+// ---------------------------------------------------------------- bulk-copy decode kernel (M <= 2)
 // The same product with the weight slab brought in by the copy engine.  A CTA owns ROWS
 // consecutive output rows; in NSL's layout their packed bytes are ONE contiguous range of the
 // weight (ROWS * K/4 bytes), so the CTA's first instruction issues a handful of cp.async.bulk
@@ -306,14 +306,9 @@ ternary_gemv_fused_kernel(const FusedParams p)
 // ~70 KB and 256 threads, so three are resident per SM: with dependent launch the next two
 // calls of a decode chain already have their weights in flight while this one does arithmetic,
 // which is what a 7 MB matrix needs to approach HBM speed (the whole matrix is in flight at once).
-//
-// Shared-memory reads of the slab: lane (g, t) of an m16n8k32 fragment reads 16 bytes of rows g
-// and g+8; a quarter-warp (the unit of a 128-bit access) is rows {2p, 2p+1} x t = 0..3.  Rows are
-// K/4 bytes apart, unpadded (the copy is linear), so WHICH 16-byte piece lane t takes within an
-// 8-piece block is chosen from the row stride such that the two rows' pieces fall in disjoint
-// banks (`pat` below); any assignment is valid because every row of an MMA uses the same k for
-// the same t and the quantised activations are stored per piece.  The activations' pieces are
-// 80 bytes apart for the same reason.
+// (An mma.sync form of this CTA served three and four tokens; quantising four token rows in every
+// CTA made it 7.3 us where the separate quantiser plus the pre-quantised kernel take 1.7 + 2.9, so
+// those token counts are two launches now and the form is gone.)
 struct BulkParams {
     const uint8_t *w;      // [N][K/4]
     const void *x;         // [M][K] fp32 / fp16 / bf16
@@ -324,7 +319,6 @@ struct BulkParams {
     int64_t N, K;
     int M, y_dtype;
     float weight_scale;
-    uint32_t pat;          // 8 nibbles: piece of lane t in sub-step 0 (nibbles 0-3) and 1 (nibbles 4-7)
     // What the token rows are made of before they are quantised (the launches in front of a decode
     // projection, done by every CTA for itself instead):
     //   SRC_PLAIN    x
@@ -351,7 +345,6 @@ static __device__ __forceinline__ void src_load(const BulkParams &p, int m, int 
 }
 
 constexpr int BULK_THREADS = 256;
-constexpr int BULK_QPIECE = 80;       // bytes between consecutive 64-k pieces of a quantised row
 
 // acc + sum_b (unsigned byte b of a) * (signed byte b of x)
 static __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t x, int acc)
@@ -671,165 +664,6 @@ ternary_gemv_bulk_dp4a_kernel(const BulkParams p)
     }
 }
 
-// The mma.sync form.  ROWS = 64 or 32 output rows per CTA, NW warps.  A warp owns one 16-row tile
-// and every KQ-th sub-step (four pieces per row) of its K range, on eight independent accumulator
-// chains (2 word pairs x 4 position classes).  Used for three and four tokens, where the dp4a form's
-// integer work (proportional to the token count) exceeds this form's.  Measured at one token on a
-// 64-row slab of K = 3200: 2.1 us for this phase with eight warps, more with sixteen (64 registers
-// per thread then, with spills); the tensor pipe itself is busy for under half a microsecond.
-template <typename T, int ROWS, int NW, int SRC>
-__global__ void __launch_bounds__(NW * 32, (NW <= 8) ? 3 : 2)
-ternary_gemv_bulk_kernel(const BulkParams p)
-{
-    using namespace sm100;
-    static_assert(ROWS == 64 || ROWS == 32, "rows per CTA");
-    constexpr int RT = ROWS / 16, KQ = NW / RT, NTHR = NW * 32;
-    static_assert(NW % RT == 0, "warps per tile");
-    extern __shared__ __align__(128) uint8_t smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int row_bytes = (int)(p.K >> 2);
-    const int npieces = row_bytes >> 4;                      // 16-byte pieces (64 trits) per row
-    const int qrow = npieces * BULK_QPIECE;                   // bytes of one quantised token row in shared memory
-    uint8_t *w_s = smem;
-    uint8_t *q_s = smem + (size_t)ROWS * row_bytes;
-    int *red = reinterpret_cast<int *>(q_s + (((size_t)p.M * qrow + 15) & ~(size_t)15));   // [NW][32][4]
-    float *part_f = reinterpret_cast<float *>(red + NW * 32 * 4);         // [NW][FUSED_MAX_M]
-    int *part_i = reinterpret_cast<int *>(part_f + NW * FUSED_MAX_M);     // [NW][FUSED_MAX_M]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(part_i + NW * FUSED_MAX_M);  // [RT]
-    double *part_d = reinterpret_cast<double *>(bars + 4);                // [NW][FUSED_MAX_M]
-    const int64_t n0 = (int64_t)blockIdx.x * ROWS;
-
-    if (threadIdx.x == 0) {
-#pragma unroll
-        for (int r = 0; r < RT; ++r) mbar_init(smem_u32(bars + r), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-#pragma unroll
-        for (int r = 0; r < RT; ++r) {
-            const int64_t first = n0 + 16 * r;
-            const int64_t rows = p.N - first < 16 ? p.N - first : 16;
-            if (rows > 0) {
-                const uint32_t bytes = (uint32_t)(rows * row_bytes);
-                mbar_arrive_expect_tx(smem_u32(bars + r), bytes);
-                bulk_load(smem_u32(w_s + (size_t)16 * r * row_bytes), p.w + first * row_bytes, bytes, smem_u32(bars + r));
-            } else {
-                mbar_arrive(smem_u32(bars + r));
-            }
-        }
-    }
-    // The weights are on their way.  Everything below reads what the preceding kernel produced (x) or
-    // writes what it may still read (y).
-    pdl_wait();
-
-    // ---- quantise the M token rows into shared memory (the arithmetic of act_quant_kernel).  A thread
-    // owns whole groups of 16 consecutive elements: they become the four words of the consumption order
-    // with no exchange between threads.  The row is read twice (maximum, then rounding); the second
-    // read hits the L1 cache.
-    if (SRC == SRC_PLAIN) {
-        const T *x = reinterpret_cast<const T *>(p.x);
-        const int ngroups = (int)(p.K >> 4);
-        for (int m = 0; m < p.M; ++m) {
-            float mx = 0.0f;
-            for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
-                float f[16];
-                Group16<T>::load(x + (int64_t)m * p.K, gi, f);
-                mx = absmax16(f, mx);
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            if (lane == 0) part_f[warp * FUSED_MAX_M + m] = mx;
-        }
-        __syncthreads();                                      // also publishes the barrier initialisation
-        for (int m = 0; m < p.M; ++m) {
-            float scale = 0.0f;
-#pragma unroll
-            for (int w = 0; w < NW; ++w) scale = fmaxf(scale, part_f[w * FUSED_MAX_M + m]);
-            const float inv = __fdiv_rn(127.0f, scale);
-            const bool fast = inv < INFINITY;                 // CTA-uniform; false for inf and NaN
-            int sum = 0;
-            for (int gi = threadIdx.x; gi < ngroups; gi += NTHR) {
-                float f[16];
-                Group16<T>::load(x + (int64_t)m * p.K, gi, f);
-                int q[16];
-                if (fast) quant16<true>(f, inv, q); else quant16<false>(f, inv, q);
-                *reinterpret_cast<uint4 *>(q_s + (size_t)m * qrow + (gi >> 2) * BULK_QPIECE + (gi & 3) * 16) = pack_perm16(q, sum);
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (lane == 0) part_i[warp * FUSED_MAX_M + m] = sum;
-        }
-    } else {
-        float *h_s = reinterpret_cast<float *>(part_d + NW * FUSED_MAX_M);
-#pragma unroll 1
-        for (int m = 0; m < p.M; ++m)
-            src_quantise_row<T, SRC, NW>(p, m, h_s, part_d, part_f, part_i, [&](const int (&q)[16], int gi, int &sum) {
-                *reinterpret_cast<uint4 *>(q_s + (size_t)m * qrow + (gi >> 2) * BULK_QPIECE + (gi & 3) * 16) = pack_perm16(q, sum);
-            });
-    }
-    __syncthreads();
-
-    // ---- multiply: warp (tile, kq) takes sub-steps kq, kq + KQ, ... of its tile
-    const int tile = warp / KQ, kq = warp % KQ;
-    const bool tok_ok = g < p.M;
-    const uint8_t *ra_s = w_s + (size_t)(16 * tile + g) * row_bytes;      // rows g and g+8 of the tile
-    const uint8_t *rb_s = ra_s + (size_t)8 * row_bytes;
-    const uint8_t *xq_s = q_s + (size_t)(tok_ok ? g : 0) * qrow;
-    const int pc0 = (p.pat >> (4 * t)) & 15, pc1 = (p.pat >> (16 + 4 * t)) & 15;
-    int first1 = 8;                                           // lowest piece of the second sub-step (warp-uniform)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) first1 = min(first1, (int)((p.pat >> (16 + 4 * i)) & 15));
-    Acc4 acc0, acc1;
-    acc_zero(acc0);
-    acc_zero(acc1);
-    const bool landed = mbar_wait_warp(smem_u32(bars + tile), 0, 0x801);
-    if (landed) {
-        const int nsub = 2 * ((npieces + 7) >> 3);
-        for (int u = kq; u < nsub; u += KQ) {
-            const int b = u >> 1, sub = u & 1;
-            if (sub && 8 * b + first1 >= npieces) continue;  // warp-uniform: the row ends inside the first sub-step
-            const int pc = 8 * b + (sub ? pc1 : pc0);
-            const bool ok = pc < npieces;
-            const uint4 zero = make_uint4(0, 0, 0, 0);
-            const uint4 ra = ok ? *reinterpret_cast<const uint4 *>(ra_s + pc * 16) : zero;
-            const uint4 rb = ok ? *reinterpret_cast<const uint4 *>(rb_s + pc * 16) : zero;
-            uint4 xq[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                xq[j] = (ok && tok_ok) ? *reinterpret_cast<const uint4 *>(xq_s + pc * BULK_QPIECE + j * 16) : zero;
-            chunk_mma2(acc0, acc1, ra, rb, xq);
-        }
-    }
-    pdl_launch_dependents();                                  // late, as in the dp4a form
-#pragma unroll
-    for (int r = 0; r < 4; ++r) red[(warp * 32 + lane) * 4 + r] = acc_value(acc0, r) + acc_value(acc1, r);
-    __syncthreads();
-
-    // ---- ROWS rows x up to 4 tokens; consecutive threads take consecutive rows
-    for (int e = threadIdx.x; e < ROWS * FUSED_MAX_M; e += NTHR) {
-        const int row = e % ROWS, tok = e / ROWS;
-        const int64_t n = n0 + row;
-        if (tok >= p.M || n >= p.N) continue;
-        const int tl = row >> 4, rr = row & 15;
-        const int src_lane = (rr & 7) * 4 + (tok >> 1);
-        const int src_reg = ((rr >> 3) << 1) | (tok & 1);
-        int a = 0, rs = 0;
-#pragma unroll
-        for (int w = 0; w < KQ; ++w) a += red[((tl * KQ + w) * 32 + src_lane) * 4 + src_reg];
-#pragma unroll
-        for (int w = 0; w < NW; ++w) rs += part_i[w * FUSED_MAX_M + tok];
-        a -= rs;
-        float sc = 0.0f;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) sc = fmaxf(sc, part_f[w * FUSED_MAX_M + tok]);
-        const int64_t o = (int64_t)tok * p.N + n;
-        if (p.acc_out) p.acc_out[o] = a;
-        float v = bitlinear_finalize(a, sc, p.weight_scale);
-        if (p.bias) v = __fadd_rn(v, p.bias[n]);
-        if (p.residual) v = __fadd_rn(v, p.residual[o]);
-        store_out(p.y, p.y_dtype, o, v);
-    }
-}
-
 // Scalar kernel for any K % 4 == 0: one thread per (token, output row), natural
 // order int8 activations, byte loads.  Correctness path for odd shapes only.
 __global__ void __launch_bounds__(128)
@@ -918,16 +752,6 @@ static int pick_fused(const FusedParams &p, cudaStream_t st)
     return launch_fused<T, 8, 1>(p, st);
 }
 
-// Bank-conflict-free piece assignment for a row stride of `row_bytes` (see the kernel's comment): the
-// pieces lanes t = 0..3 take in the two sub-steps of an 8-piece block, one nibble each.
-static uint32_t bulk_pattern(int64_t row_bytes)
-{
-    const int s = (int)((row_bytes / 4) % 32);     // bank distance between consecutive rows
-    if (s == 8 || s == 24) return 0x76325410u;     // {0,1,4,5} then {2,3,6,7}
-    if (s % 8 == 4) return 0x75316420u;            // {0,2,4,6} then {1,3,5,7}
-    return 0x76543210u;                            // s == 16: conflict-free as is; s == 0: two-way conflicts whatever the order
-}
-
 static int bulk_rows(int64_t K)
 {
     const int64_t row_bytes = K / 4;
@@ -936,40 +760,17 @@ static int bulk_rows(int64_t K)
     return 0;
 }
 
-constexpr int BULK_MMA_WARPS = 8;
-
-static size_t bulk_smem(int rows, int M, int64_t K, int nw = 8, bool staged_row = false)
+static size_t bulk_smem(int rows, int M, int64_t K, bool staged_row = false)
 {
-    const size_t qrow = (size_t)(K / 64) * BULK_QPIECE;
-    return (size_t)rows * (K / 4) + (((size_t)M * qrow + 15) & ~(size_t)15) + (size_t)nw * 32 * 4 * 4 + (size_t)nw * FUSED_MAX_M * 8 + 4 * 8 +
-           (size_t)nw * FUSED_MAX_M * 8 + (staged_row ? (size_t)K * 4 : 0) + 64;
-}
-
-template <typename T, int ROWS, int SRC>
-static int launch_bulk(const BulkParams &p, cudaStream_t st)
-{
-    constexpr int NW = BULK_MMA_WARPS;
-    const size_t smem = bulk_smem(ROWS, p.M, p.K, NW, SRC != SRC_PLAIN);
-    static std::atomic<size_t> reserved[kMaxDevices];
-    static std::atomic<int> carved[kMaxDevices];
-    if (!carved[device_index()].load(std::memory_order_acquire)) {
-        // Several CTAs of this kernel (and of the next call) must fit an SM side by side, each with its slab in
-        // shared memory: ask for the largest shared-memory carve-out instead of the one sized for a single CTA.
-        cudaFuncSetAttribute(ternary_gemv_bulk_kernel<T, ROWS, NW, SRC>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        carved[device_index()].store(1, std::memory_order_release);
-    }
-    if (reserve_smem(ternary_gemv_bulk_kernel<T, ROWS, NW, SRC>, reserved, smem) != cudaSuccess)
-        return fail(NSLQ_ERR_CUDA, "ternary_gemv_bulk_kernel: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(cudaGetLastError()));
-    const unsigned ctas = (unsigned)((p.N + ROWS - 1) / ROWS);
-    cudaError_t e = launch_kernel(ternary_gemv_bulk_kernel<T, ROWS, NW, SRC>, dim3(ctas), dim3(NW * 32), smem, st, p);
-    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "ternary_gemv_bulk_kernel: %s", cudaGetErrorString(e));
-    return check_launch("ternary_gemv_bulk_kernel");
+    constexpr size_t nw = 8;
+    return (size_t)rows * (K / 4) + (((size_t)M * K + 15) & ~(size_t)15) + nw * 32 * 4 * 4 + nw * FUSED_MAX_M * 8 + 4 * 8 +
+           nw * FUSED_MAX_M * 8 + (staged_row ? (size_t)K * 4 : 0) + 64;
 }
 
 template <typename T, int ROWS, int MT, int SRC>
 static int launch_bulk_dp4a(const BulkParams &p, cudaStream_t st)
 {
-    const size_t smem = bulk_smem(ROWS, p.M, p.K, 8, SRC != SRC_PLAIN);
+    const size_t smem = bulk_smem(ROWS, p.M, p.K, SRC != SRC_PLAIN);
     static std::atomic<size_t> reserved[kMaxDevices];
     static std::atomic<int> carved[kMaxDevices];
     if (!carved[device_index()].load(std::memory_order_acquire)) {
@@ -987,11 +788,8 @@ static int launch_bulk_dp4a(const BulkParams &p, cudaStream_t st)
 template <typename T, int SRC>
 static int pick_bulk_src(const BulkParams &p, cudaStream_t st)
 {
-    if (p.M <= 2) {                      // one or two tokens: integer ALUs (see the kernel's comment)
-        if (bulk_rows(p.K) == 64) return p.M == 1 ? launch_bulk_dp4a<T, 64, 1, SRC>(p, st) : launch_bulk_dp4a<T, 64, 2, SRC>(p, st);
-        return p.M == 1 ? launch_bulk_dp4a<T, 32, 1, SRC>(p, st) : launch_bulk_dp4a<T, 32, 2, SRC>(p, st);
-    }
-    return bulk_rows(p.K) == 64 ? launch_bulk<T, 64, SRC>(p, st) : launch_bulk<T, 32, SRC>(p, st);
+    if (bulk_rows(p.K) == 64) return p.M == 1 ? launch_bulk_dp4a<T, 64, 1, SRC>(p, st) : launch_bulk_dp4a<T, 64, 2, SRC>(p, st);
+    return p.M == 1 ? launch_bulk_dp4a<T, 32, 1, SRC>(p, st) : launch_bulk_dp4a<T, 32, 2, SRC>(p, st);
 }
 
 template <typename T>
@@ -1006,7 +804,7 @@ static int pick_bulk(const BulkParams &p, cudaStream_t st)
 static bool bulk_supported(int M, int64_t K, bool staged_row = false)
 {
     const int rows = bulk_rows(K);
-    return rows != 0 && bulk_smem(rows, M, K, BULK_MMA_WARPS, staged_row) <= 160 * 1024;
+    return M <= 2 && rows != 0 && bulk_smem(rows, M, K, staged_row) <= 160 * 1024;
 }
 
 int ternary_gemv_status(int *out) { return sm100::read_wait_status(out); }
@@ -1038,7 +836,7 @@ int ternary_gemv_src_dispatch(const uint8_t *w, const void *x, const void *x2, c
                               int M, int64_t N, int64_t K, float weight_scale, void *y, int y_dtype, int32_t *acc_out,
                               const float *bias, const float *residual, cudaStream_t st)
 {
-    BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale, bulk_pattern(K / 4),
+    BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale,
                  norm_w ? SRC_RMSNORM : (x2 ? SRC_SWIGLU : SRC_PLAIN), x2, norm_w, eps};
     return bulk_by_dtype(b, x_dtype, st);
 }
@@ -1048,7 +846,7 @@ int ternary_gemv_fused_dispatch(const uint8_t *w, const void *x, int x_dtype, in
                                 const float *residual, cudaStream_t st)
 {
     if (bulk_supported(M, K)) {
-        BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale, bulk_pattern(K / 4), SRC_PLAIN, nullptr, nullptr, 0.0};
+        BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale, SRC_PLAIN, nullptr, nullptr, 0.0};
         return bulk_by_dtype(b, x_dtype, st);
     }
     FusedParams p{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale};
