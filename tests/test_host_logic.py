@@ -85,3 +85,26 @@ def test_qtensor_num_scales_matches_the_checker():
     assert int(L.nslq_qtensor_num_scales(arr, 2, 1, 2, 0)) == -1          # axis out of range
     assert int(L.nslq_qtensor_num_scales(arr, 2, 2, 1, 0)) == -1          # group size 0
     assert int(L.nslq_qtensor_num_scales(arr, 2, 3, 0, 0)) == -1          # unknown granularity
+
+
+def test_new_entry_points_refuse_bad_arguments_before_any_cuda_call():
+    L = lib()
+    null = C.c_void_p(0)
+    one = C.c_void_p(16)                       # a non-null pointer that is never dereferenced: the checks come first
+    assert L.nslq_embed_gather(null, 3, 10, 8, one, 1, one, null) == -1
+    assert L.nslq_embed_gather(one, 3, 0, 8, one, 1, one, null) == -2
+    assert L.nslq_embed_gather(one, 7, 10, 8, one, 1, one, null) == -1          # dtype tag outside F32/FP16/BF16
+    assert L.nslq_embed_gather(one, 3, 10, 8, one, 0, one, null) == 0           # nothing to do
+    assert L.nslq_rmsnorm_rows(null, one, 1e-5, 1, 8, one, 1, null) == -1
+    assert L.nslq_rmsnorm_rows(one, one, 1e-5, 1, 0, one, 1, null) == -2
+    assert L.nslq_rmsnorm_rows(one, one, 1e-5, 1, 8, one, 0, null) == -1        # F64 output is not offered
+    assert L.nslq_argmax_rows(null, 3, 1, 8, 8, one, null, null) == -1
+    assert L.nslq_argmax_rows(one, 3, 1, 8, 4, one, null, null) == -2           # row stride shorter than the row
+    shape = (C.c_int64 * 2)(4, 4)
+    assert L.nslq_qtensor_quantize(null, 1, shape, 2, 0, 0, 0, 0, one, one, one, null) == -1
+    assert L.nslq_qtensor_quantize(one, 1, shape, 2, 5, 0, 0, 0, one, one, one, null) == -1   # unknown dtype
+    assert L.nslq_qtensor_quantize(one, 1, shape, 9, 0, 0, 0, 0, one, one, one, null) == -2   # ndim
+    assert L.nslq_qtensor_dequantize(one, one, one, shape, 2, 0, 1, 3, 0, one, 1, null) == -1  # axis out of range
+    assert L.nslq_bitlinear_forward_rmsnorm(null, one, 1, 1, one, 1e-5, one, 1, null, null, null, null, 0, null) == -1
+    assert L.nslq_bitlinear_forward_swiglu(null, one, one, 3, 1, one, 1, null, null, null, null, 0, null) == -1
+    assert b"null" in L.nslq_last_error()
