@@ -255,12 +255,34 @@ __global__ void qt_init_minmax_kernel(unsigned long long *mn, unsigned long long
 template <typename T>
 __global__ void __launch_bounds__(256) qt_minmax_kernel(const T *__restrict__ src, QtGeom g, unsigned long long *mn, unsigned long long *mx)
 {
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < g.total; i += (int64_t)gridDim.x * blockDim.x) {
-        const double v = (double)src[i];
-        if (v != v) continue;                       // the reference's comparisons never let a NaN win
-        const int64_t si = qt_scale_index(g, i);
-        atomicMin(mn + si, dkey(v));
-        atomicMax(mx + si, dkey(v));
+    // Whole warps stay in the loop (the tail is padded with NaNs, which never win), so that a warp whose 32
+    // consecutive elements share one scale -- the common case: rows, groups along the last axis, per tensor --
+    // reduces by shuffles and issues one pair of atomics instead of 32 to the same address.
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t rounds = (g.total + stride - 1) / stride;
+    for (int64_t r = 0; r < rounds; ++r) {
+        const int64_t i = r * stride + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+        const bool in = i < g.total;
+        const double v = in ? (double)src[i] : NAN;
+        const int64_t si = in ? qt_scale_index(g, i) : -1;
+        const bool live = v == v;                   // the reference's comparisons never let a NaN win
+        const int64_t s0 = __shfl_sync(0xffffffffu, si, 0);
+        if (__all_sync(0xffffffffu, si == s0)) {
+            if (s0 < 0) continue;
+            double lo = live ? v : INFINITY, hi = live ? v : -INFINITY;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                lo = fmin(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+                hi = fmax(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+            }
+            if ((threadIdx.x & 31) == 0 && lo <= hi) {
+                atomicMin(mn + s0, dkey(lo));
+                atomicMax(mx + s0, dkey(hi));
+            }
+        } else if (live && in) {
+            atomicMin(mn + si, dkey(v));
+            atomicMax(mx + si, dkey(v));
+        }
     }
 }
 
