@@ -20,7 +20,8 @@
 //     ((scale/127) * (float)acc) * weight_scale with separately rounded steps
 //     (crates/nsl-codegen/src/bitnet/phases/finalize.rs:39-53).
 //
-// For M <= 4 the activation quantisation is fused in (ternary_gemv_fused_kernel): each
+// For one or two tokens the activation quantisation is fused in (the bulk-copy kernel below, or
+// ternary_gemv_fused_kernel -- written for up to four -- where a CTA's slab does not fit): each
 // CTA issues its weight loads, then -- while they are in flight -- quantises the token
 // rows itself (absmax by warp shuffles, the reference's exact rounding) into shared memory
 // in the consumption order, so a decode-time linear is one launch and one trip to HBM.
@@ -141,7 +142,8 @@ struct FusedParams {
 
 constexpr int FUSED_MAX_M = 4;
 
-// Decode kernel with the activation quantisation fused in (M <= 4).  A CTA owns TPC row tiles
+// Decode kernel with the activation quantisation fused in (up to four tokens; the library calls it
+// for one or two: beyond that the CTAs' repeated quantisation costs more than a second launch).  A CTA owns TPC row tiles
 // of 16 output rows; each tile's K range is split over KW warps (threads = TPC*KW*32).  The
 // token rows are quantised once per CTA, so a wider CTA repeats less of that work.
 // Dynamic shared memory: [M*K int8 activations, consumption order][TPC*KW*32*4 int reduce]
@@ -809,7 +811,7 @@ static bool bulk_supported(int M, int64_t K, bool staged_row = false)
 
 int ternary_gemv_status(int *out) { return sm100::read_wait_status(out); }
 
-// x [M][K] in its own dtype, M <= 4, K % 64 == 0, 16-byte aligned x and w, M*K <= 160 KiB.
+// x [M][K] in its own dtype, M <= 4 (callers pass M <= 2), K % 64 == 0, 16-byte aligned x and w, M*K <= 160 KiB.
 bool ternary_gemv_fused_supported(const void *w, const void *x, int64_t M, int64_t K)
 {
     return M >= 1 && M <= FUSED_MAX_M && (K % 64 == 0) && aligned16(w) && aligned16(x) && M * K <= 160 * 1024;
