@@ -79,6 +79,20 @@ int64_t nsl_gptq_matmul_cuda(int64_t input, int64_t packed, int64_t group_size, 
  */
 int64_t nsl_qtensor_matmul_mixed_cuda(int64_t x, int64_t qw, int64_t out);
 
+/*
+ * GPU arms of the load-time quantisers for a weight that already lives on the device.  The host objects are
+ * allocated by the caller exactly as the originals allocate them (host buffers; shape, dtype, granularity,
+ * gran_axis, group_size, num_scales resp. k, n, group_size, num_groups filled in) and receive the
+ * reference's bytes.  Each returns its output handle, or 0 after printing the reason.
+ *   nsl_qtensor_quantize_cuda    nsl_qtensor_quantize   (crates/nsl-runtime/src/quantize.rs:283-426), f32 or f64 tensor
+ *   nsl_qtensor_dequantize_cuda  nsl_qtensor_dequantize (quantize.rs:436-537) into a device tensor, f64 (what the
+ *                                original returns) or f32
+ *   nsl_awq_quantize_cuda        nsl_awq_quantize       (crates/nsl-runtime/src/awq.rs:233-260), weight [K,N]
+ */
+int64_t nsl_qtensor_quantize_cuda(int64_t tensor, int64_t qt);
+int64_t nsl_qtensor_dequantize_cuda(int64_t qt, int64_t out);
+int64_t nsl_awq_quantize_cuda(int64_t weight, int64_t group_size, int64_t packed_out);
+
 /* Drops the device copies cached for a weight on every device (call from nsl_awq_free / nsl_qtensor_free). */
 void nsl_quant_forget_cuda(int64_t weight);
 

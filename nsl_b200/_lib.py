@@ -80,6 +80,9 @@ SHIM_SIGNATURES = {
     "nsl_quant_set_stream_cuda": (None, [i64]),
     "nsl_quant_reserve_cuda": (i64, [i64]),
     "nsl_awq_pre_scale_weight_cuda": (i64, [i64, i64, i64, C.c_double, i64]),
+    "nsl_qtensor_quantize_cuda": (i64, [i64, i64]),
+    "nsl_qtensor_dequantize_cuda": (i64, [i64, i64]),
+    "nsl_awq_quantize_cuda": (i64, [i64, i64, i64]),
     "nsl_bitlinear_pack": (i64, [i64, i64, i64, C.c_double]),
     "nsl_bitlinear_forward": (i64, [i64, i64, i64]),
     "nsl_bitlinear_free": (None, [i64]),

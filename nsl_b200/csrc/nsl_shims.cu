@@ -307,6 +307,105 @@ int64_t nsl_awq_pre_scale_weight_cuda(int64_t weight_ptr, int64_t scales_ptr, in
     return out;
 }
 
+// ---------------------------------------------------------------- load-time quantisers
+// The host objects (QuantizedTensor, AwqPackedWeight) keep their buffers in host memory, as the originals do; the
+// tensor to quantise is on the device, the arithmetic runs there and the bytes come back.  Load-time calls: they
+// allocate and synchronise.
+int64_t nsl_qtensor_quantize_cuda(int64_t tensor_ptr, int64_t qt_ptr)
+{
+    if (tensor_ptr == 0 || qt_ptr == 0) { fprintf(stderr, "nsl_qtensor_quantize: null argument\n"); return 0; }
+    const NslTensor *t = reinterpret_cast<const NslTensor *>(tensor_ptr);
+    NslQuantizedTensor *q = reinterpret_cast<NslQuantizedTensor *>(qt_ptr);
+    DeviceScope scope(t, "nsl_qtensor_quantize");
+    if (!scope.ok) return 0;
+    if (t->dtype != NSLQ_DTYPE_F32 && t->dtype != NSLQ_DTYPE_F64) { fprintf(stderr, "nsl_qtensor_quantize: f32 or f64 tensors only\n"); return 0; }
+    if (q->ndim != t->ndim) { fprintf(stderr, "nsl_qtensor_quantize: the QuantizedTensor was allocated for another shape\n"); return 0; }
+    int64_t total = 1;
+    for (int64_t d = 0; d < t->ndim; ++d) {
+        if (q->shape[d] != t->shape[d]) { fprintf(stderr, "nsl_qtensor_quantize: the QuantizedTensor was allocated for another shape\n"); return 0; }
+        total *= t->shape[d];
+    }
+    const int64_t ns = nslq_qtensor_num_scales(t->shape, (int)t->ndim, (int)q->granularity, (int)q->gran_axis, q->group_size);
+    if (ns < 0 || ns != q->num_scales) { fprintf(stderr, "nsl_qtensor_quantize: %s\n", ns < 0 ? nslq_last_error() : "num_scales does not match the granularity"); return 0; }
+    const size_t data_bytes = (size_t)(q->dtype == 1 ? (total + 1) / 2 : total);
+    const size_t off_scale = (data_bytes + 255) & ~(size_t)255, off_zp = off_scale + (((size_t)ns * 4 + 255) & ~(size_t)255);
+    uint8_t *sc = (uint8_t *)scratch_for(off_zp + (size_t)ns);
+    if (!sc) { fprintf(stderr, "nsl_qtensor_quantize: cannot allocate device scratch\n"); return 0; }
+    if (nslq_qtensor_quantize(t->data, (int)t->dtype, t->shape, (int)t->ndim, (int)q->dtype, (int)q->granularity, (int)q->gran_axis,
+                              q->group_size, sc, (float *)(sc + off_scale), sc + off_zp, t_stream) != NSLQ_OK) {
+        fprintf(stderr, "nsl_qtensor_quantize: %s\n", nslq_last_error());
+        return 0;
+    }
+    if (cudaMemcpy(q->data, sc, data_bytes, cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(q->scale, sc + off_scale, (size_t)ns * 4, cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(q->zero_point, sc + off_zp, (size_t)ns, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        fprintf(stderr, "nsl_qtensor_quantize: copy to the host failed\n");
+        return 0;
+    }
+    return qt_ptr;
+}
+
+int64_t nsl_qtensor_dequantize_cuda(int64_t qt_ptr, int64_t out)
+{
+    if (qt_ptr == 0 || out == 0) { fprintf(stderr, "nsl_qtensor_dequantize: null argument\n"); return 0; }
+    const NslQuantizedTensor *q = reinterpret_cast<const NslQuantizedTensor *>(qt_ptr);
+    NslTensor *y = reinterpret_cast<NslTensor *>(out);
+    DeviceScope scope(y, "nsl_qtensor_dequantize");
+    if (!scope.ok) return 0;
+    if (y->dtype != NSLQ_DTYPE_F32 && y->dtype != NSLQ_DTYPE_F64) { fprintf(stderr, "nsl_qtensor_dequantize: f32 or f64 output only\n"); return 0; }
+    int64_t total = 1;
+    for (int64_t d = 0; d < q->ndim; ++d) total *= q->shape[d];
+    if (y->len != total) { fprintf(stderr, "nsl_qtensor_dequantize: output of %lld elements for a tensor of %lld\n", (long long)y->len, (long long)total); return 0; }
+    const int64_t ns = q->num_scales;
+    const size_t data_bytes = (size_t)(q->dtype == 1 ? (total + 1) / 2 : total);
+    const size_t off_scale = (data_bytes + 255) & ~(size_t)255, off_zp = off_scale + (((size_t)ns * 4 + 255) & ~(size_t)255);
+    uint8_t *sc = (uint8_t *)scratch_for(off_zp + (size_t)ns);
+    if (!sc || cudaMemcpyAsync(sc, q->data, data_bytes, cudaMemcpyHostToDevice, t_stream) != cudaSuccess ||
+        cudaMemcpyAsync(sc + off_scale, q->scale, (size_t)ns * 4, cudaMemcpyHostToDevice, t_stream) != cudaSuccess ||
+        cudaMemcpyAsync(sc + off_zp, q->zero_point, (size_t)ns, cudaMemcpyHostToDevice, t_stream) != cudaSuccess) {
+        fprintf(stderr, "nsl_qtensor_dequantize: cannot stage the quantized tensor on the device\n");
+        return 0;
+    }
+    if (nslq_qtensor_dequantize(sc, (const float *)(sc + off_scale), sc + off_zp, q->shape, (int)q->ndim, (int)q->dtype, (int)q->granularity,
+                                (int)q->gran_axis, q->group_size, y->data, (int)y->dtype, t_stream) != NSLQ_OK) {
+        fprintf(stderr, "nsl_qtensor_dequantize: %s\n", nslq_last_error());
+        return 0;
+    }
+    if (cudaStreamSynchronize(t_stream) != cudaSuccess) return 0;      // the scratch may be reused by the next call
+    return out;
+}
+
+int64_t nsl_awq_quantize_cuda(int64_t weight_ptr, int64_t group_size, int64_t packed_out)
+{
+    if (weight_ptr == 0 || packed_out == 0) { fprintf(stderr, "nsl_awq_quantize: null argument\n"); return 0; }
+    const NslTensor *t = reinterpret_cast<const NslTensor *>(weight_ptr);
+    NslAwqPackedWeight *pw = reinterpret_cast<NslAwqPackedWeight *>(packed_out);
+    if (t->ndim != 2) { fprintf(stderr, "nsl_awq_quantize: weight must be 2D (got %lldD)\n", (long long)t->ndim); return 0; }
+    DeviceScope scope(t, "nsl_awq_quantize");
+    if (!scope.ok) return 0;
+    const int64_t K = t->shape[0], N = t->shape[1];
+    if (group_size <= 0 || pw->k != K || pw->n != N || pw->group_size != group_size || pw->num_groups != (K + group_size - 1) / group_size) {
+        fprintf(stderr, "nsl_awq_quantize: the AwqPackedWeight was allocated for another shape or group size\n");
+        return 0;
+    }
+    if (t->dtype != NSLQ_DTYPE_F32 && t->dtype != NSLQ_DTYPE_F64) { fprintf(stderr, "nsl_awq_quantize: f32 or f64 weights only\n"); return 0; }
+    const size_t data_bytes = (size_t)((K * N + 1) / 2), tab = (size_t)pw->num_groups * (size_t)N * 8;
+    const size_t off_s = (data_bytes + 255) & ~(size_t)255, off_z = off_s + ((tab + 255) & ~(size_t)255);
+    uint8_t *sc = (uint8_t *)scratch_for(off_z + tab);
+    if (!sc) { fprintf(stderr, "nsl_awq_quantize: cannot allocate device scratch\n"); return 0; }
+    if (nslq_awq_quantize_kn(t->data, (int)t->dtype, K, N, group_size, sc, (double *)(sc + off_s), (double *)(sc + off_z), t_stream) != NSLQ_OK) {
+        fprintf(stderr, "nsl_awq_quantize: %s\n", nslq_last_error());
+        return 0;
+    }
+    if (cudaStreamSynchronize(t_stream) != cudaSuccess || cudaMemcpy(pw->data, sc, data_bytes, cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(pw->scales, sc + off_s, tab, cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(pw->zeros, sc + off_z, tab, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        fprintf(stderr, "nsl_awq_quantize: copy to the host failed\n");
+        return 0;
+    }
+    return packed_out;
+}
+
 // ---------------------------------------------------------------- BitLinear trio
 struct NslBitlinearHandle {
     nslq_bitlinear_t *w;

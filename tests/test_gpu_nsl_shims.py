@@ -30,7 +30,7 @@ class AwqPackedWeight(C.Structure):
                 ("group_size", C.c_int64), ("num_groups", C.c_int64), ("refcount", C.c_int64)]
 
 
-TAG = {torch.float32: 1, torch.float16: 2, torch.bfloat16: 3}
+TAG = {torch.float64: 0, torch.float32: 1, torch.float16: 2, torch.bfloat16: 3}
 
 
 def nsl_tensor(t):
@@ -218,3 +218,54 @@ def test_reserved_code_is_rejected(lib, oracle, kat):
     layer = ops.BitLinear(torch.from_numpy(good).cuda(), 1.0)
     layer.validate()
     assert layer.invalid_bytes() == 0
+
+
+def _empty_qtensor(oracle, shape, dtype, gran, axis, gs):
+    """A QuantizedTensor as nsl_qtensor_quantize allocates it: host buffers sized by compute_num_scales."""
+    total = int(np.prod(shape))
+    ns = int(oracle.qtensor_num_scales(tuple(shape), gran, axis, gs))
+    keep = (np.zeros((total + 1) // 2 if dtype == 1 else total, np.uint8), np.zeros(ns, np.float32), np.zeros(ns, np.uint8),
+            (C.c_int64 * len(shape))(*shape))
+    q = QuantizedTensor(keep[0].ctypes.data, keep[1].ctypes.data, keep[2].ctypes.data, keep[3], len(shape), dtype, gran, axis, gs, ns, 1)
+    q._keep = keep
+    return q, keep
+
+
+@pytest.mark.parametrize("src_dt", [torch.float64, torch.float32])
+def test_load_time_quantisers_fill_host_objects_with_the_reference_bytes(lib, oracle, src_dt):
+    rng = np.random.default_rng(8)
+    for shape, dtype, gran, axis, gs in [((64, 48), 1, 2, 0, 16), ((33, 40), 0, 1, 1, 0), ((6, 10, 4), 0, 0, 0, 0), ((128, 24), 1, 2, 1, 8)]:
+        w = (rng.standard_normal(shape) * 2).astype(np.float32 if src_dt == torch.float32 else np.float64)
+        wt = torch.from_numpy(w).cuda()
+        ws = nsl_tensor(wt)
+        q, (data, scale, zp, _) = _empty_qtensor(oracle, shape, dtype, gran, axis, gs)
+        assert lib.nsl_qtensor_quantize_cuda(C.addressof(ws), C.addressof(q)) == C.addressof(q)
+        want = oracle.qtensor_quantize(w.astype(np.float64), dtype, gran, axis, gs)
+        used = 1 if gran == 0 else (shape[axis] if gran == 1 else int(np.prod(shape[:axis], dtype=np.int64)) * ((shape[axis] + gs - 1) // gs))
+        assert np.array_equal(data, want[0]) and np.array_equal(zp, want[2])
+        assert np.array_equal(scale[:used].view(np.uint32), want[1][:used].view(np.uint32))
+        # and back, into a device tensor of the type the original returns
+        out = torch.empty(shape, device="cuda", dtype=torch.float64)
+        os_ = nsl_tensor(out)
+        assert lib.nsl_qtensor_dequantize_cuda(C.addressof(q), C.addressof(os_)) == C.addressof(os_)
+        ref = oracle.qtensor_dequantize(*want, shape, dtype, gran, axis, gs)
+        assert np.array_equal(out.cpu().numpy().view(np.uint64), ref.view(np.uint64))
+    # AWQ packing of a [K,N] weight
+    K, N, gs = 96, 40, 32
+    w = (rng.standard_normal((K, N)) * 0.05).astype(np.float32 if src_dt == torch.float32 else np.float64)
+    wt = torch.from_numpy(w).cuda()
+    ws = nsl_tensor(wt)
+    G = (K + gs - 1) // gs
+    keep = (np.zeros((K * N + 1) // 2, np.uint8), np.zeros(G * N, np.float64), np.zeros(G * N, np.float64))
+    pw = AwqPackedWeight(keep[0].ctypes.data, keep[1].ctypes.data, keep[2].ctypes.data, K, N, gs, G, 1)
+    assert lib.nsl_awq_quantize_cuda(C.addressof(ws), gs, C.addressof(pw)) == C.addressof(pw)
+    data, scales, zeros = oracle.awq_quantize(w.astype(np.float64), gs)
+    assert np.array_equal(keep[0], np.asarray(data).ravel())
+    assert np.array_equal(keep[1].view(np.uint64), np.asarray(scales, np.float64).ravel().view(np.uint64))
+    assert np.array_equal(keep[2].view(np.uint64), np.asarray(zeros, np.float64).ravel().view(np.uint64))
+    # refusals: a CPU tensor, a QuantizedTensor allocated for another shape
+    cpu = nsl_tensor(wt)
+    cpu.device = 0
+    assert lib.nsl_awq_quantize_cuda(C.addressof(cpu), gs, C.addressof(pw)) == 0
+    q, _ = _empty_qtensor(oracle, (K, N + 1), 0, 0, 0, 0)
+    assert lib.nsl_qtensor_quantize_cuda(C.addressof(ws), C.addressof(q)) == 0
