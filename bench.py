@@ -716,7 +716,7 @@ def run_decoder(torch, batch, peaks, prompt=512, steps=256, warm=8, layers=None)
            "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                         "frac": round(ach / peaks["hbm_gbs"], 4), "bytes_per_step": step_bytes,
                         "note": "ternary weights + bf16 lm_head + KV read at mid-run context; a decode step is library launches "
-                                "(embedding rows, RMSNorm and SiLU*up inside the projections' launches up to two tokens, RoPE + KV "
+                                "(embedding rows, RMSNorm and SiLU*up inside the projections' launches at one token per sequence batch of one, RoPE + KV "
                                 "append + attention, final norm, argmax) except the lm_head's bf16 GEMM (cuBLAS); the prefill "
                                 "glue is PyTorch"},
            "ceiling_tok_s": round(batch / (step_bytes / (peaks["hbm_gbs"] * 1e9)), 1)}

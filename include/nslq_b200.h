@@ -243,9 +243,9 @@ int nslq_bitlinear_forward_quantized(const nslq_bitlinear_t *w, const int8_t *q_
  * nslq_bitlinear_forward with the launch in front of it folded in: the input rows are
  *   RMSNorm(x) with `norm_weight`, `eps`      (= nslq_rmsnorm_act_quant_i8, then forward_quantized), or
  *   SiLU(gate) * up                           (= nslq_swiglu_act_quant_i8,  then forward_quantized),
- * with the same bits as those two calls.  For one or two tokens (a decode step) every CTA of the one launch
+ * with the same bits as those two calls.  For one token (a decode step) every CTA of the one launch
  * forms and quantises the rows for itself -- NSL's BitNet kernel config names this prologue (`fused_rmsnorm`,
- * crates/nsl-codegen/src/bitnet/config.rs:23-31) and never emits it; above two tokens (measured: the CTAs' repeated work then costs more than a launch), or when a row
+ * crates/nsl-codegen/src/bitnet/config.rs:23-31) and never emits it; from two tokens on (measured: the CTAs' repeated work then costs more than a launch), or when a row
  * does not fit the CTA's shared memory next to the weights, the call issues the two launches itself and
  * needs the workspace of nslq_bitlinear_forward (pass it always).  K % 64 == 0; gate, up: [M,K], packed.
  */
@@ -257,6 +257,20 @@ int nslq_bitlinear_forward_swiglu(const nslq_bitlinear_t *w, const void *gate, c
                                   void *y, int y_dtype, int32_t *acc_out,
                                   const float *bias, const float *residual,
                                   void *workspace, int64_t workspace_bytes, void *stream);
+
+/*
+ * Sibling projections of the same rows -- q, k and v of an attention block, gate and up of an MLP: the
+ * reference's `BitLinear.forward` is called once per projection on the same normalised input
+ * (stdlib/nsl/quant/bitlinear.nsl:74-88) -- as one call.  ys[i] [M, layers[i]->N] gets exactly the bits of
+ * nslq_bitlinear_forward_rmsnorm(layers[i], x, ..., ys[i], ...) (norm_weight != NULL) or of
+ * nslq_bitlinear_forward(layers[i], x, ..., ys[i], ...) (norm_weight == NULL) without bias or residual.  For one
+ * token all layers share ONE launch (each CTA quantises the rows for itself and multiplies a slab of one
+ * layer's weights); above that the rows are normalised and quantised once and each layer is one launch, which
+ * needs the workspace of nslq_bitlinear_forward (pass it always).  1 <= n_layers <= 4; all layers the same K, K % 64 == 0.
+ */
+int nslq_bitlinear_forward_multi(const nslq_bitlinear_t *const *layers, int n_layers, const void *x, int x_dtype, int64_t M,
+                                 const float *norm_weight, double eps, void *const *ys, int y_dtype,
+                                 void *workspace, int64_t workspace_bytes, void *stream);
 
 /*
  * nslq_bitlinear_forward without a caller workspace.  (No counterpart in NSL: the

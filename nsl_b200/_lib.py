@@ -28,6 +28,7 @@ SIGNATURES = {
     "nslq_bitlinear_forward_quantized": (i32, [vp, vp, vp, vp, i64, vp, i32, vp, vp, vp, vp]),
     "nslq_bitlinear_forward_rmsnorm": (i32, [vp, vp, i32, i64, vp, C.c_double, vp, i32, vp, vp, vp, vp, i64, vp]),
     "nslq_bitlinear_forward_swiglu": (i32, [vp, vp, vp, i32, i64, vp, i32, vp, vp, vp, vp, i64, vp]),
+    "nslq_bitlinear_forward_multi": (i32, [vp, i32, vp, i32, i64, vp, C.c_double, vp, i32, vp, i64, vp]),
     "nslq_bitlinear_forward_noalloc": (i32, [vp, vp, i32, i64, vp, i32, vp]),
     "nslq_noalloc_scratch_bytes": (i64, []),
     "nslq_w4a16_create_nk": (i32, [vp, vp, i32, vp, i32, i64, i64, i64, C.POINTER(vp)]),

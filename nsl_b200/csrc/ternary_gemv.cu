@@ -311,6 +311,7 @@ ternary_gemv_fused_kernel(const FusedParams p)
 // (An mma.sync form of this CTA served three and four tokens; quantising four token rows in every
 // CTA made it 7.3 us where the separate quantiser plus the pre-quantised kernel take 1.7 + 2.9, so
 // those token counts are two launches now and the form is gone.)
+constexpr int BULK_MAX_LAYERS = 4;
 struct BulkParams {
     const uint8_t *w;      // [N][K/4]
     const void *x;         // [M][K] fp32 / fp16 / bf16
@@ -330,6 +331,19 @@ struct BulkParams {
     const void *x2;        // [M][K], SRC_SWIGLU
     const float *norm_w;   // [K], SRC_RMSNORM
     double eps;
+    // Sibling projections of the same token rows (q/k/v, gate/up) in the same launch: CTAs from
+    // sib[i].first_cta on multiply sibling i's weights instead.  Every CTA quantises the rows for itself
+    // anyway, so siblings cost nothing but their own CTAs, and one launch replaces a fork onto side
+    // streams and its join.  acc_out and residual are null when there are siblings.
+    int nsib;
+    struct Sibling {
+        const uint8_t *w;
+        void *y;
+        const float *bias;
+        int64_t N;
+        float weight_scale;
+        unsigned first_cta;
+    } sib[BULK_MAX_LAYERS - 1];
 };
 enum { SRC_PLAIN = 0, SRC_RMSNORM = 1, SRC_SWIGLU = 2 };
 
@@ -471,7 +485,20 @@ ternary_gemv_bulk_dp4a_kernel(const BulkParams p)
     int *part_i = reinterpret_cast<int *>(part_f + 8 * FUSED_MAX_M);      // [8][FUSED_MAX_M]
     uint64_t *bars = reinterpret_cast<uint64_t *>(part_i + 8 * FUSED_MAX_M);   // [RT]
     double *part_d = reinterpret_cast<double *>(bars + 4);                // [8][FUSED_MAX_M]
-    const int64_t n0 = (int64_t)blockIdx.x * ROWS;
+    // this CTA's projection: the first one, or the last sibling whose range the CTA index has reached
+    const uint8_t *lw = p.w;
+    void *ly = p.y;
+    const float *lbias = p.bias;
+    int64_t lN = p.N;
+    float lws = p.weight_scale;
+    unsigned cta0 = 0;
+#pragma unroll
+    for (int i = 0; i < BULK_MAX_LAYERS - 1; ++i) {
+        if (i < p.nsib && blockIdx.x >= p.sib[i].first_cta) {
+            lw = p.sib[i].w; ly = p.sib[i].y; lbias = p.sib[i].bias; lN = p.sib[i].N; lws = p.sib[i].weight_scale; cta0 = p.sib[i].first_cta;
+        }
+    }
+    const int64_t n0 = (int64_t)(blockIdx.x - cta0) * ROWS;
 
     if (threadIdx.x == 0) {
 #pragma unroll
@@ -480,11 +507,11 @@ ternary_gemv_bulk_dp4a_kernel(const BulkParams p)
 #pragma unroll
         for (int r = 0; r < RT; ++r) {
             const int64_t first = n0 + 16 * r;
-            const int64_t rows = p.N - first < 16 ? p.N - first : 16;
+            const int64_t rows = lN - first < 16 ? lN - first : 16;
             if (rows > 0) {
                 const uint32_t bytes = (uint32_t)(rows * row_bytes);
                 mbar_arrive_expect_tx(smem_u32(bars + r), bytes);
-                bulk_load(smem_u32(w_s + (size_t)16 * r * row_bytes), p.w + first * row_bytes, bytes, smem_u32(bars + r));
+                bulk_load(smem_u32(w_s + (size_t)16 * r * row_bytes), lw + first * row_bytes, bytes, smem_u32(bars + r));
             } else {
                 mbar_arrive(smem_u32(bars + r));
             }
@@ -651,17 +678,17 @@ ternary_gemv_bulk_dp4a_kernel(const BulkParams p)
     const int64_t n = n0 + 8 * rset + myrow;
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
-        if ((lane & 3) == m && m < p.M && n < p.N) {
+        if ((lane & 3) == m && m < p.M && n < lN) {
             int rs = 0;
 #pragma unroll
             for (int w = 0; w < 8; ++w) rs += part_i[w * FUSED_MAX_M + m];
             const int a = rowtot[m] - rs;
-            const int64_t o = (int64_t)m * p.N + n;
+            const int64_t o = (int64_t)m * lN + n;
             if (p.acc_out) p.acc_out[o] = a;
-            float v = bitlinear_finalize(a, scale[m], p.weight_scale);
-            if (p.bias) v = __fadd_rn(v, p.bias[n]);
+            float v = bitlinear_finalize(a, scale[m], lws);
+            if (lbias) v = __fadd_rn(v, lbias[n]);
             if (p.residual) v = __fadd_rn(v, p.residual[o]);
-            store_out(p.y, p.y_dtype, o, v);
+            store_out(ly, p.y_dtype, o, v);
         }
     }
 }
@@ -781,8 +808,13 @@ static int launch_bulk_dp4a(const BulkParams &p, cudaStream_t st)
     }
     if (reserve_smem(ternary_gemv_bulk_dp4a_kernel<T, ROWS, MT, SRC>, reserved, smem) != cudaSuccess)
         return fail(NSLQ_ERR_CUDA, "ternary_gemv_bulk_dp4a_kernel: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(cudaGetLastError()));
-    const unsigned ctas = (unsigned)((p.N + ROWS - 1) / ROWS);
-    cudaError_t e = launch_kernel(ternary_gemv_bulk_dp4a_kernel<T, ROWS, MT, SRC>, dim3(ctas), dim3(BULK_THREADS), smem, st, p);
+    BulkParams q = p;
+    unsigned ctas = (unsigned)((p.N + ROWS - 1) / ROWS);
+    for (int i = 0; i < q.nsib; ++i) {
+        q.sib[i].first_cta = ctas;
+        ctas += (unsigned)((q.sib[i].N + ROWS - 1) / ROWS);
+    }
+    cudaError_t e = launch_kernel(ternary_gemv_bulk_dp4a_kernel<T, ROWS, MT, SRC>, dim3(ctas), dim3(BULK_THREADS), smem, st, q);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "ternary_gemv_bulk_dp4a_kernel: %s", cudaGetErrorString(e));
     return check_launch("ternary_gemv_bulk_dp4a_kernel");
 }
@@ -790,6 +822,10 @@ static int launch_bulk_dp4a(const BulkParams &p, cudaStream_t st)
 template <typename T, int SRC>
 static int pick_bulk_src(const BulkParams &p, cudaStream_t st)
 {
+    if (SRC != SRC_PLAIN) {                                   // the prologue forms take one token (see their callers)
+        if (p.M != 1) return fail(NSLQ_ERR_UNSUPPORTED, "BitLinear: the one-launch RMSNorm / SiLU*up forms take one token, not %d", p.M);
+        return bulk_rows(p.K) == 64 ? launch_bulk_dp4a<T, 64, 1, SRC>(p, st) : launch_bulk_dp4a<T, 32, 1, SRC>(p, st);
+    }
     if (bulk_rows(p.K) == 64) return p.M == 1 ? launch_bulk_dp4a<T, 64, 1, SRC>(p, st) : launch_bulk_dp4a<T, 64, 2, SRC>(p, st);
     return p.M == 1 ? launch_bulk_dp4a<T, 32, 1, SRC>(p, st) : launch_bulk_dp4a<T, 32, 2, SRC>(p, st);
 }
@@ -827,10 +863,10 @@ static int bulk_by_dtype(const BulkParams &b, int x_dtype, cudaStream_t st)
     }
 }
 
-// Up to four token rows whose RMSNorm (norm_w != null) or SiLU(x) * x2 (x2 != null) the CTAs form for themselves.
+// One token row whose RMSNorm (norm_w != null) or SiLU(x) * x2 (x2 != null) the CTAs form for themselves.
 bool ternary_gemv_src_supported(const void *w, const void *x, const void *x2, const float *norm_w, int64_t M, int64_t K)
 {
-    return M >= 1 && M <= FUSED_MAX_M && (K % 64 == 0) && aligned16(w) && aligned16(x) && (!x2 || aligned16(x2)) &&
+    return M == 1 && (K % 64 == 0) && aligned16(w) && aligned16(x) && (!x2 || aligned16(x2)) &&
            (!norm_w || aligned16(norm_w)) && bulk_supported((int)M, K, true);
 }
 
@@ -839,7 +875,21 @@ int ternary_gemv_src_dispatch(const uint8_t *w, const void *x, const void *x2, c
                               const float *bias, const float *residual, cudaStream_t st)
 {
     BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale,
-                 norm_w ? SRC_RMSNORM : (x2 ? SRC_SWIGLU : SRC_PLAIN), x2, norm_w, eps};
+                 norm_w ? SRC_RMSNORM : (x2 ? SRC_SWIGLU : SRC_PLAIN), x2, norm_w, eps, 0, {}};
+    return bulk_by_dtype(b, x_dtype, st);
+}
+
+// The same for up to four projections of the same token rows in one launch (q/k/v, gate/up): ws[i] [N[i]][K/4],
+// ys[i] [M][N[i]]; no accumulator output and no residual.  The callers have checked ternary_gemv_src_supported
+// for every weight pointer.
+int ternary_gemv_multi_dispatch(int nl, const uint8_t *const *ws, const int64_t *Ns, const float *weight_scales, const float *const *biases,
+                                void *const *ys, const void *x, const float *norm_w, double eps, int x_dtype, int M, int64_t K,
+                                int y_dtype, cudaStream_t st)
+{
+    if (nl < 1 || nl > BULK_MAX_LAYERS) return fail(NSLQ_ERR_ARG, "BitLinear: %d projections in one launch, at most %d", nl, BULK_MAX_LAYERS);
+    BulkParams b{ws[0], x, ys[0], nullptr, biases[0], nullptr, Ns[0], K, M, y_dtype, weight_scales[0],
+                 norm_w ? SRC_RMSNORM : SRC_PLAIN, nullptr, norm_w, eps, nl - 1, {}};
+    for (int i = 1; i < nl; ++i) b.sib[i - 1] = BulkParams::Sibling{ws[i], ys[i], biases[i], Ns[i], weight_scales[i], 0u};
     return bulk_by_dtype(b, x_dtype, st);
 }
 
@@ -848,7 +898,7 @@ int ternary_gemv_fused_dispatch(const uint8_t *w, const void *x, int x_dtype, in
                                 const float *residual, cudaStream_t st)
 {
     if (bulk_supported(M, K)) {
-        BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale, SRC_PLAIN, nullptr, nullptr, 0.0};
+        BulkParams b{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale, SRC_PLAIN, nullptr, nullptr, 0.0, 0, {}};
         return bulk_by_dtype(b, x_dtype, st);
     }
     FusedParams p{w, x, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale};

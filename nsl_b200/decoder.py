@@ -6,9 +6,9 @@ library replaces (NSL has them in stdlib/nsl/nn/{norms,rope,gqa}.nsl and
 stdlib/nsl/inference/generate.nsl).  Every projection of every layer (q, k, v, o, gate, up, down) runs
 through nsl_b200.ops.BitLinear, i.e. the C ABI.  A decode step is library launches throughout, the
 lm_head's bf16 GEMM aside: the embedding rows (nslq_embed_gather), the RMSNorms (inside the projections'
-launches up to two tokens, nslq_rmsnorm_act_quant_i8 above), the attention of the new token (RoPE, cache
-append, softmax(qK)V: nslq_decode_attention), SiLU(gate)*up (inside the down projection's launch up to
-two tokens), the final norm (nslq_rmsnorm_rows) and the greedy choice (nslq_argmax_rows, which also
+launches for one token, nslq_rmsnorm_act_quant_i8 above), the attention of the new token (RoPE, cache
+append, softmax(qK)V: nslq_decode_attention), SiLU(gate)*up (inside the down projection's launch for
+one token), the final norm (nslq_rmsnorm_rows) and the greedy choice (nslq_argmax_rows, which also
 advances the position).  Weights are random ternary (no
 checkpoint is available offline), so the numbers are throughput numbers, not quality numbers.
 
@@ -118,7 +118,7 @@ class BitNetDecoder:
 
     def _swiglu_down(self, layer, g, u, residual):
         """down(silu(gate) * up) + residual: one launch forms and quantises the product, one multiplies."""
-        if g.shape[0] <= 2:               # a decode step of one or two tokens: the product is formed inside the projection's launch
+        if g.shape[0] == 1:               # a decode step of one token: the product is formed inside the projection's launch
             return layer.forward_swiglu(g, u, out_dtype=torch.float32, residual=residual)
         qa = ops.swiglu_act_quant_i8(g, u, plain=False, perm=True)
         return layer.forward_quantized(qa, out_dtype=torch.float32, residual=residual)
@@ -126,12 +126,12 @@ class BitNetDecoder:
     def _norm_lin_shared(self, layers, x2d, norm_w):
         """RMSNorm, then several projections of the normalised rows.  More than two rows: one
         launch normalises and quantises (the normalised rows never reach memory) and the
-        projections share the result; one or two: every projection's launch normalises and
-        quantises for itself (nslq_bitlinear_forward_rmsnorm), so the norm is no launch at all."""
+        projections share the result; one row: norm and all projections are ONE launch whose CTAs each
+        normalise and quantise for themselves (nslq_bitlinear_forward_multi), so neither the norm nor the
+        siblings' side streams exist."""
         M = x2d.shape[0]
-        if M <= 2:
-            eps = self.cfg.eps
-            return self._siblings([lambda l=l: l.forward_rmsnorm(x2d, norm_w, eps, out_dtype=torch.bfloat16) for l in layers])
+        if M == 1:
+            return ops.BitLinear.forward_multi(layers, x2d, norm_w, self.cfg.eps, out_dtype=torch.bfloat16)
         qa = ops.rmsnorm_act_quant_i8(x2d, norm_w, self.cfg.eps, plain=False, perm=True)
         return self._siblings([lambda l=l: l.forward_quantized(qa, out_dtype=torch.bfloat16) for l in layers])
 

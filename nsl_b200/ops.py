@@ -202,21 +202,21 @@ class BitLinear:
 
     def forward_rmsnorm(self, x, norm_weight, eps=1e-5, out_dtype=torch.float32, return_acc=False, bias=None, residual=None,
                         out=None):
-        """BitLinear(RMSNorm(x)): one launch for one or two tokens (nslq_bitlinear_forward_rmsnorm)."""
+        """BitLinear(RMSNorm(x)): one launch for one token (nslq_bitlinear_forward_rmsnorm)."""
         _cuda2d(x, "x")
         M = x.shape[0]
         if x.shape[1] != self.K or norm_weight.numel() != self.K or norm_weight.dtype != torch.float32:
             raise ValueError("x [M, %d] and an fp32 norm weight of %d elements expected" % (self.K, self.K))
         y = out if out is not None else torch.empty(M, self.N, dtype=out_dtype, device=x.device)
         acc = torch.empty(M, self.N, dtype=torch.int32, device=x.device) if return_acc else None
-        ws = self.workspace(M)            # used when the one-launch form does not take the call (more than two tokens, very wide rows)
+        ws = self.workspace(M)            # used when the one-launch form does not take the call (more than one token, very wide rows)
         check(lib().nslq_bitlinear_forward_rmsnorm(self._h, _ptr(x), _tag(x.dtype), M, _ptr(norm_weight), float(eps), _ptr(y),
                                                    _tag(y.dtype), _ptr(acc), _ptr(bias), _ptr(residual), _ptr(ws),
                                                    ws.numel(), _stream()))
         return (y, acc) if return_acc else y
 
     def forward_swiglu(self, gate, up, out_dtype=torch.float32, return_acc=False, bias=None, residual=None, out=None):
-        """BitLinear(SiLU(gate) * up): one launch for one or two tokens (nslq_bitlinear_forward_swiglu)."""
+        """BitLinear(SiLU(gate) * up): one launch for one token (nslq_bitlinear_forward_swiglu)."""
         _cuda2d(gate, "gate")
         _cuda2d(up, "up")
         M = gate.shape[0]
@@ -224,11 +224,30 @@ class BitLinear:
             raise ValueError("gate and up must both be [M, %d] of one dtype" % self.K)
         y = out if out is not None else torch.empty(M, self.N, dtype=out_dtype, device=gate.device)
         acc = torch.empty(M, self.N, dtype=torch.int32, device=gate.device) if return_acc else None
-        ws = self.workspace(M)            # used when the one-launch form does not take the call (more than two tokens, very wide rows)
+        ws = self.workspace(M)            # used when the one-launch form does not take the call (more than one token, very wide rows)
         check(lib().nslq_bitlinear_forward_swiglu(self._h, _ptr(gate), _ptr(up), _tag(gate.dtype), M, _ptr(y), _tag(y.dtype),
                                                   _ptr(acc), _ptr(bias), _ptr(residual), _ptr(ws),
                                                   ws.numel(), _stream()))
         return (y, acc) if return_acc else y
+
+    @staticmethod
+    def forward_multi(layers, x, norm_weight=None, eps=1e-5, out_dtype=torch.float32):
+        """Sibling projections (q/k/v, gate/up) of the same rows, optionally behind an RMSNorm, as one call
+        (nslq_bitlinear_forward_multi): one launch for one token.  Returns one [M, N_i] tensor per layer."""
+        import ctypes as C
+        _cuda2d(x, "x")
+        M, K = x.shape
+        if not 1 <= len(layers) <= 4 or any(l.K != K for l in layers):
+            raise ValueError("1 to 4 layers with K = %d expected" % K)
+        if norm_weight is not None and (norm_weight.numel() != K or norm_weight.dtype != torch.float32):
+            raise ValueError("an fp32 norm weight of %d elements expected" % K)
+        ys = [torch.empty(M, l.N, dtype=out_dtype, device=x.device) for l in layers]
+        ws = layers[0].workspace(M)
+        hs = (C.c_void_p * len(layers))(*[l._h for l in layers])
+        ps = (C.c_void_p * len(layers))(*[y.data_ptr() for y in ys])
+        check(lib().nslq_bitlinear_forward_multi(hs, len(layers), _ptr(x), _tag(x.dtype), M, _ptr(norm_weight), float(eps), ps,
+                                                 _tag(out_dtype), _ptr(ws), ws.numel(), _stream()))
+        return ys
 
     def forward_noalloc(self, x, out):
         """nslq_bitlinear_forward_noalloc: the scratch is the library's built-in area, so the

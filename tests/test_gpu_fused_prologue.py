@@ -1,5 +1,5 @@
 """nslq_bitlinear_forward_rmsnorm / _swiglu: the RMSNorm or SiLU(gate)*up in front of a projection, formed
-inside the projection's launch for one or two tokens (the same call issues the two launches above that).
+inside the projection's launch for one token (the same call issues the two launches above that).
 
 Bars.  (1) Where the f64 sum of squares does not depend on the summation order (power-of-two magnitudes)
 the int32 accumulators and the fp32 outputs must equal the CPU checker's norm -> quantise -> matmul bit
@@ -66,7 +66,7 @@ def test_rmsnorm_prologue_on_gaussian_rows(M, xdt):
     _, _, _, y_ref = o.bitlinear_forward_packed(h, packed, N, ws)
     rms = np.sqrt((y_ref.astype(np.float64) ** 2).mean(axis=1, keepdims=True))
     assert np.all(np.abs(host(y) - y_ref) <= 2e-3 * rms)
-    if M > 2:                                             # above two tokens the call is the two launches
+    if M > 1:                                             # above one token the call is the two launches
         assert np.array_equal(host(acc), host(acc2))
 
 
@@ -106,3 +106,41 @@ def test_errors():
     _, odd, _ = _layer(rng, 64, 48)                        # K % 64 != 0: no fused form
     with pytest.raises(NslqError):
         odd.forward_rmsnorm(torch.zeros(1, 48, device="cuda"), torch.ones(48, device="cuda"))
+
+
+@pytest.mark.parametrize("M", [1, 2, 5])
+@pytest.mark.parametrize("normed", [True, False])
+@pytest.mark.parametrize("K,Ns", [(3200, (3200, 200, 72)), (2560, (6912, 6912)), (8640, (130,)), (256, (64, 64, 64, 50))])
+def test_sibling_projections_in_one_call_equal_the_separate_calls(M, normed, K, Ns):
+    """nslq_bitlinear_forward_multi: q/k/v (gate/up) of the same rows; every output has the bits of the
+    layer's own forward_rmsnorm / forward call, and in an exact-sum case those of the CPU checker."""
+    rng = np.random.default_rng(M * 31 + K + len(Ns))
+    layers = [_layer(rng, N, K, ws=0.02 + 0.01 * i) for i, N in enumerate(Ns)]
+    x = (np.exp2(rng.integers(-6, 7, size=(M, K))) * rng.choice([-1.0, 1.0], size=(M, K))).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, size=K).astype(np.float32)
+    xd, wd = dev(x), dev(w)
+    for out_dtype in (torch.float32, torch.bfloat16):
+        ys = ops.BitLinear.forward_multi([l[1] for l in layers], xd, wd if normed else None, 1e-5, out_dtype=out_dtype)
+        torch.cuda.synchronize()
+        for (packed, layer, ws), y, N in zip(layers, ys, Ns):
+            one = layer.forward_rmsnorm(xd, wd, 1e-5, out_dtype=out_dtype) if normed else layer.forward(xd, out_dtype=out_dtype)
+            torch.cuda.synchronize()
+            assert y.shape == (M, N)
+            assert torch.equal(y.view(torch.int16 if out_dtype == torch.bfloat16 else torch.int32),
+                               one.view(torch.int16 if out_dtype == torch.bfloat16 else torch.int32))
+            if out_dtype == torch.float32:
+                h = o.rmsnorm_f32(x, w, 1e-5) if normed else x
+                _, _, _, y_ref = o.bitlinear_forward_packed(h, packed, N, ws)
+                assert bits_equal(host(y), y_ref)
+    assert ops.device_status() == 0
+
+
+def test_sibling_projections_refuse_mismatched_layers():
+    rng = np.random.default_rng(3)
+    a = _layer(rng, 64, 256)[1]
+    b = _layer(rng, 64, 320)[1]
+    x = dev(rng.standard_normal((1, 256)).astype(np.float32))
+    with pytest.raises(ValueError):
+        ops.BitLinear.forward_multi([a, b], x)
+    with pytest.raises(ValueError):
+        ops.BitLinear.forward_multi([a] * 5, x)

@@ -107,4 +107,6 @@ def test_new_entry_points_refuse_bad_arguments_before_any_cuda_call():
     assert L.nslq_qtensor_dequantize(one, one, one, shape, 2, 0, 1, 3, 0, one, 1, null) == -1  # axis out of range
     assert L.nslq_bitlinear_forward_rmsnorm(null, one, 1, 1, one, 1e-5, one, 1, null, null, null, null, 0, null) == -1
     assert L.nslq_bitlinear_forward_swiglu(null, one, one, 3, 1, one, 1, null, null, null, null, 0, null) == -1
+    assert L.nslq_bitlinear_forward_multi(one, 5, one, 3, 1, null, 1e-5, one, 1, null, 0, null) == -1
+    assert L.nslq_bitlinear_forward_multi(null, 1, one, 3, 1, null, 1e-5, one, 1, null, 0, null) == -1
     assert b"null" in L.nslq_last_error()
