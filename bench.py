@@ -651,6 +651,39 @@ def make_workload(key, torch, ops, rank, world, streams=1, comm=None, gather="pe
     raise SystemExit("unknown workload %s" % key)
 
 
+def gpu_prior_art(torch, ours_prefill_ms, ours_decode_us):
+    """The design of the one GPU kernel NSL emits for BitLinear (one thread per output column, scalar loop over
+    packed bytes read straight from HBM, every CTA re-quantising its activation row), restated in
+    oracle/gpu_prior_art.cu and timed on this GPU on the two BitLinear configurations: a baseline leg beside the
+    CPU one, never part of the product.  Its results are checked bit for bit in tests/test_gpu_prior_art.py."""
+    from oracle import oracle as o
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1)
+
+    def timed_call(M, N, K, iters):
+        x = torch.randn(M, K, device="cuda", generator=g)
+        w = torch.randint(0, 256, (N, K // 4), device="cuda", dtype=torch.uint8, generator=g) & 0xA5   # codes 0..2 only
+        o.gpu_prior_art_bitlinear(x, w, 0.02)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            o.gpu_prior_art_bitlinear(x, w, 0.02)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    M = PrefillGemm.M
+    pre = sum(timed_call(M, n, k, 3) for n, k in PrefillGemm.SHAPES)
+    dec = timed_call(1, 8640, 3200, 20) * 1e3
+    return {"kernel": "oracle/gpu_prior_art.cu: structure of NSL's emitted BitLinear kernel (crates/nsl-codegen/src/bitnet/mod.rs:133-236), "
+                      "block_n 128, fp32 in and out, quantisation inside as in the reference",
+            "prefill_m2048_both_projections": {"ms": round(pre, 3), "TOPS": round(2 * PrefillGemm.OPS_PER_PROJ / 1e12 / (pre * 1e-3), 2),
+                                               "ours_ms": round(ours_prefill_ms, 5), "speedup_of_ours": round(pre / ours_prefill_ms, 1)},
+            "decode_m1_8640x3200": {"us": round(dec, 2), "ours_us": ours_decode_us,
+                                    "speedup_of_ours": round(dec / ours_decode_us, 1) if ours_decode_us else None}}
+
+
 def cpu_arm(key, threads, budget_s):
     if key == "prefill_gemm":
         return PrefillGemm.cpu_baseline(threads, budget_s)
@@ -948,6 +981,8 @@ def run_ours(args):
         line["decoder"] = [dict(run_decoder(torch, b, peaks), cpu_baseline=dec_cpu) for b in (64, 8, 1)]
         line["also"] = also                 # the decode GEMV of configs[0] comes last: the end of a long line is what survives a cut
         g1 = [a for a in also if a["workload"].startswith("bitlinear_decode_gemv_m1_n8640")]
+        chain = [a for a in g1 if a["streams"] == 1]
+        line["gpu_prior_art"] = gpu_prior_art(torch, m["ms_per_step"], chain[0]["roofline"]["kernel_us"] if chain else None)
         line["targets"] = {
             "decode_gemv_m1_8640x3200": {("independent_calls_%d_streams" % a["streams"]) if a["streams"] > 1 else "dependent_chain":
                                          {"us_per_call": a["roofline"]["kernel_us"], "GBps": a["roofline"]["achieved"],

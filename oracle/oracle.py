@@ -1,7 +1,7 @@
 """ctypes front end of the CPU checker (oracle/nslq_oracle.c) plus a numpy mirror.
 
 TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the
-benchmark's CPU-baseline leg.  The product package never imports this module.
+benchmark's baseline legs (the CPU port; the reference's GPU kernel design restated).  The product package never imports this module.
 
 The numpy mirror (`np_*`) restates the BitLinear arithmetic a second time, so
 the C restatement is not its own only witness; both are pinned to the NSL
@@ -15,7 +15,9 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "libnslq_oracle.so")
+_PRIOR_SO = os.path.join(_HERE, "libnslq_prior_art.so")
 _lib = None
+_prior = None
 
 i64, f32p, f64p = C.c_int64, C.POINTER(C.c_float), C.POINTER(C.c_double)
 i8p, u8p, i32p, i64p = (C.POINTER(C.c_int8), C.POINTER(C.c_uint8), C.POINTER(C.c_int32),
@@ -23,11 +25,37 @@ i8p, u8p, i32p, i64p = (C.POINTER(C.c_int8), C.POINTER(C.c_uint8), C.POINTER(C.c
 
 
 def build(force=False):
-    """Compile the C checker with the Makefile beside it (gcc only)."""
-    src = os.path.join(_HERE, "nslq_oracle.c")
-    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+    """Compile the C checker (gcc) and the GPU prior-art baseline kernel (nvcc) with the Makefile beside them."""
+    stale = False
+    for so, src in ((_SO, "nslq_oracle.c"), (_PRIOR_SO, "gpu_prior_art.cu")):
+        src = os.path.join(_HERE, src)
+        stale = stale or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src)
+    if force or stale:
         subprocess.check_call(["make", "-C", _HERE, "-s"])
     return _SO
+
+
+def gpu_prior_art_bitlinear(x, packed, weight_scale, return_acc=False, bias=None, residual=None):
+    """The reference's GPU kernel design restated (oracle/gpu_prior_art.cu) on torch CUDA tensors: x [rows, hidden]
+    f32, packed [out_dim, hidden/4] u8.  A baseline to time and to check, never part of the product."""
+    global _prior
+    import torch
+    if _prior is None:
+        if not os.path.exists(_PRIOR_SO):
+            build()
+        _prior = C.CDLL(_PRIOR_SO)
+        _prior.nslo_gpu_prior_art_bitlinear.argtypes = [C.c_void_p] * 4 + [C.c_int64] * 3 + [C.c_float] + [C.c_void_p] * 3
+    rows, hidden = x.shape
+    out_dim = packed.shape[0]
+    assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and packed.is_contiguous() and packed.dtype == torch.uint8
+    y = torch.empty(rows, out_dim, dtype=torch.float32, device=x.device)
+    acc = torch.empty(rows, out_dim, dtype=torch.int32, device=x.device) if return_acc else None
+    ptr = lambda t: None if t is None else t.data_ptr()  # noqa: E731
+    rc = _prior.nslo_gpu_prior_art_bitlinear(ptr(x), ptr(packed), ptr(y), ptr(acc), rows, hidden, out_dim, float(weight_scale),
+                                             ptr(bias), ptr(residual), torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise RuntimeError("nslo_gpu_prior_art_bitlinear returned %d" % rc)
+    return (y, acc) if return_acc else y
 
 
 def lib():
