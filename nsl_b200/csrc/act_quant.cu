@@ -27,7 +27,7 @@ static __device__ __forceinline__ float block_max(float v, float *smem)
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
     if (l == 0) smem[w] = v;
     __syncthreads();
-    float r = (l < AQ_THREADS / 32) ? smem[l] : 0.0f;
+    float r = (l < (int)(blockDim.x >> 5)) ? smem[l] : 0.0f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, o));
     return r;  // every thread holds the block maximum
@@ -41,7 +41,7 @@ static __device__ __forceinline__ int block_sum(int v, int *smem)
     __syncthreads();
     if (l == 0) smem[w] = v;
     __syncthreads();
-    int r = (l < AQ_THREADS / 32) ? smem[l] : 0;
+    int r = (l < (int)(blockDim.x >> 5)) ? smem[l] : 0;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
     return r;
@@ -93,20 +93,20 @@ static __device__ __forceinline__ int quant_group(const float (&f)[16], float in
 // elements, so both output orders are assembled in registers and stored 16 bytes at a time: no
 // shuffles, no lane masks.  (The kernel is bound by issued instructions, not by HBM, as long as it
 // spends more than about eight per element.)
-template <typename T, bool VEC, int XG>
-__global__ void __launch_bounds__(AQ_THREADS)
+template <typename T, bool VEC, int XG, int NT = AQ_THREADS>
+__global__ void __launch_bounds__(NT)
 act_quant_kernel(const T *__restrict__ x, int64_t K, int8_t *__restrict__ q_plain,
                  int8_t *__restrict__ q_perm, float *__restrict__ scale_out,
                  int32_t *__restrict__ rowsum_out)
 {
-    __shared__ float smax[AQ_THREADS / 32];
-    __shared__ int ssum[AQ_THREADS / 32];
+    __shared__ float smax[NT / 32];
+    __shared__ int ssum[NT / 32];
     const int64_t r = blockIdx.x;
     const T *row = x + r * K;
     pdl_wait();
 
     // VEC path: the thread's groups stay in registers between the absmax pass and the rounding pass
-    // (XG groups per thread: K <= XG*16*AQ_THREADS; longer rows re-read the tail, which is still in
+    // (XG groups per thread: K <= XG*16*NT; longer rows re-read the tail, which is still in
     // L1/L2).  XG is 1 or 3: short rows keep registers low so that more rows are in flight per SM.
     const int ngrp = VEC ? (int)(K >> 4) : 0;
     float xv[VEC ? XG : 1][16];
@@ -114,7 +114,7 @@ act_quant_kernel(const T *__restrict__ x, int64_t K, int8_t *__restrict__ q_plai
     if (VEC) {
 #pragma unroll
         for (int i = 0; i < XG; ++i) {
-            const int g = i * AQ_THREADS + threadIdx.x;
+            const int g = i * NT + threadIdx.x;
             if (g < ngrp) Group16<T>::load(row, g, xv[i]);
             else {
 #pragma unroll
@@ -123,13 +123,13 @@ act_quant_kernel(const T *__restrict__ x, int64_t K, int8_t *__restrict__ q_plai
         }
 #pragma unroll
         for (int i = 0; i < XG; ++i) m = absmax16(xv[i], m);
-        for (int g = XG * AQ_THREADS + threadIdx.x; g < ngrp; g += AQ_THREADS) {
+        for (int g = XG * NT + threadIdx.x; g < ngrp; g += NT) {
             float f[16];
             Group16<T>::load(row, g, f);
             m = absmax16(f, m);
         }
     } else {
-        for (int64_t k = threadIdx.x; k < K; k += AQ_THREADS) m = fmaxf(m, fabsf(Elem<T>::to_f32(row[k])));
+        for (int64_t k = threadIdx.x; k < K; k += NT) m = fmaxf(m, fabsf(Elem<T>::to_f32(row[k])));
     }
     const float scale = block_max(m, smax);
     pdl_launch_dependents();
@@ -142,23 +142,23 @@ act_quant_kernel(const T *__restrict__ x, int64_t K, int8_t *__restrict__ q_plai
         if (inv < INFINITY) {                              // CTA-uniform; false for inf and NaN
 #pragma unroll
             for (int i = 0; i < XG; ++i) {
-                const int g = i * AQ_THREADS + threadIdx.x;
+                const int g = i * NT + threadIdx.x;
                 if (g < ngrp) sum += quant_group<true>(xv[i], inv, pl, pp, g);
             }
-            for (int g = XG * AQ_THREADS + threadIdx.x; g < ngrp; g += AQ_THREADS) {
+            for (int g = XG * NT + threadIdx.x; g < ngrp; g += NT) {
                 float f[16];
                 Group16<T>::load(row, g, f);
                 sum += quant_group<true>(f, inv, pl, pp, g);
             }
         } else {
-            for (int g = threadIdx.x; g < ngrp; g += AQ_THREADS) {
+            for (int g = threadIdx.x; g < ngrp; g += NT) {
                 float f[16];
                 Group16<T>::load(row, g, f);
                 sum += quant_group<false>(f, inv, pl, pp, g);
             }
         }
     } else {
-        for (int64_t k = threadIdx.x; k < K; k += AQ_THREADS) {
+        for (int64_t k = threadIdx.x; k < K; k += NT) {
             int q = zero_row ? 0 : quant_one(Elem<T>::to_f32(row[k]), inv);
             sum += q;
             if (q_plain) q_plain[r * K + k] = (int8_t)q;
@@ -488,6 +488,12 @@ static int launch_act_quant(const void *x, int64_t M, int64_t K, int8_t *q_plain
     dim3 grid((unsigned)M), block(AQ_THREADS);
     cudaError_t e;
     if (!vec) e = launch_kernel(act_quant_kernel<T, false, 1>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
+    else if (M >= 1024 && K > 16 * 128 && K <= 2 * 16 * 128)
+        // many medium rows (a prefill): CTAs of 128 threads with two groups per thread keep more rows in flight per SM and
+        // halve the block reductions per byte
+        e = launch_kernel(act_quant_kernel<T, true, 2, 128>, grid, dim3(128), 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
+    else if (M >= 1024 && K > 2 * 16 * 192 && K <= 3 * 16 * 192)
+        e = launch_kernel(act_quant_kernel<T, true, 3, 192>, grid, dim3(192), 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
     else if (K <= 16 * AQ_THREADS) e = launch_kernel(act_quant_kernel<T, true, 1>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
     else e = launch_kernel(act_quant_kernel<T, true, 3>, grid, block, 0, st, (const T *)x, K, q_plain, q_perm, scale, rowsum);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "act_quant_kernel: %s", cudaGetErrorString(e));
