@@ -251,8 +251,13 @@ class PrefillGemm(Workload):
         self.kernel_launches = 2                               # per kernel_only() pass
         # 2 x (act quant + GEMM); sharded: + 2 flag barriers (peer) or 2 NCCL all-gathers, not counted as ours
         self.launches_per_step = 4 + (2 if self.mode in ("peer", "ce") else 0)
-        self.h2d = self.M * (self.H + self.F) * 4
-        self.d2h = self.M * (self.H + self.F) * es
+        # bytes over PCIe per step for the whole job (sharded with peer memory: every rank moves 1/G of them)
+        whole_job_once = world == 1 or (self.mode == "peer" and self.M % world == 0)
+        self.h2d = self.M * (self.H + self.F) * 4 * (1 if whole_job_once else world)
+        self.d2h = self.M * (self.H + self.F) * es * (1 if whole_job_once else world)
+        self.e2e_io = ("x from pinned host memory, y to pinned host memory" if world == 1 else
+                       "each rank uploads M/G rows of x (all-gathered over NVLink) and reads back M/G rows of the gathered y"
+                       if whole_job_once else "every rank uploads all of x and reads back all of the gathered y")
         self.l2_note = "inputs larger than L2 (26+71 MB of x, 14 MB of W, %d MB of y per step)" % (self.d2h // 1000000)
 
     def units_per_step(self):
@@ -367,19 +372,59 @@ class PrefillGemm(Workload):
         """Pinned host x -> device -> quantise + GEMM -> pinned host y, both projections.  Single GPU: the
         copies in and out run on their own streams, so the result of the first projection leaves while the
         input of the second arrives (PCIe is full duplex); every buffer is single and guarded by events, and
-        the step ends only when its last result is on the host.  Sharded: both inputs arrive, the sharded
-        step runs, both gathered results leave."""
+        the step ends only when its last result is on the host.  Sharded: the inputs arrive (a row block per
+        rank, all-gathered over NVLink), the sharded step runs, the gathered results leave (a row block per rank)."""
         torch = self.torch
         cur = torch.cuda.current_stream()
+        if self.world > 1 and self.mode == "peer" and self.M % self.world == 0:
+            # Every byte crosses PCIe once for the whole job: rank r uploads rows r*M/G.. of each x and the ranks
+            # all-gather the rows over NVLink (ncclAllGather called by the library); after a projection rank r reads
+            # rows r*M/G.. of its gathered result -- columns computed by every rank -- back to its host.  Copies in
+            # and out run on their own streams as on one GPU; a projection stands between two flag barriers, and a
+            # rank arrives at the first one only when its own read-back of that buffer's previous content is over.
+            rows = self.M // self.world
+            r0 = self.rank * rows
+            if not hasattr(self, "xsl"):
+                self.xsl = [torch.empty(rows, k, device="cuda") for _, k in self.SHAPES]
+                self.e2e_streams = (torch.cuda.Stream(), torch.cuda.Stream())
+                self.e2e_consumed = [None, None]             # row block i gathered, its staging buffer free again
+                self.e2e_out_done = [None, None]             # rows of result i copied to the host
+            s_in, s_out = self.e2e_streams
+            for i in range(2):
+                if self.e2e_consumed[i] is not None:
+                    s_in.wait_event(self.e2e_consumed[i])
+                with torch.cuda.stream(s_in):
+                    self.xsl[i].copy_(self.xh[i][r0:r0 + rows], non_blocking=True)
+                    arrived = torch.cuda.Event()
+                    arrived.record(s_in)
+                cur.wait_event(arrived)
+                self.comm.allgather_cols(self.xsl[i], gathered=self.xst[i].view(self.world, rows, -1))
+                gathered = torch.cuda.Event()
+                gathered.record(cur)
+                self.e2e_consumed[i] = gathered
+                if self.e2e_out_done[i] is not None:
+                    cur.wait_event(self.e2e_out_done[i])
+                self.comm.barrier()
+                self.one_call(i, self.xst[i])
+                self.comm.barrier()
+                computed = torch.cuda.Event()
+                computed.record(cur)
+                s_out.wait_event(computed)
+                out = self.ygs[i][r0:r0 + rows]
+                with torch.cuda.stream(s_out):
+                    self.y_host[:out.numel()].copy_(out.reshape(-1), non_blocking=True)   # the host buffer holds one result at a time
+                    left = torch.cuda.Event()
+                    left.record(s_out)
+                self.e2e_out_done[i] = left
+            cur.wait_event(self.e2e_out_done[1])              # the timed stream sees the last byte reach the host
+            return
         if self.world > 1:
             for i in range(2):
                 self.xst[i].copy_(self.xh[i], non_blocking=True)
             self.step(self.xst)
-            off = 0
             for i in range(2):
                 out = self.ygs[i]
-                self.y_host[off:off + out.numel()].copy_(out.view(-1), non_blocking=True)
-                off = 0                                          # the host buffer holds one result at a time
+                self.y_host[:out.numel()].copy_(out.view(-1), non_blocking=True)    # the host buffer holds one result at a time
             return
         if self.e2e_streams is None:
             self.e2e_streams = (torch.cuda.Stream(), torch.cuda.Stream())
@@ -945,7 +990,8 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seed 0)",
             "config": {"workload": wl.name, "cuda_graph": m["graph"], "dependent_launch": not args.no_pdl,
                        "streams": getattr(wl, "streams", 1), "l2": wl.l2_note,
-                       "x_dtype": "f32", "y_dtype": getattr(wl, "out_dtype", "f32"), "parallelism": par},
+                       "x_dtype": "f32", "y_dtype": getattr(wl, "out_dtype", "f32"), "parallelism": par,
+                       "e2e_io": getattr(wl, "e2e_io", None)},
             "e2e": {"value": round(m["e2e"], 3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
                     "d2h_bytes_per_step": wl.d2h},
             "gpu_launches": wl.launches_per_step * args.steps,
