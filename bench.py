@@ -22,9 +22,12 @@ configurations):
                 projection (and, per decode step, norms, attention and SwiGLU) through the C ABI; value in decode tok/s.
 One JSON line is printed by rank 0; at N=1 the default run appends the other workloads' figures
 under "also" and the decoder's under "decoder".  With --gpus N > 1 (launched by torchrun) the weights are column-sharded over the
-ranks, x is replicated and each output is all-gathered with NCCL: total work is fixed ("strong").
+ranks, x is replicated and each output is all-gathered (by peer stores from the GEMM epilogue, or with NCCL:
+--gather): total work is fixed ("strong").
 "e2e" is the same step fed from pinned host memory and read back to pinned host memory inside the
 timed region; the prefill step keeps the copies in and out on streams of their own (PCIe is full duplex).
+Sharded, every byte still crosses PCIe once for the whole job: each rank uploads its block of x's rows, the
+rows are all-gathered over NVLink, and each rank reads back its block of rows of the gathered result.
 
 --impl reference times the reference's CPU arithmetic for the same workload (the C restatement
 under oracle/, all host threads) on a bounded sample and prints the same line with
