@@ -798,8 +798,8 @@ def run_decoder(torch, batch, peaks, prompt=512, steps=256, warm=8, layers=None)
                         "frac": round(ach / peaks["hbm_gbs"], 4), "bytes_per_step": step_bytes,
                         "note": "ternary weights + bf16 lm_head + KV read at mid-run context; a decode step is library launches "
                                 "(embedding rows, RMSNorm and SiLU*up inside the projections' launches at one token per sequence batch of one, RoPE + KV "
-                                "append + attention, final norm, argmax) except the lm_head's bf16 GEMM (cuBLAS); the prefill "
-                                "glue is PyTorch"},
+                                "append + attention, final norm, argmax) except the lm_head's bf16 GEMM (cuBLAS); at prefill the attention "
+                                "over the prompt (SDPA) and the lm_head are PyTorch, RoPE + cache writes are one library launch"},
            "ceiling_tok_s": round(batch / (step_bytes / (peaks["hbm_gbs"] * 1e9)), 1)}
     del model
     torch.cuda.empty_cache()

@@ -152,6 +152,20 @@ int nslq_decode_attention(const void *q, const void *k_new, const void *v_new,
                           float sm_scale, void *out, void *stream);
 
 /*
+ * The rotary embedding of a prompt and its cache writes in one launch (RotaryEmbedding.forward,
+ * stdlib/nsl/nn/rope.nsl:41-68: x * cos + rotate_half(x) * sin with cos/sin = concat(freqs, freqs)): q [B*T, H*D]
+ * is rotated in place, k [B*T, Hkv*D] is rotated into k_cache[b, h, pos0 + t, :] and v copied into v_cache
+ * ([B, Hkv, max_ctx, D]); token row r belongs to sequence r / T at position pos0 + r % T.  All BF16; cos_t, sin_t
+ * [max_ctx, D/2] F32; q_ld, k_ld, v_ld: elements between token rows (so q, k, v may be column blocks of one fused
+ * projection).  Each product and each sum is rounded separately in fp32 and the result once to bf16 -- the bits of the
+ * same expression evaluated operation by operation on fp32 tensors.  nslq_decode_attention continues from pos0 + T.
+ */
+int nslq_rope_kv_prefill(void *q, const void *k, const void *v, int64_t q_ld, int64_t k_ld, int64_t v_ld,
+                         void *k_cache, void *v_cache, const float *cos_t, const float *sin_t,
+                         int64_t B, int64_t T, int64_t pos0, int64_t H, int64_t Hkv, int64_t D, int64_t max_ctx,
+                         void *stream);
+
+/*
  * The three remaining launches of a greedy decode step, each one runtime function of NSL as one launch on
  * device-resident data (one CTA per row; launch-latency work):
  *

@@ -42,6 +42,7 @@ SIGNATURES = {
     "nslq_int4_quantize_nk": (i32, [vp, i32, i64, i64, i64, vp, vp, vp, vp]),
     "nslq_embed_gather": (i32, [vp, i32, i64, i64, vp, i64, vp, vp]),
     "nslq_rmsnorm_rows": (i32, [vp, vp, C.c_double, i64, i64, vp, i32, vp]),
+    "nslq_rope_kv_prefill": (i32, [vp, vp, vp, i64, i64, i64, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, vp]),
     "nslq_argmax_rows": (i32, [vp, i32, i64, i64, i64, vp, vp, vp]),
     "nslq_bitnet_load_safetensors": (i32, [C.c_char_p, vp, C.POINTER(vp)]),
     "nslq_ternary_set_size": (i64, [vp]),

@@ -1,13 +1,16 @@
-// The three launches of a decode step that are neither a quantized linear nor attention: the embedding
-// rows of the current tokens, the RMSNorm in front of the output head, and the greedy choice of the next
-// token.  Each restates a runtime function of NSL as one launch, so that a decode step of the harness is
-// library launches from the first to the last (the head's bf16 GEMM aside):
+// The launches around the quantized linears and the attention of a decoder: for a decode step the embedding
+// rows of the current tokens, the RMSNorm in front of the output head and the greedy choice of the next
+// token, so that a step of the harness is library launches from the first to the last (the head's bf16 GEMM
+// aside); for the prompt the rotary embedding and the cache writes.  Each restates a runtime function of NSL
+// as one launch:
 //
 //   nslq_embed_gather   nsl_tensor_embedding_lookup  crates/nsl-runtime/src/tensor/mod.rs:2592-2680
 //   nslq_rmsnorm_rows   nsl_tensor_rmsnorm           crates/nsl-runtime/src/tensor/mod.rs:3016-3035
 //   nslq_argmax_rows    nsl_tensor_argmax            crates/nsl-runtime/src/sampling.rs:322-400
 //
-// All three are one CTA per row and bound by launch latency at decode sizes.
+//   nslq_rope_kv_prefill  RotaryEmbedding.forward + the cache writes of a prompt   stdlib/nsl/nn/rope.nsl:41-68
+//
+// The first three are one CTA per row and bound by launch latency at decode sizes; the last is one CTA per prompt token.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -110,6 +113,48 @@ __global__ void __launch_bounds__(AM_THREADS) argmax_rows_kernel(const T *__rest
     pdl_launch_dependents();
 }
 
+// Prefill: RoPE of the prompt's queries (in place) and keys, and the keys and values written into the cache, one
+// launch instead of the framework's slice / multiply / concatenate / copy kernels.  x * cos + rotate_half(x) * sin
+// with table = concat(freqs, freqs) (stdlib/nsl/nn/rope.nsl:41-68): for i < D/2
+//   out[i]       = x[i] * cos[t, i]       - x[i + D/2] * sin[t, i]
+//   out[i + D/2] = x[i + D/2] * cos[t, i] + x[i]       * sin[t, i]
+// each product and the sum rounded separately in fp32, then once to bf16 (the same bits as the expression
+// evaluated operation by operation on fp32 tensors).  One CTA per token; q, k, v are token rows [B*T, heads*D].
+__global__ void __launch_bounds__(256) rope_kv_prefill_kernel(__nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restrict__ k,
+                                                              const __nv_bfloat16 *__restrict__ v, int64_t q_ld, int64_t k_ld, int64_t v_ld,
+                                                              __nv_bfloat16 *__restrict__ k_cache, __nv_bfloat16 *__restrict__ v_cache,
+                                                              const float *__restrict__ cos_t, const float *__restrict__ sin_t,
+                                                              int T, int64_t pos0, int H, int Hkv, int D, int64_t max_ctx)
+{
+    pdl_wait();
+    const int64_t row = blockIdx.x;
+    const int64_t b = row / T, t = pos0 + row % T;
+    const int half = D >> 1;
+    const float *cr = cos_t + t * half, *sr = sin_t + t * half;
+    __nv_bfloat16 *qr = q + row * q_ld;
+    for (int i = threadIdx.x; i < H * half; i += 256) {
+        const int h = i / half, d = i % half;
+        const float x1 = __bfloat162float(qr[h * D + d]), x2 = __bfloat162float(qr[h * D + d + half]);
+        const float c = cr[d], sn = sr[d];
+        qr[h * D + d] = __float2bfloat16_rn(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)));
+        qr[h * D + d + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
+    }
+    const __nv_bfloat16 *kr = k + row * k_ld, *vr = v + row * v_ld;
+    for (int i = threadIdx.x; i < Hkv * half; i += 256) {
+        const int h = i / half, d = i % half;
+        const float x1 = __bfloat162float(kr[h * D + d]), x2 = __bfloat162float(kr[h * D + d + half]);
+        const float c = cr[d], sn = sr[d];
+        __nv_bfloat16 *dst = k_cache + ((b * Hkv + h) * max_ctx + t) * D;
+        dst[d] = __float2bfloat16_rn(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)));
+        dst[d + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
+    }
+    for (int i = threadIdx.x; i < Hkv * D; i += 256) {
+        const int h = i / D, d = i % D;
+        v_cache[((b * Hkv + h) * max_ctx + t) * D + d] = vr[i];
+    }
+    pdl_launch_dependents();
+}
+
 int decode_glue_status(int *out)
 {
     int v = 0;
@@ -154,6 +199,24 @@ int nslq_rmsnorm_rows(const float *x, const float *weight, double eps, int64_t M
     const cudaError_t e = launch_kernel(rmsnorm_rows_kernel, dim3((unsigned)M), dim3(256), 0, (cudaStream_t)stream, x, weight, eps, K, y, y_dtype);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "rmsnorm_rows_kernel: %s", cudaGetErrorString(e));
     return check_launch("rmsnorm_rows_kernel");
+}
+
+int nslq_rope_kv_prefill(void *q, const void *k, const void *v, int64_t q_ld, int64_t k_ld, int64_t v_ld, void *k_cache, void *v_cache,
+                         const float *cos_t, const float *sin_t, int64_t B, int64_t T, int64_t pos0, int64_t H, int64_t Hkv, int64_t D,
+                         int64_t max_ctx, void *stream)
+{
+    if (!q || !k || !v || !k_cache || !v_cache || !cos_t || !sin_t) return fail(NSLQ_ERR_ARG, "nslq_rope_kv_prefill: null argument");
+    if (B <= 0 || T <= 0 || H <= 0 || Hkv <= 0 || D <= 0 || D % 2 != 0 || pos0 < 0 || pos0 + T > max_ctx || B * T > 0x7fffffffLL ||
+        q_ld < H * D || k_ld < Hkv * D || v_ld < Hkv * D)
+        return fail(NSLQ_ERR_SHAPE, "nslq_rope_kv_prefill: B=%lld T=%lld pos0=%lld H=%lld Hkv=%lld D=%lld (even) max_ctx=%lld, row strides %lld %lld %lld",
+                    (long long)B, (long long)T, (long long)pos0, (long long)H, (long long)Hkv, (long long)D, (long long)max_ctx,
+                    (long long)q_ld, (long long)k_ld, (long long)v_ld);
+    const cudaError_t e = launch_kernel(rope_kv_prefill_kernel, dim3((unsigned)(B * T)), dim3(256), 0, (cudaStream_t)stream,
+                                        (__nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v, q_ld, k_ld, v_ld,
+                                        (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, cos_t, sin_t, (int)T, pos0, (int)H, (int)Hkv,
+                                        (int)D, max_ctx);
+    if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "rope_kv_prefill_kernel: %s", cudaGetErrorString(e));
+    return check_launch("rope_kv_prefill_kernel");
 }
 
 int nslq_argmax_rows(const void *x, int x_dtype, int64_t M, int64_t V, int64_t ld, int64_t *out, int64_t *counter, void *stream)

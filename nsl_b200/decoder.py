@@ -1,9 +1,9 @@
 """Decoder harness for the model-shaped workloads of the benchmark (BitNet b1.58-3B shape).
 
-At prefill, everything that is NOT a quantized linear -- embedding, RoPE, attention over the prompt, the
-bf16 lm_head -- is plain PyTorch, on purpose: those pieces are outside the quantized-linear path this
-library replaces (NSL has them in stdlib/nsl/nn/{norms,rope,gqa}.nsl and
-stdlib/nsl/inference/generate.nsl).  Every projection of every layer (q, k, v, o, gate, up, down) runs
+At prefill, the attention over the prompt and the bf16 lm_head are plain PyTorch (library kernels), on
+purpose: those pieces are outside the quantized-linear path this library replaces (NSL has them in
+stdlib/nsl/nn/gqa.nsl and stdlib/nsl/inference/generate.nsl); the embedding rows, the rotary embedding with
+the cache writes (nslq_rope_kv_prefill), the norms and the greedy choice are this library's launches.  Every projection of every layer (q, k, v, o, gate, up, down) runs
 through nsl_b200.ops.BitLinear, i.e. the C ABI.  A decode step is library launches throughout, the
 lm_head's bf16 GEMM aside: the embedding rows (nslq_embed_gather), the RMSNorms (inside the projections'
 launches for one token, nslq_rmsnorm_act_quant_i8 above), the attention of the new token (RoPE, cache
@@ -42,13 +42,8 @@ def _ternary(n, k, gen):
     return ((c[..., 0] << 6) | (c[..., 1] << 4) | (c[..., 2] << 2) | c[..., 3]).contiguous()
 
 
-def _rms_norm(x, w, eps):
-    """fp32 in, fp32 out (one kernel)."""
-    return F.rms_norm(x, (x.shape[-1],), w, eps)
-
-
 def _rope(x, cos, sin):
-    """x [B, H, T, D]; cos/sin [T, D/2] (rotate-half convention)."""
+    """x [B, H, T, D]; cos/sin [T, D/2] (rotate-half convention).  The expression nslq_rope_kv_prefill is tested against."""
     d = x.shape[-1] // 2
     x1, x2 = x[..., :d].float(), x[..., d:].float()
     return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1).to(x.dtype)
@@ -139,22 +134,19 @@ class BitNetDecoder:
     def prefill(self, ids):
         """ids [B, T]; fills the KV cache, leaves pos = T and tokens = greedy next token."""
         cfg, B, T = self.cfg, ids.shape[0], ids.shape[1]
-        x = self.embed[ids].float().reshape(B * T, cfg.hidden)            # residual stream, fp32
-        cos, sin = self.cos[:T], self.sin[:T]
+        x = ops.embed_gather(self.embed, ids.reshape(-1))                 # [B*T, h] residual stream, fp32
         for li, L in enumerate(self.layers):
             q, k, v = self._norm_lin_shared([L["q"], L["k"], L["v"]], x, L["n1"])
-            q = _rope(q.view(B, T, cfg.heads, cfg.head_dim).transpose(1, 2), cos, sin)
-            k = _rope(k.view(B, T, cfg.heads, cfg.head_dim).transpose(1, 2), cos, sin)
-            v = v.view(B, T, cfg.heads, cfg.head_dim).transpose(1, 2)
-            self.k_cache[li, :, :, :T] = k
-            self.v_cache[li, :, :, :T] = v
-            a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+            # rotary embedding and cache writes in one launch; the attention reads keys and values from the cache
+            ops.rope_kv_prefill(q, k, v, self.k_cache[li], self.v_cache[li], self.cos, self.sin, T)
+            a = F.scaled_dot_product_attention(q.view(B, T, cfg.heads, cfg.head_dim).transpose(1, 2),
+                                               self.k_cache[li, :, :, :T], self.v_cache[li, :, :, :T], is_causal=True)
             a = a.transpose(1, 2).reshape(B * T, cfg.heads * cfg.head_dim)
             x = self._lin(L["o"], a, x)
             g, u = self._norm_lin_shared([L["gate"], L["up"]], x, L["n2"])
             x = self._swiglu_down(L["down"], g, u, x)
-        last = _rms_norm(x.view(B, T, cfg.hidden)[:, -1], self.final_norm, cfg.eps).to(torch.bfloat16)
-        self.tokens.copy_((last @ self.lm_head.t()).argmax(-1))
+        last = ops.rmsnorm_rows(x.view(B, T, cfg.hidden)[:, -1].contiguous(), self.final_norm, cfg.eps, out_dtype=torch.bfloat16)
+        ops.argmax_rows(last @ self.lm_head.t(), out=self.tokens)
         self.pos.fill_(T)
         self.host_pos = T
 

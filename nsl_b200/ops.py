@@ -143,6 +143,25 @@ def rmsnorm_rows(x, weight, eps=1e-5, out_dtype=torch.float32, out=None):
     return out
 
 
+def rope_kv_prefill(q, k, v, k_cache, v_cache, cos_table, sin_table, T, pos0=0):
+    """Rotary embedding of a prompt in one launch (nslq_rope_kv_prefill): q [B*T, H*D] bf16 is rotated in place, k is
+    rotated into k_cache[:, :, pos0:pos0+T] and v copied into v_cache ([B, Hkv, max_ctx, D] bf16)."""
+    B, Hkv, max_ctx, D = k_cache.shape
+    for t in (q, k, v):
+        if t.dtype != torch.bfloat16 or not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.shape[0] != B * T:
+            raise ValueError("rope_kv_prefill: q, k, v must be CUDA bfloat16 [B*T, heads*D] with contiguous rows")
+    for t in (k_cache, v_cache):
+        if t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous() or t.shape != k_cache.shape:
+            raise ValueError("rope_kv_prefill: caches must be contiguous CUDA bfloat16 [B, Hkv, max_ctx, D]")
+    if k.shape[1] != Hkv * D or v.shape[1] != Hkv * D or q.shape[1] % D != 0:
+        raise ValueError("rope_kv_prefill: k, v rows must hold Hkv*D elements and q rows a multiple of D")
+    for t in (cos_table, sin_table):
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.shape[0] < max_ctx or t.shape[1] != D // 2:
+            raise ValueError("rope_kv_prefill: cos/sin must be contiguous fp32 [max_ctx, D/2]")
+    check(lib().nslq_rope_kv_prefill(_ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(k_cache), _ptr(v_cache),
+                                     _ptr(cos_table), _ptr(sin_table), B, T, pos0, q.shape[1] // D, Hkv, D, max_ctx, _stream()))
+
+
 def argmax_rows(x, out=None, counter=None):
     """Lowest index of each row's maximum as int64 (nslq_argmax_rows); `counter` (int64 tensor) is incremented."""
     if not x.is_cuda or x.dim() != 2 or x.stride(1) != 1:

@@ -75,3 +75,33 @@ def test_argmax_rows(dt):
     wide[:, 512:] = 100.0                              # outside the view
     wide[0, 100] = wide[1, 511] = wide[2, 0] = 1.0
     assert host(ops.argmax_rows(wide[:, :512])).tolist() == [100, 511, 0]
+
+
+@pytest.mark.parametrize("D", [100, 128, 6])
+@pytest.mark.parametrize("pos0", [0, 5])
+def test_rope_kv_prefill_equals_the_expression_on_fp32_tensors(D, pos0):
+    """nslq_rope_kv_prefill: rotated queries, rotated keys in the cache and copied values have the bits of
+    x * cos + rotate_half(x) * sin evaluated operation by operation on fp32 tensors and rounded to bf16 once;
+    rows of the cache outside [pos0, pos0 + T) stay untouched; q, k, v may be column blocks of one fused tensor."""
+    from nsl_b200.decoder import _rope
+    B, T, H, cap = 3, 37, 4, 64
+    g = torch.Generator(device="cuda")
+    g.manual_seed(D + pos0)
+    fused = torch.randn(B * T, 3 * H * D, device="cuda", generator=g).to(torch.bfloat16)
+    q, k, v = fused[:, :H * D], fused[:, H * D:2 * H * D], fused[:, 2 * H * D:]
+    inv = 1.0 / (10000.0 ** (torch.arange(D // 2, device="cuda").float() / (D // 2)))
+    ang = torch.arange(cap, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    kc = torch.full((B, H, cap, D), 7.0, device="cuda", dtype=torch.bfloat16)
+    vc = torch.full((B, H, cap, D), 7.0, device="cuda", dtype=torch.bfloat16)
+    want_q = _rope(q.reshape(B, T, H, D).transpose(1, 2), cos[pos0:pos0 + T], sin[pos0:pos0 + T])
+    want_k = _rope(k.reshape(B, T, H, D).transpose(1, 2), cos[pos0:pos0 + T], sin[pos0:pos0 + T])
+    want_v = v.reshape(B, T, H, D).transpose(1, 2).clone()
+    ops.rope_kv_prefill(q, k, v, kc, vc, cos, sin, T, pos0)
+    torch.cuda.synchronize()
+    assert torch.equal(q.reshape(B, T, H, D).transpose(1, 2), want_q)
+    assert torch.equal(kc[:, :, pos0:pos0 + T], want_k)
+    assert torch.equal(vc[:, :, pos0:pos0 + T], want_v)
+    assert bool((kc[:, :, :pos0] == 7).all()) and bool((kc[:, :, pos0 + T:] == 7).all())
+    assert bool((vc[:, :, :pos0] == 7).all()) and bool((vc[:, :, pos0 + T:] == 7).all())
+    assert ops.device_status() == 0

@@ -99,6 +99,9 @@ def test_new_entry_points_refuse_bad_arguments_before_any_cuda_call():
     assert L.nslq_rmsnorm_rows(one, one, 1e-5, 1, 0, one, 1, null) == -2
     assert L.nslq_rmsnorm_rows(one, one, 1e-5, 1, 8, one, 0, null) == -1        # F64 output is not offered
     assert L.nslq_argmax_rows(null, 3, 1, 8, 8, one, null, null) == -1
+    assert L.nslq_rope_kv_prefill(null, one, one, 8, 8, 8, one, one, one, one, 1, 1, 0, 1, 1, 8, 4, null) == -1
+    assert L.nslq_rope_kv_prefill(one, one, one, 8, 8, 8, one, one, one, one, 1, 4, 1, 1, 1, 8, 4, null) == -2   # pos0 + T past the cache
+    assert L.nslq_rope_kv_prefill(one, one, one, 8, 8, 8, one, one, one, one, 1, 1, 0, 1, 1, 7, 4, null) == -2   # odd head dimension
     assert L.nslq_argmax_rows(one, 3, 1, 8, 4, one, null, null) == -2           # row stride shorter than the row
     shape = (C.c_int64 * 2)(4, 4)
     assert L.nslq_qtensor_quantize(null, 1, shape, 2, 0, 0, 0, 0, one, one, one, null) == -1
