@@ -120,6 +120,16 @@ __global__ void __launch_bounds__(AM_THREADS) argmax_rows_kernel(const T *__rest
 //   out[i + D/2] = x[i + D/2] * cos[t, i] + x[i]       * sin[t, i]
 // each product and the sum rounded separately in fp32, then once to bf16 (the same bits as the expression
 // evaluated operation by operation on fp32 tensors).  One CTA per token; q, k, v are token rows [B*T, heads*D].
+// One rotated pair (d, d + D/2) from the inputs x1 = x[d], x2 = x[d + D/2].
+static __device__ __forceinline__ void rope_pair(float x1, float x2, float c, float sn, float &lo, float &hi)
+{
+    lo = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn));
+    hi = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn));
+}
+
+// VEC: D/2 and the row strides are even and every base pointer 4-byte aligned, so a thread takes two neighbouring
+// dimensions with 4-byte accesses (8-byte for the tables).
+template <bool VEC>
 __global__ void __launch_bounds__(256) rope_kv_prefill_kernel(__nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restrict__ k,
                                                               const __nv_bfloat16 *__restrict__ v, int64_t q_ld, int64_t k_ld, int64_t v_ld,
                                                               __nv_bfloat16 *__restrict__ k_cache, __nv_bfloat16 *__restrict__ v_cache,
@@ -132,25 +142,43 @@ __global__ void __launch_bounds__(256) rope_kv_prefill_kernel(__nv_bfloat16 *__r
     const int half = D >> 1;
     const float *cr = cos_t + t * half, *sr = sin_t + t * half;
     __nv_bfloat16 *qr = q + row * q_ld;
-    for (int i = threadIdx.x; i < H * half; i += 256) {
-        const int h = i / half, d = i % half;
-        const float x1 = __bfloat162float(qr[h * D + d]), x2 = __bfloat162float(qr[h * D + d + half]);
-        const float c = cr[d], sn = sr[d];
-        qr[h * D + d] = __float2bfloat16_rn(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)));
-        qr[h * D + d + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
-    }
     const __nv_bfloat16 *kr = k + row * k_ld, *vr = v + row * v_ld;
-    for (int i = threadIdx.x; i < Hkv * half; i += 256) {
-        const int h = i / half, d = i % half;
-        const float x1 = __bfloat162float(kr[h * D + d]), x2 = __bfloat162float(kr[h * D + d + half]);
-        const float c = cr[d], sn = sr[d];
-        __nv_bfloat16 *dst = k_cache + ((b * Hkv + h) * max_ctx + t) * D;
-        dst[d] = __float2bfloat16_rn(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)));
-        dst[d + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
-    }
-    for (int i = threadIdx.x; i < Hkv * D; i += 256) {
-        const int h = i / D, d = i % D;
-        v_cache[((b * Hkv + h) * max_ctx + t) * D + d] = vr[i];
+    if (VEC) {
+        const int hp = half >> 1;                             // pairs of neighbouring dimensions per half
+        for (int i = threadIdx.x; i < (H + Hkv) * hp; i += 256) {
+            const int h = i / hp, d = 2 * (i % hp);
+            const bool isq = h < H;
+            const __nv_bfloat16 *src = isq ? qr + h * D : kr + (h - H) * D;
+            __nv_bfloat16 *dst = isq ? qr + h * D : k_cache + ((b * Hkv + (h - H)) * max_ctx + t) * D;
+            const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(src + d));
+            const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(src + d + half));
+            const float2 c = *reinterpret_cast<const float2 *>(cr + d), sn = *reinterpret_cast<const float2 *>(sr + d);
+            float2 lo, hi;
+            rope_pair(x1.x, x2.x, c.x, sn.x, lo.x, hi.x);
+            rope_pair(x1.y, x2.y, c.y, sn.y, lo.y, hi.y);
+            *reinterpret_cast<__nv_bfloat162 *>(dst + d) = __floats2bfloat162_rn(lo.x, lo.y);
+            *reinterpret_cast<__nv_bfloat162 *>(dst + d + half) = __floats2bfloat162_rn(hi.x, hi.y);
+        }
+        for (int i = threadIdx.x; i < Hkv * half; i += 256) {  // values: 4-byte copies (D is a multiple of 4 here)
+            const int h = i / half, d = 2 * (i % half);
+            *reinterpret_cast<uint32_t *>(v_cache + ((b * Hkv + h) * max_ctx + t) * D + d) =
+                *reinterpret_cast<const uint32_t *>(vr + h * D + d);
+        }
+    } else {
+        for (int i = threadIdx.x; i < (H + Hkv) * half; i += 256) {
+            const int h = i / half, d = i % half;
+            const bool isq = h < H;
+            const __nv_bfloat16 *src = isq ? qr + h * D : kr + (h - H) * D;
+            __nv_bfloat16 *dst = isq ? qr + h * D : k_cache + ((b * Hkv + (h - H)) * max_ctx + t) * D;
+            float lo, hi;
+            rope_pair(__bfloat162float(src[d]), __bfloat162float(src[d + half]), cr[d], sr[d], lo, hi);
+            dst[d] = __float2bfloat16_rn(lo);
+            dst[d + half] = __float2bfloat16_rn(hi);
+        }
+        for (int i = threadIdx.x; i < Hkv * D; i += 256) {
+            const int h = i / D, d = i % D;
+            v_cache[((b * Hkv + h) * max_ctx + t) * D + d] = vr[i];
+        }
     }
     pdl_launch_dependents();
 }
@@ -211,10 +239,13 @@ int nslq_rope_kv_prefill(void *q, const void *k, const void *v, int64_t q_ld, in
         return fail(NSLQ_ERR_SHAPE, "nslq_rope_kv_prefill: B=%lld T=%lld pos0=%lld H=%lld Hkv=%lld D=%lld (even) max_ctx=%lld, row strides %lld %lld %lld",
                     (long long)B, (long long)T, (long long)pos0, (long long)H, (long long)Hkv, (long long)D, (long long)max_ctx,
                     (long long)q_ld, (long long)k_ld, (long long)v_ld);
-    const cudaError_t e = launch_kernel(rope_kv_prefill_kernel, dim3((unsigned)(B * T)), dim3(256), 0, (cudaStream_t)stream,
-                                        (__nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v, q_ld, k_ld, v_ld,
-                                        (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, cos_t, sin_t, (int)T, pos0, (int)H, (int)Hkv,
-                                        (int)D, max_ctx);
+    auto al = [](const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
+    const bool vec = D % 4 == 0 && q_ld % 2 == 0 && k_ld % 2 == 0 && v_ld % 2 == 0 && al(q, 4) && al(k, 4) && al(v, 4) && al(k_cache, 4) &&
+                     al(v_cache, 4) && al(cos_t, 8) && al(sin_t, 8);
+    const cudaError_t e = launch_kernel(vec ? rope_kv_prefill_kernel<true> : rope_kv_prefill_kernel<false>, dim3((unsigned)(B * T)), dim3(256),
+                                        0, (cudaStream_t)stream, (__nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v, q_ld,
+                                        k_ld, v_ld, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, cos_t, sin_t, (int)T, pos0, (int)H,
+                                        (int)Hkv, (int)D, max_ctx);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "rope_kv_prefill_kernel: %s", cudaGetErrorString(e));
     return check_launch("rope_kv_prefill_kernel");
 }
