@@ -182,7 +182,7 @@ class Workload:
             ach, unit = per_launch / (kernel_ms * 1e-3) / 1e12, self.unit
             peak = peaks["bf16_tflops"] * (2.0 if self.int8 else 1.0)
             src = ("2 x " if self.int8 else "") + peaks["source"] + " bf16 burst" + \
-                  (" (no measured int8 figure is available; datasheet int8 dense = 4500)" if self.int8 else "")
+                  (" (the line's library_int8_gemm gives a measured int8 figure; datasheet int8 dense = 4500)" if self.int8 else "")
         out = {"bound": self.bound, "kernel": self.kernel_name, "achieved": round(ach, 1), "peak": round(peak, 1),
                "unit": unit, "frac": round(ach / peak, 4),
                "traffic": NCU_TRAFFIC.get(self.kernel_name) if self.world == 1 else None,
@@ -699,6 +699,43 @@ def make_workload(key, torch, ops, rank, world, streams=1, comm=None, gather="pe
     raise SystemExit("unknown workload %s" % key)
 
 
+def library_int8_yardstick(torch, ours_kernel_us):
+    """A measured int8 yardstick for the tensor roofline: the BLAS library's dense int8 x int8 -> int32 GEMM
+    (torch._int_mm, cuBLASLt) timed here on the two projection shapes of the prefill workload -- plain int8 operands,
+    nothing to unpack, int32 results left as they are -- and on a large cube for its peak rate.  Never on the
+    product path."""
+    if not hasattr(torch, "_int_mm"):
+        return None
+    g = torch.Generator(device="cuda")
+    g.manual_seed(2)
+
+    def timed_call(M, N, K, reps):
+        a = torch.randint(-127, 128, (M, K), device="cuda", dtype=torch.int8, generator=g)
+        b = torch.randint(-1, 2, (N, K), device="cuda", dtype=torch.int8, generator=g).t()
+        for _ in range(3):
+            torch._int_mm(a, b)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            torch._int_mm(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    try:
+        same = [timed_call(PrefillGemm.M, n, k, 20) for n, k in PrefillGemm.SHAPES]
+        cube = timed_call(8192, 8192, 8192, 5)
+    except RuntimeError as e:                 # a build of the framework without this routine for the device
+        return {"unavailable": str(e)[:120]}
+    mean = sum(same) / len(same)
+    return {"routine": "torch._int_mm (cuBLASLt int8 x int8 -> int32), dense int8 weights, no epilogue",
+            "same_shapes_us": [round(v, 2) for v in same], "same_shapes_mean_us": round(mean, 2),
+            "same_shapes_TOPS": round(PrefillGemm.OPS_PER_PROJ / 1e12 / (mean * 1e-6), 1),
+            "ours_kernel_us": ours_kernel_us, "ours_over_library": round(mean / ours_kernel_us, 3) if ours_kernel_us else None,
+            "peak_TOPS_8192_cube": round(2.0 * 8192 ** 3 / 1e12 / (cube * 1e-6), 1)}
+
+
 def gpu_prior_art(torch, ours_prefill_ms, ours_decode_us):
     """The design of the one GPU kernel NSL emits for BitLinear (one thread per output column, scalar loop over
     packed bytes read straight from HBM, every CTA re-quantising its activation row), restated in
@@ -1032,6 +1069,7 @@ def run_ours(args):
         g1 = [a for a in also if a["workload"].startswith("bitlinear_decode_gemv_m1_n8640")]
         chain = [a for a in g1 if a["streams"] == 1]
         line["gpu_prior_art"] = gpu_prior_art(torch, m["ms_per_step"], chain[0]["roofline"]["kernel_us"] if chain else None)
+        line["library_int8_gemm"] = library_int8_yardstick(torch, roof.get("kernel_us"))
         line["targets"] = {
             "decode_gemv_m1_8640x3200": {("independent_calls_%d_streams" % a["streams"]) if a["streams"] > 1 else "dependent_chain":
                                          {"us_per_call": a["roofline"]["kernel_us"], "GBps": a["roofline"]["achieved"],
