@@ -279,8 +279,9 @@ int nslq_bitlinear_forward_swiglu(const nslq_bitlinear_t *w, const void *gate, c
  * nslq_bitlinear_forward_rmsnorm(layers[i], x, ..., ys[i], ...) (norm_weight != NULL) or of
  * nslq_bitlinear_forward(layers[i], x, ..., ys[i], ...) (norm_weight == NULL) without bias or residual.  For one
  * token all layers share ONE launch (each CTA quantises the rows for itself and multiplies a slab of one
- * layer's weights); above that the rows are normalised and quantised once and each layer is one launch, which
- * needs the workspace of nslq_bitlinear_forward (pass it always).  1 <= n_layers <= 4; all layers the same K, K % 64 == 0.
+ * layer's weights); above that the rows are normalised and quantised once (which needs the workspace of
+ * nslq_bitlinear_forward: pass it always) and the layers share one launch of the streaming kernel where that kernel
+ * would take each of them (up to 16 rows of small matrices), else each layer is one launch.  1 <= n_layers <= 4; all layers the same K, K % 64 == 0.
  */
 int nslq_bitlinear_forward_multi(const nslq_bitlinear_t *const *layers, int n_layers, const void *x, int x_dtype, int64_t M,
                                  const float *norm_weight, double eps, void *const *ys, int y_dtype,

@@ -46,6 +46,8 @@ bool ternary_gemv_fused_supported(const void *, const void *, int64_t, int64_t);
 bool ternary_gemv_src_supported(const void *, const void *, const void *, const float *, int64_t, int64_t);
 int ternary_gemv_src_dispatch(const uint8_t *, const void *, const void *, const float *, double, int, int, int64_t, int64_t, float, void *,
                               int, int32_t *, const float *, const float *, cudaStream_t);
+int ternary_gemv_multi_dispatch_q(int, const uint8_t *const *, const int64_t *, const float *, void *const *, const int8_t *, const float *,
+                                  const int32_t *, int, int64_t, int, cudaStream_t);
 int ternary_gemv_multi_dispatch(int, const uint8_t *const *, const int64_t *, const float *, const float *const *, void *const *, const void *,
                                 const float *, double, int, int, int64_t, int, cudaStream_t);
 int ternary_gemv_fused_dispatch(const uint8_t *, const void *, int, int, int64_t, int64_t, float, void *, int, int32_t *,
@@ -495,6 +497,17 @@ int nslq_bitlinear_forward_multi(const nslq_bitlinear_t *const *layers, int n_la
     int rc = norm_weight ? rmsnorm_act_quant_dispatch(x, x_dtype, norm_weight, eps, M, K, nullptr, nullptr, q, scale, rowsum, st)
                          : act_quant_dispatch(x, x_dtype, M, K, nullptr, q, scale, rowsum, st);
     if (rc) return rc;
+    // a few rows of small matrices: the streaming kernel takes all layers as one launch
+    bool one_gemv = M <= 16 && n_layers > 1;
+    for (int i = 0; one_gemv && i < n_layers; ++i)
+        one_gemv = !decode_pays(M, layers[i]->N, K) && ternary_gemv_supported(layers[i]->packed, q, K);
+    if (one_gemv) {
+        const uint8_t *ws[4];
+        int64_t Ns[4];
+        float scales[4];
+        for (int i = 0; i < n_layers; ++i) { ws[i] = layers[i]->packed; Ns[i] = layers[i]->N; scales[i] = layers[i]->weight_scale; }
+        return ternary_gemv_multi_dispatch_q(n_layers, ws, Ns, scales, ys, q, scale, rowsum, (int)M, K, y_dtype, st);
+    }
     for (int i = 0; i < n_layers; ++i)
         if ((rc = nslq_bitlinear_forward_quantized(layers[i], q, scale, rowsum, M, ys[i], y_dtype, nullptr, nullptr, nullptr, stream))) return rc;
     return NSLQ_OK;

@@ -34,6 +34,7 @@
 
 namespace nslq {
 
+constexpr int GEMV_MAX_LAYERS = 4;
 struct GemvParams {
     const uint8_t *w;      // [N][K/4]
     const int8_t *q;       // [M][K] permuted order
@@ -46,6 +47,16 @@ struct GemvParams {
     int64_t N, K;
     int M, y_dtype;
     float weight_scale;
+    // Sibling projections of the same quantised rows (q/k/v, gate/up) in the same launch: CTAs from
+    // sib[i].first_cta on multiply sibling i's weights.  acc_out, bias and residual are null then.
+    int nsib;
+    struct Sibling {
+        const uint8_t *w;
+        void *y;
+        int64_t N;
+        float weight_scale;
+        unsigned first_cta;
+    } sib[GEMV_MAX_LAYERS - 1];
 };
 
 // KW warps per CTA split K; NT = token tiles of 8; UNROLL = steps whose weight
@@ -57,13 +68,25 @@ ternary_gemv_kernel(const GemvParams p)
     __shared__ int red[KW][NT][32][4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int64_t n0 = (int64_t)blockIdx.x * 16;
+    // this CTA's projection: the first one, or the last sibling whose range the CTA index has reached
+    const uint8_t *lw = p.w;
+    void *ly = p.y;
+    int64_t lN = p.N;
+    float lws = p.weight_scale;
+    unsigned cta0 = 0;
+#pragma unroll
+    for (int i = 0; i < GEMV_MAX_LAYERS - 1; ++i) {
+        if (i < p.nsib && blockIdx.x >= p.sib[i].first_cta) {
+            lw = p.sib[i].w; ly = p.sib[i].y; lN = p.sib[i].N; lws = p.sib[i].weight_scale; cta0 = p.sib[i].first_cta;
+        }
+    }
+    const int64_t n0 = (int64_t)(blockIdx.x - cta0) * 16;
     const int64_t row_bytes = p.K >> 2;
     const int nchunks = (int)(p.K >> 6);            // 64 trits = 16 bytes per chunk
     const int nsteps = (nchunks + 3) >> 2;
-    const bool rowa_ok = (n0 + g) < p.N, rowb_ok = (n0 + g + 8) < p.N;
-    const uint8_t *wa = p.w + (n0 + g) * row_bytes;
-    const uint8_t *wb = p.w + (n0 + g + 8) * row_bytes;
+    const bool rowa_ok = (n0 + g) < lN, rowb_ok = (n0 + g + 8) < lN;
+    const uint8_t *wa = lw + (n0 + g) * row_bytes;
+    const uint8_t *wb = lw + (n0 + g + 8) * row_bytes;
 
     Acc4 acc[NT];
 #pragma unroll
@@ -110,7 +133,7 @@ ternary_gemv_kernel(const GemvParams p)
     // One output per thread-iteration; consecutive threads take consecutive rows.
     for (int e = threadIdx.x; e < 16 * 8 * NT; e += KW * 32) {
         const int row = e & 15, tok = e >> 4;
-        if (tok >= p.M || n0 + row >= p.N) continue;
+        if (tok >= p.M || n0 + row >= lN) continue;
         const int nt = tok >> 3, tl = tok & 7;
         const int src_lane = (row & 7) * 4 + (tl >> 1);
         const int src_reg = ((row >> 3) << 1) | (tl & 1);
@@ -118,12 +141,12 @@ ternary_gemv_kernel(const GemvParams p)
 #pragma unroll
         for (int w = 0; w < KW; ++w) a += red[w][nt][src_lane][src_reg];
         a -= p.rowsum[tok];
-        const int64_t o = (int64_t)tok * p.N + n0 + row;
+        const int64_t o = (int64_t)tok * lN + n0 + row;
         if (p.acc_out) p.acc_out[o] = a;
-        float v = bitlinear_finalize(a, p.scale[tok], p.weight_scale);
+        float v = bitlinear_finalize(a, p.scale[tok], lws);
         if (p.bias) v = __fadd_rn(v, p.bias[n0 + row]);
         if (p.residual) v = __fadd_rn(v, p.residual[o]);
-        store_out(p.y, p.y_dtype, o, v);
+        store_out(ly, p.y_dtype, o, v);
     }
 }
 
@@ -726,8 +749,13 @@ ternary_scalar_kernel(const uint8_t *__restrict__ w, const int8_t *__restrict__ 
 template <int KW, int NT>
 static int launch_gemv(const GemvParams &p, cudaStream_t st)
 {
-    const unsigned tiles = (unsigned)((p.N + 15) / 16);
-    cudaError_t e = launch_kernel(ternary_gemv_kernel<KW, NT, 4>, dim3(tiles), dim3(KW * 32), 0, st, p);
+    GemvParams q = p;
+    unsigned tiles = (unsigned)((p.N + 15) / 16);
+    for (int i = 0; i < q.nsib; ++i) {
+        q.sib[i].first_cta = tiles;
+        tiles += (unsigned)((q.sib[i].N + 15) / 16);
+    }
+    cudaError_t e = launch_kernel(ternary_gemv_kernel<KW, NT, 4>, dim3(tiles), dim3(KW * 32), 0, st, q);
     if (e != cudaSuccess) return fail(NSLQ_ERR_CUDA, "ternary_gemv_kernel: %s", cudaGetErrorString(e));
     return check_launch("ternary_gemv_kernel");
 }
@@ -744,9 +772,23 @@ int ternary_gemv_dispatch(const uint8_t *w, const int8_t *q_perm, const float *s
                           void *y, int y_dtype, int32_t *acc_out, const float *bias,
                           const float *residual, cudaStream_t st)
 {
-    GemvParams p{w, q_perm, scale, rowsum, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale};
+    GemvParams p{w, q_perm, scale, rowsum, y, acc_out, bias, residual, N, K, M, y_dtype, weight_scale, 0, {}};
     const int nsteps = (int)((K / 64 + 3) / 4);
     const bool wide = nsteps > 16;   // long rows: 8 warps split K
+    if (M <= 8) return wide ? launch_gemv<8, 1>(p, st) : launch_gemv<4, 1>(p, st);
+    return wide ? launch_gemv<8, 2>(p, st) : launch_gemv<4, 2>(p, st);
+}
+
+// Up to four projections of the same quantised rows in one launch (q/k/v, gate/up): ws[i] [Ns[i]][K/4], ys[i] [M][Ns[i]].
+int ternary_gemv_multi_dispatch_q(int nl, const uint8_t *const *ws, const int64_t *Ns, const float *weight_scales, void *const *ys,
+                                  const int8_t *q_perm, const float *scale, const int32_t *rowsum, int M, int64_t K, int y_dtype,
+                                  cudaStream_t st)
+{
+    if (nl < 1 || nl > GEMV_MAX_LAYERS) return fail(NSLQ_ERR_ARG, "BitLinear: %d projections in one launch, at most %d", nl, GEMV_MAX_LAYERS);
+    GemvParams p{ws[0], q_perm, scale, rowsum, ys[0], nullptr, nullptr, nullptr, Ns[0], K, M, y_dtype, weight_scales[0], nl - 1, {}};
+    for (int i = 1; i < nl; ++i) p.sib[i - 1] = GemvParams::Sibling{ws[i], ys[i], Ns[i], weight_scales[i], 0u};
+    const int nsteps = (int)((K / 64 + 3) / 4);
+    const bool wide = nsteps > 16;
     if (M <= 8) return wide ? launch_gemv<8, 1>(p, st) : launch_gemv<4, 1>(p, st);
     return wide ? launch_gemv<8, 2>(p, st) : launch_gemv<4, 2>(p, st);
 }

@@ -125,7 +125,7 @@ class BitNetDecoder:
         normalise and quantise for themselves (nslq_bitlinear_forward_multi), so neither the norm nor the
         siblings' side streams exist."""
         M = x2d.shape[0]
-        if M == 1:
+        if M <= 8:                        # one row: one launch in all; up to eight: the quantiser and ONE launch for all projections
             return ops.BitLinear.forward_multi(layers, x2d, norm_w, self.cfg.eps, out_dtype=torch.bfloat16)
         qa = ops.rmsnorm_act_quant_i8(x2d, norm_w, self.cfg.eps, plain=False, perm=True)
         return self._siblings([lambda l=l: l.forward_quantized(qa, out_dtype=torch.bfloat16) for l in layers])
