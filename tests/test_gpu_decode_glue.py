@@ -8,7 +8,7 @@ pytestmark = pytest.mark.gpu
 
 torch = pytest.importorskip("torch")
 from gpu_util import bf16_round, dev, host  # noqa: E402
-from nsl_b200 import ops  # noqa: E402
+from nsl_b200 import NslqError, ops  # noqa: E402
 from oracle import oracle as o  # noqa: E402
 
 
@@ -105,3 +105,29 @@ def test_rope_kv_prefill_equals_the_expression_on_fp32_tensors(D, pos0):
     assert bool((kc[:, :, :pos0] == 7).all()) and bool((kc[:, :, pos0 + T:] == 7).all())
     assert bool((vc[:, :, :pos0] == 7).all()) and bool((vc[:, :, pos0 + T:] == 7).all())
     assert ops.device_status() == 0
+
+
+def test_rope_kv_prefill_with_grouped_heads_and_a_single_token():
+    """Fewer key/value heads than query heads, one token per sequence appended at a later position."""
+    from nsl_b200.decoder import _rope
+    B, T, H, Hkv, D, cap, pos0 = 2, 1, 8, 2, 64, 16, 9
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    q = torch.randn(B * T, H * D, device="cuda", generator=g).to(torch.bfloat16)
+    k = torch.randn(B * T, Hkv * D, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(B * T, Hkv * D, device="cuda", generator=g).to(torch.bfloat16)
+    inv = 1.0 / (10000.0 ** (torch.arange(D // 2, device="cuda").float() / (D // 2)))
+    ang = torch.arange(cap, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    kc = torch.zeros(B, Hkv, cap, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    want_q = _rope(q.reshape(B, T, H, D).transpose(1, 2), cos[pos0:pos0 + T], sin[pos0:pos0 + T])
+    want_k = _rope(k.reshape(B, T, Hkv, D).transpose(1, 2), cos[pos0:pos0 + T], sin[pos0:pos0 + T])
+    ops.rope_kv_prefill(q, k, v, kc, vc, cos, sin, T, pos0)
+    torch.cuda.synchronize()
+    assert torch.equal(q.reshape(B, T, H, D).transpose(1, 2), want_q)
+    assert torch.equal(kc[:, :, pos0:pos0 + T], want_k)
+    assert torch.equal(vc[:, :, pos0:pos0 + T], v.reshape(B, T, Hkv, D).transpose(1, 2))
+    assert int((kc != 0).any(-1).sum()) <= B * Hkv * T and int((vc != 0).any(-1).sum()) <= B * Hkv * T
+    with pytest.raises(NslqError):
+        ops.rope_kv_prefill(q, k, v, kc, vc, cos, sin, T, cap)                      # past the end of the cache

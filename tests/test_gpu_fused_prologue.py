@@ -108,9 +108,10 @@ def test_errors():
         odd.forward_rmsnorm(torch.zeros(1, 48, device="cuda"), torch.ones(48, device="cuda"))
 
 
-@pytest.mark.parametrize("M", [1, 2, 5])
+@pytest.mark.parametrize("M", [1, 2, 5, 8, 16, 40])
 @pytest.mark.parametrize("normed", [True, False])
-@pytest.mark.parametrize("K,Ns", [(3200, (3200, 200, 72)), (2560, (6912, 6912)), (8640, (130,)), (256, (64, 64, 64, 50))])
+@pytest.mark.parametrize("K,Ns", [(3200, (3200, 200, 72)), (2560, (6912, 6912)), (8640, (130,)), (8640, (3200, 40)),
+                                  (256, (64, 64, 64, 50))])
 def test_sibling_projections_in_one_call_equal_the_separate_calls(M, normed, K, Ns):
     """nslq_bitlinear_forward_multi: q/k/v (gate/up) of the same rows; every output has the bits of the
     layer's own forward_rmsnorm / forward call, and in an exact-sum case those of the CPU checker."""
