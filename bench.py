@@ -1074,6 +1074,9 @@ def run_ours(args):
             "decode_gemv_m1_8640x3200": {("independent_calls_%d_streams" % a["streams"]) if a["streams"] > 1 else "dependent_chain":
                                          {"us_per_call": a["roofline"]["kernel_us"], "GBps": a["roofline"]["achieved"],
                                           "frac_of_measured_hbm": a["roofline"]["frac"]} for a in g1},
+            "decode_gemv_floor_us": {"dependent_chain": 2.9, "independent_calls_4_streams": 1.0,
+                                     "what": "a kernel that only streams the 6.9 MB matrix into registers, launched the same two ways "
+                                             "(measured once with a load-only probe, not per run): what launch, latency and HBM leave"},
             "prefill_gemm_m2048": {"TOPS_kernel": roof["achieved"], "frac_of_2x_measured_bf16": roof["frac"],
                                    "frac_of_datasheet_int8": roof.get("frac_datasheet")},
             "bitnet3b_decode_tok_s": {d["workload"].split("_")[4]: d["decode_tok_s"] for d in line["decoder"]},
