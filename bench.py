@@ -576,9 +576,9 @@ class DecodeGemv(Workload):
 
 class DecodeGemvVocab(DecodeGemv):
     """The same decode call on the decoder's largest matrix shape (vocabulary projection, 25.6 MB
-    packed): large enough for the tensor-memory streaming kernel."""
+    packed)."""
     key, name = "decode_gemv_vocab", "bitlinear_decode_gemv_m1_n32002_k3200"
-    kernel_name = "ternary_decode_kernel"
+    kernel_name = "ternary_gemv_bulk_dp4a_kernel"
     N, K, M, LAYERS = 32002, 3200, 1, 16
     BYTES_PER_CALL = 32002 * 3200 // 4 + 3200 * 4 + 32002 * 4
 
@@ -1049,7 +1049,7 @@ def run_ours(args):
     if world == 1 and args.workload == DEFAULT_WORKLOAD and not args.no_also:
         also, cpu_cache = [], {}
         for key, streams in (("w4a16_m256", 1), ("w4a16_m16", 1), ("w4a16_m1", 1), ("decode_gemv_vocab_m16", 1),
-                             ("decode_gemv_vocab", 1), ("decode_gemv", 1), ("decode_gemv", 4)):
+                             ("decode_gemv_vocab", 1), ("decode_gemv_vocab", 4), ("decode_gemv", 1), ("decode_gemv", 4)):
             w2 = make_workload(key, torch, ops, rank, world, streams=streams)
             m2 = measure(torch, w2, max(10, args.steps // 3), 3, use_graph, None, None, want_e2e=True)
             r2 = w2.roofline(peaks, m2["kernel_ms"])

@@ -887,6 +887,9 @@ static bool bulk_supported(int M, int64_t K, bool staged_row = false)
     return M <= 2 && rows != 0 && bulk_smem(rows, M, K, staged_row) <= 160 * 1024;
 }
 
+// Whether one token row goes to the bulk-copy kernel (and not to the older register-staged one) in ternary_gemv_fused_dispatch.
+bool ternary_gemv_bulk_takes_one_row(int64_t K) { return bulk_supported(1, K); }
+
 int ternary_gemv_status(int *out) { return sm100::read_wait_status(out); }
 
 // x [M][K] in its own dtype, M <= 4 (callers pass M <= 2), K % 64 == 0, 16-byte aligned x and w, M*K <= 160 KiB.
