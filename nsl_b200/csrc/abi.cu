@@ -92,7 +92,8 @@ int64_t qtensor_num_scales(const int64_t *, int, int, int, int64_t);
 // at 4-5 TB/s but has ~5 us of start-up (TMEM allocation, token staging, pipeline fill); the
 // register-staged kernels (ternary_gemv*.cu) start in ~2 us and stream at 1-2 TB/s.  Measured
 // crossovers on B200 (K = 3200): 13 MB of packed weights at M = 1, 10 MB at M = 4, 28 MB at M = 8,
-// none at M = 16 (the tensor-memory kernel wins from the smallest size).
+// none at M = 16 (the tensor-memory kernel wins from the smallest size).  (One row in its own dtype never gets
+// here: nslq_bitlinear_forward sends it to the bulk-copy kernel first; the rule still decides for pre-quantised rows.)
 static inline bool decode_pays(int64_t M, int64_t N, int64_t K)
 {
     const double mb = (double)N * (double)K / 4.0 / 1.0e6;
