@@ -511,8 +511,8 @@ class DecodeGemv(Workload):
         self.ws = torch.empty(int(ops.lib().nslq_bitlinear_workspace_bytes(self.M, self.K)), dtype=torch.uint8,
                               device="cuda")
         self.kernel_launches = self.LAYERS
-        # M <= 2: the quantisation is fused into the decode kernel
-        self.launches_per_step = self.LAYERS * (1 if self.M <= 2 else 2)
+        # one row: the quantisation is fused into the decode kernel
+        self.launches_per_step = self.LAYERS * (1 if self.M == 1 else 2)
         self.h2d, self.d2h = self.M * self.K * 4, self.M * self.N * 4
         mb = self.N * self.K / 4e6
         self.l2_note = "%d distinct %.1f MB weights per step (%.0f MB > L2)" % (self.LAYERS, mb, self.LAYERS * mb)
@@ -535,7 +535,7 @@ class DecodeGemv(Workload):
             for i, layer in enumerate(self.layers):
                 j = i % self.streams
                 with self.torch.cuda.stream(self.side[j]):
-                    layer.forward(self.x, out=self.y_side[j], workspace=self.ws)   # M <= 2: workspace unused
+                    layer.forward(self.x, out=self.y_side[j], workspace=self.ws)   # one row: workspace unused
             for st in self.side:
                 cur.wait_stream(st)
             return

@@ -398,10 +398,11 @@ int nslq_bitlinear_forward(const nslq_bitlinear_t *w, const void *x, int x_dtype
     if (decode_pays(M, w->N, w->K) && ternary_decode_fused_supported(w->packed, x, x_dtype, M, w->N, w->K))
         return ternary_decode_fused_dispatch(w->packed, x, x_dtype, (int)M, w->N, w->K, w->weight_scale, y, y_dtype, acc_out,
                                              bias, residual, st);
-    // One launch that also quantises the tokens pays for one or two of them: every CTA repeats the quantisation, and
-    // measured at four tokens ([3200, 3200]) it took 7.3 us against 1.7 + 2.9 for the quantiser and the
-    // pre-quantised kernel as two launches.
-    if (M <= 2 && !decode_pays(M, w->N, w->K) && ternary_gemv_fused_supported(w->packed, x, M, w->K) &&
+    // One launch that also quantises the tokens pays for one of them: every CTA repeats the quantisation.  Measured in
+    // chains over weights that come from HBM, one launch against quantiser + pre-quantised kernel: one row 3.9 against
+    // 5.3 us ([8640, 3200]) and 5.4 against 6.7 ([3200, 8640]); two rows 6.0 against 5.6 and 9.4 against 7.2; four rows
+    // ([3200, 3200]) 7.3 against 1.7 + 2.9.
+    if (M == 1 && !decode_pays(M, w->N, w->K) && ternary_gemv_fused_supported(w->packed, x, M, w->K) &&
         (x_dtype == NSLQ_DTYPE_F32 || aligned16(x)))
         return ternary_gemv_fused_dispatch(w->packed, x, x_dtype, (int)M, w->N, w->K, w->weight_scale, y, y_dtype, acc_out,
                                            bias, residual, st);

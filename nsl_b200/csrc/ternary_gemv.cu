@@ -20,7 +20,7 @@
 //     ((scale/127) * (float)acc) * weight_scale with separately rounded steps
 //     (crates/nsl-codegen/src/bitnet/phases/finalize.rs:39-53).
 //
-// For one or two tokens the activation quantisation is fused in (the bulk-copy kernel below, or
+// For one token the activation quantisation is fused in (the bulk-copy kernel below, or
 // ternary_gemv_fused_kernel -- written for up to four -- where a CTA's slab does not fit): each
 // CTA issues its weight loads, then -- while they are in flight -- quantises the token
 // rows itself (absmax by warp shuffles, the reference's exact rounding) into shared memory
@@ -166,7 +166,7 @@ struct FusedParams {
 constexpr int FUSED_MAX_M = 4;
 
 // Decode kernel with the activation quantisation fused in (up to four tokens; the library calls it
-// for one or two: beyond that the CTAs' repeated quantisation costs more than a second launch).  A CTA owns TPC row tiles
+// for one: beyond that the CTAs' repeated quantisation costs more than a second launch).  A CTA owns TPC row tiles
 // of 16 output rows; each tile's K range is split over KW warps (threads = TPC*KW*32).  The
 // token rows are quantised once per CTA, so a wider CTA repeats less of that work.
 // Dynamic shared memory: [M*K int8 activations, consumption order][TPC*KW*32*4 int reduce]
@@ -321,7 +321,7 @@ ternary_gemv_fused_kernel(const FusedParams p)
     }
 }
 
-// ---------------------------------------------------------------- bulk-copy decode kernel (M <= 2)
+// ---------------------------------------------------------------- bulk-copy decode kernel (one token row)
 // The same product with the weight slab brought in by the copy engine.  A CTA owns ROWS
 // consecutive output rows; in NSL's layout their packed bytes are ONE contiguous range of the
 // weight (ROWS * K/4 bytes), so the CTA's first instruction issues a handful of cp.async.bulk
@@ -477,7 +477,7 @@ static __device__ __forceinline__ void src_quantise_row(const BulkParams &p, int
 }
 
 // The same CTA with the products on the integer ALUs (dp4a) instead of mma.sync: the form used for
-// one and two tokens.  Measured on this part: with eight warps and at most sixteen accumulator
+// one token (the MT = 2 form of the template is kept but no longer dispatched).  Measured on this part: with eight warps and at most sixteen accumulator
 // chains per warp the mma.sync form spends 1.5-2 us multiplying a 64-row slab (one sub-step of
 // 16 MMAs, their 64 ANDs and 8 shared-memory loads takes ~800 cycles at two warps per scheduler),
 // twice the time of this form, and its registers allow two CTAs per SM where this one fits three.
@@ -864,12 +864,9 @@ static int launch_bulk_dp4a(const BulkParams &p, cudaStream_t st)
 template <typename T, int SRC>
 static int pick_bulk_src(const BulkParams &p, cudaStream_t st)
 {
-    if (SRC != SRC_PLAIN) {                                   // the prologue forms take one token (see their callers)
-        if (p.M != 1) return fail(NSLQ_ERR_UNSUPPORTED, "BitLinear: the one-launch RMSNorm / SiLU*up forms take one token, not %d", p.M);
-        return bulk_rows(p.K) == 64 ? launch_bulk_dp4a<T, 64, 1, SRC>(p, st) : launch_bulk_dp4a<T, 32, 1, SRC>(p, st);
-    }
-    if (bulk_rows(p.K) == 64) return p.M == 1 ? launch_bulk_dp4a<T, 64, 1, SRC>(p, st) : launch_bulk_dp4a<T, 64, 2, SRC>(p, st);
-    return p.M == 1 ? launch_bulk_dp4a<T, 32, 1, SRC>(p, st) : launch_bulk_dp4a<T, 32, 2, SRC>(p, st);
+    // one token row in every form (see the callers for the measurements)
+    if (p.M != 1) return fail(NSLQ_ERR_UNSUPPORTED, "BitLinear: the bulk-copy kernel takes one token row, not %d", p.M);
+    return bulk_rows(p.K) == 64 ? launch_bulk_dp4a<T, 64, 1, SRC>(p, st) : launch_bulk_dp4a<T, 32, 1, SRC>(p, st);
 }
 
 template <typename T>
@@ -884,7 +881,7 @@ static int pick_bulk(const BulkParams &p, cudaStream_t st)
 static bool bulk_supported(int M, int64_t K, bool staged_row = false)
 {
     const int rows = bulk_rows(K);
-    return M <= 2 && rows != 0 && bulk_smem(rows, M, K, staged_row) <= 160 * 1024;
+    return M == 1 && rows != 0 && bulk_smem(rows, M, K, staged_row) <= 160 * 1024;
 }
 
 // Whether one token row goes to the bulk-copy kernel (and not to the older register-staged one) in ternary_gemv_fused_dispatch.
@@ -892,7 +889,7 @@ bool ternary_gemv_bulk_takes_one_row(int64_t K) { return bulk_supported(1, K); }
 
 int ternary_gemv_status(int *out) { return sm100::read_wait_status(out); }
 
-// x [M][K] in its own dtype, M <= 4 (callers pass M <= 2), K % 64 == 0, 16-byte aligned x and w, M*K <= 160 KiB.
+// x [M][K] in its own dtype, M <= 4 (callers pass M = 1), K % 64 == 0, 16-byte aligned x and w, M*K <= 160 KiB.
 bool ternary_gemv_fused_supported(const void *w, const void *x, int64_t M, int64_t K)
 {
     return M >= 1 && M <= FUSED_MAX_M && (K % 64 == 0) && aligned16(w) && aligned16(x) && M * K <= 160 * 1024;

@@ -119,7 +119,7 @@ class BitNetDecoder:
         return layer.forward_quantized(qa, out_dtype=torch.float32, residual=residual)
 
     def _norm_lin_shared(self, layers, x2d, norm_w):
-        """RMSNorm, then several projections of the normalised rows.  More than two rows: one
+        """RMSNorm, then several projections of the normalised rows.  More than one row: one
         launch normalises and quantises (the normalised rows never reach memory) and the
         projections share the result; one row: norm and all projections are ONE launch whose CTAs each
         normalise and quantise for themselves (nslq_bitlinear_forward_multi), so neither the norm nor the
