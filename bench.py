@@ -736,7 +736,7 @@ def library_int8_yardstick(torch, ours_kernel_us):
             "peak_TOPS_8192_cube": round(2.0 * 8192 ** 3 / 1e12 / (cube * 1e-6), 1)}
 
 
-def gpu_prior_art(torch, ours_prefill_ms, ours_decode_us):
+def gpu_prior_art(torch, ours_prefill_ms, ours_decode_us, ours_w4_us=None):
     """The design of the one GPU kernel NSL emits for BitLinear (one thread per output column, scalar loop over
     packed bytes read straight from HBM, every CTA re-quantising its activation row), restated in
     oracle/gpu_prior_art.cu and timed on this GPU on the two BitLinear configurations: a baseline leg beside the
@@ -758,15 +758,39 @@ def gpu_prior_art(torch, ours_prefill_ms, ours_decode_us):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / iters
 
+    def timed_w4(Mt, iters):
+        N, K, GS = W4A16.N, W4A16.K, W4A16.GS
+        codes = torch.randint(0, 256, (N, K // 2), device="cuda", dtype=torch.uint8, generator=g)
+        scale = torch.rand(N, K // GS, device="cuda", generator=g) * 0.003
+        zp = torch.randint(0, 16, (N, K // GS), device="cuda", dtype=torch.uint8, generator=g)
+        x = torch.randn(Mt, K, device="cuda", generator=g).to(torch.bfloat16)
+        o.gpu_prior_art_w4_matmul(x, codes, scale, zp, GS)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            o.gpu_prior_art_w4_matmul(x, codes, scale, zp, GS)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e3
+
     M = PrefillGemm.M
     pre = sum(timed_call(M, n, k, 3) for n, k in PrefillGemm.SHAPES)
     dec = timed_call(1, 8640, 3200, 20) * 1e3
+    w4 = {m: timed_w4(m, 10) for m in (1, 16, 256)}
     return {"kernel": "oracle/gpu_prior_art.cu: structure of NSL's emitted BitLinear kernel (crates/nsl-codegen/src/bitnet/mod.rs:133-236), "
                       "block_n 128, fp32 in and out, quantisation inside as in the reference",
             "prefill_m2048_both_projections": {"ms": round(pre, 3), "TOPS": round(2 * PrefillGemm.OPS_PER_PROJ / 1e12 / (pre * 1e-3), 2),
                                                "ours_ms": round(ours_prefill_ms, 5), "speedup_of_ours": round(pre / ours_prefill_ms, 1)},
             "decode_m1_8640x3200": {"us": round(dec, 2), "ours_us": ours_decode_us,
-                                    "speedup_of_ours": round(dec / ours_decode_us, 1) if ours_decode_us else None}}
+                                    "speedup_of_ours": round(dec / ours_decode_us, 1) if ours_decode_us else None},
+            "w4a16_n11008_k4096_g128": {
+                "route": "the reference's nsl_qtensor_matmul_mixed (crates/nsl-runtime/src/quantize.rs:547-585): dequantise the whole "
+                         "weight to f32 on every call (here on the GPU, oracle/gpu_prior_art.cu; the reference does it on the CPU), "
+                         "then the BLAS library's f32 tensor-core (TF32) matmul",
+                "us": {"m%d" % m: round(v, 1) for m, v in w4.items()},
+                "ours_us": ours_w4_us,
+                "speedup_of_ours": {k: round(w4[int(k[1:])] / v, 1) for k, v in (ours_w4_us or {}).items() if v}}}
 
 
 def cpu_arm(key, threads, budget_s):
@@ -1068,7 +1092,8 @@ def run_ours(args):
         line["also"] = also                 # the decode GEMV of configs[0] comes last: the end of a long line is what survives a cut
         g1 = [a for a in also if a["workload"].startswith("bitlinear_decode_gemv_m1_n8640")]
         chain = [a for a in g1 if a["streams"] == 1]
-        line["gpu_prior_art"] = gpu_prior_art(torch, m["ms_per_step"], chain[0]["roofline"]["kernel_us"] if chain else None)
+        w4_us = {"m" + a["workload"].split("_")[1][1:]: a["roofline"]["kernel_us"] for a in also if a["workload"].startswith("w4a16_m")}
+        line["gpu_prior_art"] = gpu_prior_art(torch, m["ms_per_step"], chain[0]["roofline"]["kernel_us"] if chain else None, w4_us)
         line["library_int8_gemm"] = library_int8_yardstick(torch, roof.get("kernel_us"))
         line["targets"] = {
             "decode_gemv_m1_8640x3200": {("independent_calls_%d_streams" % a["streams"]) if a["streams"] > 1 else "dependent_chain":

@@ -90,7 +90,37 @@ __global__ void __launch_bounds__(BLOCK_N) prior_art_bitlinear_kernel(const floa
     y[o] = v;
 }
 
+// The reference's route for a weight-only-quantised linear (crates/nsl-runtime/src/quantize.rs:547-585
+// nsl_qtensor_matmul_mixed): dequantise the whole weight to a dense tensor, every call, then a dense matmul (on the GPU its
+// f32 tensor-core GEMM).  This kernel is the dequantisation, (q - zp) * scale in f64 rounded to f32 (dequantize_val, :258-266),
+// for INT4 codes [N][K/2] (low nibble = even k) with per-group scale and zero point [N][K/group]; the dense matmul is the BLAS
+// library's, called by the benchmark.  The reference dequantises on the CPU; doing it on the GPU flatters the baseline.
+__global__ void __launch_bounds__(256) prior_art_w4_dequant_kernel(const uint8_t *__restrict__ codes, const float *__restrict__ scale,
+                                                                   const uint8_t *__restrict__ zp, float *__restrict__ out, int64_t N,
+                                                                   int64_t K, int64_t group)
+{
+    const int64_t G = (K + group - 1) / group;
+    const int64_t total = N * (K >> 1);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i / (K >> 1), kb = i % (K >> 1);
+        const uint8_t b = codes[i];
+        const int64_t g = (2 * kb) / group;
+        const double sc = (double)scale[n * G + g];
+        const double z = (double)zp[n * G + g];
+        out[n * K + 2 * kb] = (float)(((double)(b & 15u) - z) * sc);
+        out[n * K + 2 * kb + 1] = (float)(((double)(b >> 4) - z) * sc);
+    }
+}
+
 }  // namespace
+
+extern "C" int nslo_gpu_prior_art_w4_dequant(const uint8_t *codes, const float *scale, const uint8_t *zp, float *out, int64_t N, int64_t K,
+                                             int64_t group, void *stream)
+{
+    if (!codes || !scale || !zp || !out || N <= 0 || K <= 0 || K % 2 != 0 || group <= 0 || group % 2 != 0) return -1;
+    prior_art_w4_dequant_kernel<<<148 * 8, 256, 0, (cudaStream_t)stream>>>(codes, scale, zp, out, N, K, group);
+    return (int)cudaGetLastError();
+}
 
 // x [rows][hidden] f32, w [out_dim][hidden/4] NSL's packed bytes, y [rows][out_dim] f32, all on the device.
 // Returns 0, -1 for a bad argument, or the CUDA error code of the launch.

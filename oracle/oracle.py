@@ -35,16 +35,20 @@ def build(force=False):
     return _SO
 
 
+def _load_prior():
+    global _prior
+    build()
+    _prior = C.CDLL(_PRIOR_SO)
+    _prior.nslo_gpu_prior_art_bitlinear.argtypes = [C.c_void_p] * 4 + [C.c_int64] * 3 + [C.c_float] + [C.c_void_p] * 3
+    _prior.nslo_gpu_prior_art_w4_dequant.argtypes = [C.c_void_p] * 4 + [C.c_int64] * 3 + [C.c_void_p]
+
+
 def gpu_prior_art_bitlinear(x, packed, weight_scale, return_acc=False, bias=None, residual=None):
     """The reference's GPU kernel design restated (oracle/gpu_prior_art.cu) on torch CUDA tensors: x [rows, hidden]
     f32, packed [out_dim, hidden/4] u8.  A baseline to time and to check, never part of the product."""
-    global _prior
     import torch
     if _prior is None:
-        if not os.path.exists(_PRIOR_SO):
-            build()
-        _prior = C.CDLL(_PRIOR_SO)
-        _prior.nslo_gpu_prior_art_bitlinear.argtypes = [C.c_void_p] * 4 + [C.c_int64] * 3 + [C.c_float] + [C.c_void_p] * 3
+        _load_prior()
     rows, hidden = x.shape
     out_dim = packed.shape[0]
     assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and packed.is_contiguous() and packed.dtype == torch.uint8
@@ -56,6 +60,37 @@ def gpu_prior_art_bitlinear(x, packed, weight_scale, return_acc=False, bias=None
     if rc != 0:
         raise RuntimeError("nslo_gpu_prior_art_bitlinear returned %d" % rc)
     return (y, acc) if return_acc else y
+
+
+def gpu_prior_art_w4_dequant(codes, scale, zp, group):
+    """The dequantisation half of the reference's route for a weight-only INT4 linear (oracle/gpu_prior_art.cu): codes
+    [N, K/2] u8, scale [N, G] f32, zp [N, G] u8 on the GPU -> dense f32 [N, K], (q - zp) * scale in f64 rounded once."""
+    import torch
+    if _prior is None:
+        _load_prior()
+    N, K = codes.shape[0], codes.shape[1] * 2
+    assert codes.is_cuda and codes.dtype == torch.uint8 and scale.dtype == torch.float32 and zp.dtype == torch.uint8
+    assert codes.is_contiguous() and scale.is_contiguous() and zp.is_contiguous()
+    w = torch.empty(N, K, dtype=torch.float32, device=codes.device)
+    rc = _prior.nslo_gpu_prior_art_w4_dequant(codes.data_ptr(), scale.data_ptr(), zp.data_ptr(), w.data_ptr(), N, K, int(group),
+                                              torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise RuntimeError("nslo_gpu_prior_art_w4_dequant returned %d" % rc)
+    return w
+
+
+def gpu_prior_art_w4_matmul(x, codes, scale, zp, group):
+    """The reference's route for a weight-only INT4 linear -- dequantise the whole weight on every call, then a dense
+    matmul (crates/nsl-runtime/src/quantize.rs:547-585) -- on torch CUDA tensors; the matmul is the BLAS library's f32
+    tensor-core GEMM (TF32).  x [M, K] in any float dtype; returns f32 [M, N]."""
+    import torch
+    w = gpu_prior_art_w4_dequant(codes, scale, zp, group)
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        return x.float() @ w.t()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
 
 
 def lib():

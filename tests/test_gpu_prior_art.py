@@ -34,3 +34,25 @@ def test_prior_art_kernel_equals_the_checker_and_the_library(M, N, K):
         y2 = ops.BitLinear(dev(packed), 0.043).forward(dev(x), bias=dev(bias), residual=dev(res))
         torch.cuda.synchronize()
         assert bits_equal(host(y2), host(y))
+
+
+@pytest.mark.parametrize("M", [1, 16, 40])
+def test_prior_art_w4_route_dequantises_like_the_checker(M):
+    """The W4 baseline (dequantise the whole weight, then a dense TF32 matmul): its dequantised weights equal
+    dequantize_val's (q - zp) * scale in f64, rounded once, bit for bit, and its product agrees with the f64 product of
+    those weights within TF32's rounding of the operands (1e-2 of the row rms)."""
+    rng = np.random.default_rng(M)
+    N, K, GS = 320, 512, 128
+    codes = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+    scale = (np.abs(rng.standard_normal((N, K // GS))) * 0.003).astype(np.float32)
+    zp = rng.integers(0, 16, size=(N, K // GS), dtype=np.uint8)
+    x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).cuda().to(torch.bfloat16)
+    w_gpu = o.gpu_prior_art_w4_dequant(dev(codes), dev(scale), dev(zp), GS)
+    y = o.gpu_prior_art_w4_matmul(x, dev(codes), dev(scale), dev(zp), GS)
+    torch.cuda.synchronize()
+    q = np.stack([codes & 15, codes >> 4], axis=-1).reshape(N, K).astype(np.float64)
+    w_ref = ((q - np.repeat(zp, GS, axis=1).astype(np.float64)) * np.repeat(scale, GS, axis=1).astype(np.float64)).astype(np.float32)
+    assert bits_equal(host(w_gpu), w_ref)
+    want = x.double().cpu().numpy() @ w_ref.astype(np.float64).T
+    rms = np.sqrt((want ** 2).mean(axis=1, keepdims=True))
+    assert np.all(np.abs(host(y).astype(np.float64) - want) <= 1e-2 * rms)
